@@ -1,0 +1,30 @@
+// SiLU-mul of the fused gate|up projection: out[t, i] = silu(gu[t, i]) * gu[t, I + i],
+// silu(z) = z / (1 + exp(-z)) in 32-bit
+// (crates/vllm-models/src/llama/architecture.rs:81-85 computes silu(gate) * up
+// with two library ops).
+#include "common.cuh"
+
+template <typename A>
+__global__ void silu_mul_kernel(const A* __restrict__ gu, A* __restrict__ out, int I, size_t total) {
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const size_t t = idx / I;
+    const int i = (int)(idx - t * I);
+    const float g = to_f32(gu[t * 2 * I + i]);
+    const float u = to_f32(gu[t * 2 * I + I + i]);
+    out[idx] = from_f32<A>(g / (1.f + expf(-g)) * u);
+}
+
+extern "C" int rg_silu_mul(const void* gu, void* out, int dtype, int T, int I, void* stream) {
+    if (T <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t total = (size_t)T * I;
+    const int threads = 256;
+    const unsigned blocks = (unsigned)((total + threads - 1) / threads);
+    if (dtype == RG_DTYPE_BF16)
+        silu_mul_kernel<bf16><<<blocks, threads, 0, s>>>((const bf16*)gu, (bf16*)out, I, total);
+    else if (dtype == RG_DTYPE_F32)
+        silu_mul_kernel<float><<<blocks, threads, 0, s>>>((const float*)gu, (float*)out, I, total);
+    else return RG_ERR_UNSUPPORTED;
+    return RG_LAUNCH_RESULT();
+}

@@ -1,0 +1,76 @@
+// Fused residual-add + RMSNorm.
+//
+//   r = residual[row] (+ pending[row])        32-bit sum, written back
+//   out[i] = w * r / sqrt(mean(r^2) + eps)     sum of squares, rsqrt and the
+//                                              product in 32-bit, one rounding
+// The reference builds the norm from its tensor library
+// (crates/vllm-models/src/llama/architecture.rs:27-28,48,56,154) and adds the
+// residual as a separate op (:53,58); here both are one pass over the row.
+// With `rows` given, output row i is computed from residual row rows[i] and the
+// residual is not written back (the final norm runs only where logits are wanted).
+#include "common.cuh"
+
+template <typename P, typename O>
+__global__ void add_rmsnorm_kernel(float* __restrict__ resid, const P* __restrict__ pending,
+                                   const float* __restrict__ w, float eps, O* __restrict__ out,
+                                   const int* __restrict__ rows, int H) {
+    __shared__ float scratch[33];
+    const int orow = blockIdx.x;
+    const int srow = rows ? rows[orow] : orow;
+    float* r = resid + (size_t)srow * H;
+    const P* p = pending ? pending + (size_t)srow * H : nullptr;
+    const bool write_back = (rows == nullptr) && (p != nullptr);
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = r[i];
+        if (p) v += to_f32(p[i]);
+        if (write_back) r[i] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / (float)H + eps);
+    O* o = out + (size_t)orow * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = r[i];
+        if (p && !write_back) v += to_f32(p[i]);
+        o[i] = from_f32<O>(v * inv * w[i]);
+    }
+}
+
+// residual[row] += pending[row] only (a block arrangement that ends without a norm).
+template <typename P>
+__global__ void residual_add_kernel(float* __restrict__ resid, const P* __restrict__ pending, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) resid[i] += to_f32(pending[i]);
+}
+
+extern "C" int rg_add_rmsnorm(float* resid, const void* pending, int pending_dtype, const float* w,
+                              float eps, void* out, int out_dtype, const int* rows, int n_out_rows,
+                              int H, void* stream) {
+    if (n_out_rows <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+#define RG_NORM(P, O) add_rmsnorm_kernel<P, O><<<n_out_rows, threads, 0, s>>>( \
+        resid, (const P*)pending, w, eps, (O*)out, rows, H)
+    if (pending == nullptr) pending_dtype = out_dtype;
+    if (pending_dtype == RG_DTYPE_BF16 && out_dtype == RG_DTYPE_BF16) RG_NORM(bf16, bf16);
+    else if (pending_dtype == RG_DTYPE_F32 && out_dtype == RG_DTYPE_F32) RG_NORM(float, float);
+    else if (pending_dtype == RG_DTYPE_F32 && out_dtype == RG_DTYPE_BF16) RG_NORM(float, bf16);
+    else if (pending_dtype == RG_DTYPE_BF16 && out_dtype == RG_DTYPE_F32) RG_NORM(bf16, float);
+    else return RG_ERR_UNSUPPORTED;
+#undef RG_NORM
+    return RG_LAUNCH_RESULT();
+}
+
+extern "C" int rg_residual_add(float* resid, const void* pending, int pending_dtype, long long n, void* stream) {
+    if (n <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = 256;
+    const unsigned blocks = (unsigned)((n + threads - 1) / threads);
+    if (pending_dtype == RG_DTYPE_BF16)
+        residual_add_kernel<bf16><<<blocks, threads, 0, s>>>(resid, (const bf16*)pending, (size_t)n);
+    else if (pending_dtype == RG_DTYPE_F32)
+        residual_add_kernel<float><<<blocks, threads, 0, s>>>(resid, (const float*)pending, (size_t)n);
+    else return RG_ERR_UNSUPPORTED;
+    return RG_LAUNCH_RESULT();
+}

@@ -1,0 +1,83 @@
+// Rotary position encoding of Q and K fused with the write of K and V into the
+// paged cache.
+//
+// Rotation (pairs (i, i + d/2), 32-bit):  x'[i] = x[i] c - x[i+d/2] s,
+// x'[i+d/2] = x[i+d/2] c + x[i] s, with c, s = table[pos][i], table[pos][d/2+i]
+// (crates/vllm-cuda/src/kernels/rope.cu:30-41; the table layout [max_pos, d] =
+// cos | sin is that kernel's).  Cache write: token slot = page * page_size +
+// offset, cache[page][0|1][kv_head][offset][:] = k | v, slot < 0 skipped
+// (crates/vllm-cuda/src/kernels/paged_attention.cu:111-138).  The reference
+// never calls its rope kernel; here rotation happens once, before the write,
+// so cached keys are rotated by their absolute position.
+#include "common.cuh"
+
+// qkv: [T, (nh + 2 nkv) d], q rotated in place.  kv_cache: [NP, 2, nkv, ps, d].
+template <typename A>
+__global__ void rope_cache_kernel(A* __restrict__ qkv, const float* __restrict__ table,
+                                  const int* __restrict__ positions, const int* __restrict__ slots,
+                                  A* __restrict__ kv_cache, int nh, int nkv, int d, int page_size,
+                                  int max_pos, int* __restrict__ err) {
+    const int t = blockIdx.x;
+    const int half = d >> 1;
+    int pos = positions[t];
+    if (pos < 0 || pos >= max_pos) {          // host-validated; never read outside the table
+        if (threadIdx.x == 0 && err) atomicExch(err, 1);
+        pos = 0;
+    }
+    A* row = qkv + (size_t)t * (nh + 2 * nkv) * d;
+    const float* cs = table ? table + (size_t)pos * d : nullptr;
+    const int slot = slots ? slots[t] : -1;
+    A* kdst = nullptr;
+    A* vdst = nullptr;
+    if (slot >= 0) {
+        const int page = slot / page_size, off = slot - page * page_size;
+        kdst = kv_cache + (((size_t)page * 2 + 0) * nkv * page_size + off) * d;
+        vdst = kv_cache + (((size_t)page * 2 + 1) * nkv * page_size + off) * d;
+    }
+    const size_t head_stride = (size_t)page_size * d;   // between kv heads inside a page
+    // q heads: rotate in place; k heads: rotate into the cache (and in place)
+    const int n_rot = (nh + nkv) * half;
+    for (int w = threadIdx.x; w < n_rot; w += blockDim.x) {
+        const int h = w / half, i = w - h * half;
+        A* x = row + (size_t)h * d;
+        const float lo = to_f32(x[i]), hi = to_f32(x[i + half]);
+        float nlo = lo, nhi = hi;
+        if (cs) {
+            const float c = cs[i], s = cs[half + i];
+            nlo = lo * c - hi * s;
+            nhi = hi * c + lo * s;
+        }
+        const A olo = from_f32<A>(nlo), ohi = from_f32<A>(nhi);
+        x[i] = olo;
+        x[i + half] = ohi;
+        if (h >= nh && kdst) {
+            A* kd = kdst + (size_t)(h - nh) * head_stride;
+            kd[i] = olo;
+            kd[i + half] = ohi;
+        }
+    }
+    if (vdst) {
+        const A* v = row + (size_t)(nh + nkv) * d;
+        for (int w = threadIdx.x; w < nkv * d; w += blockDim.x) {
+            const int h = w / d, i = w - h * d;
+            vdst[(size_t)h * head_stride + i] = v[w];
+        }
+    }
+}
+
+extern "C" int rg_rope_cache(void* qkv, int dtype, const float* table, const int* positions,
+                             const int* slots, void* kv_cache, int T, int nh, int nkv, int d,
+                             int page_size, int max_pos, int* err, void* stream) {
+    if (T <= 0) return 0;
+    if (d % 2) return RG_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = 256;
+    if (dtype == RG_DTYPE_BF16)
+        rope_cache_kernel<bf16><<<T, threads, 0, s>>>((bf16*)qkv, table, positions, slots, (bf16*)kv_cache,
+                                                      nh, nkv, d, page_size, max_pos, err);
+    else if (dtype == RG_DTYPE_F32)
+        rope_cache_kernel<float><<<T, threads, 0, s>>>((float*)qkv, table, positions, slots, (float*)kv_cache,
+                                                       nh, nkv, d, page_size, max_pos, err);
+    else return RG_ERR_UNSUPPORTED;
+    return RG_LAUNCH_RESULT();
+}

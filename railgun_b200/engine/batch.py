@@ -1,0 +1,148 @@
+"""One step's batch: requests with their next tokens, packed.
+
+An entry is (request, its next tokens, the places among them whose logits are
+wanted).  Portions of prompts and single decoded tokens are the same thing
+here: tokens that continue at the request's position in the cache.  The
+reference packs prefill chunks first and then one token per decode slot, with
+a slot mapping, context lengths and a zero-padded block table
+(crates/vllm-engine/src/engine.rs:185-227, crates/vllm-scheduler/src/batch.rs:41-51);
+the same fields are built here, plus the per-token request index and absolute
+positions that let one attention call serve every cut of the work.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import numpy as np
+import torch
+
+
+class BatchError(ValueError):
+    """A step that cannot run: bad token ids, positions or requests."""
+
+
+@dataclass
+class StepEntry:
+    request_id: int
+    tokens: list
+    want: list = field(default_factory=list)     # indices into ``tokens``
+
+
+@dataclass
+class StepBatch:
+    """Device-side description of a step (int32 tensors unless noted)."""
+    num_tokens: int
+    num_requests: int
+    num_wanted: int
+    max_query_len: int
+    max_context_len: int
+    token_ids: torch.Tensor          # [T]
+    positions: torch.Tensor          # [T] absolute position of each token in its request
+    req_of_token: torch.Tensor       # [T] index into the step's requests
+    want_rows: torch.Tensor          # [W] rows whose logits are wanted
+    cu_seqlens: torch.Tensor         # [R+1] offsets of each request's tokens
+    context_lens: torch.Tensor       # [R] tokens in the cache after this step
+    start_pos: torch.Tensor          # [R] tokens in the cache before this step
+    state_slots: torch.Tensor        # [R] state slot of each request
+    slot_mapping: list               # per page group: [T] page * page_size + offset
+    block_table: list                # per page group: [R, max_blocks]
+    err_flag: torch.Tensor | None = None
+    # host copies, for parts that plan on the host
+    host_cu_seqlens: np.ndarray | None = None
+    host_start_pos: np.ndarray | None = None
+    host_state_slots: np.ndarray | None = None
+    request_ids: list = field(default_factory=list)
+
+
+def build_step_batch(entries, alloc, page_sizes, vocab_size: int, max_position: int, device,
+                     err_flag=None) -> StepBatch:
+    """Validate the entries against the cache's bookkeeping, reserve pages and
+    pack everything into one host buffer that goes to the device in one copy.
+
+    ``alloc`` is the PageAllocator; a request it does not know yet is added.
+    Nothing is launched and nothing is reserved if any entry is invalid."""
+    if not entries:
+        raise BatchError("a step needs at least one entry")
+    seen = set()
+    starts = []
+    for e in entries:
+        if e.request_id in seen:
+            raise BatchError(f"request {e.request_id} appears twice in one step")
+        seen.add(e.request_id)
+        n = len(e.tokens)
+        if n < 1:
+            raise BatchError(f"request {e.request_id}: an entry needs at least one token")
+        toks = np.asarray(e.tokens)
+        if toks.min() < 0 or toks.max() >= vocab_size:
+            raise BatchError(f"request {e.request_id}: token ids must be in [0, {vocab_size})")
+        start = alloc.num_computed(e.request_id) if alloc.has(e.request_id) else 0
+        if start + n > max_position:
+            raise BatchError(f"request {e.request_id}: position {start + n - 1} is beyond the model's "
+                             f"max_position_embeddings {max_position}")
+        for w in e.want:
+            if not 0 <= w < n:
+                raise BatchError(f"request {e.request_id}: wanted place {w} is outside its {n} tokens")
+        starts.append(start)
+    # reserve (atomic per request; on failure give back what this call added)
+    added = []
+    try:
+        for e, start in zip(entries, starts):
+            if not alloc.has(e.request_id):
+                alloc.add_request(e.request_id)
+                added.append(e.request_id)
+            alloc.reserve(e.request_id, start + len(e.tokens))
+    except Exception:
+        for rid in added:
+            alloc.release(rid)
+        raise
+
+    R = len(entries)
+    counts = np.array([len(e.tokens) for e in entries], dtype=np.int64)
+    T = int(counts.sum())
+    W = sum(len(e.want) for e in entries)
+    G = len(page_sizes)
+    tables = [[alloc.block_table(e.request_id, g) for e in entries] for g in range(G)]
+    max_blocks = [max(1, max(len(t) for t in tables[g])) for g in range(G)]
+
+    sizes = [T, T, T, W, R + 1, R, R, R]
+    for g in range(G):
+        sizes += [T, R * max_blocks[g]]
+    offs = np.concatenate([[0], np.cumsum(sizes)])
+    buf = torch.empty(int(offs[-1]), dtype=torch.int32, pin_memory=torch.cuda.is_available())
+    host = buf.numpy()
+    seg = lambda i: host[offs[i]:offs[i + 1]]
+    cu = np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
+    start_arr = np.array(starts, dtype=np.int32)
+    seg(0)[:] = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries])
+    pos = np.concatenate([np.arange(s, s + c, dtype=np.int32) for s, c in zip(starts, counts)])
+    seg(1)[:] = pos
+    req = np.repeat(np.arange(R, dtype=np.int32), counts)
+    seg(2)[:] = req
+    if W:
+        seg(3)[:] = np.concatenate([cu[i] + np.asarray(e.want, dtype=np.int32)
+                                    for i, e in enumerate(entries) if len(e.want)])
+    seg(4)[:] = cu
+    seg(5)[:] = start_arr + counts.astype(np.int32)
+    seg(6)[:] = start_arr
+    slots = np.array([alloc.slot(e.request_id) for e in entries], dtype=np.int32)
+    seg(7)[:] = slots
+    for g in range(G):
+        ps = page_sizes[g]
+        bt = np.zeros((R, max_blocks[g]), dtype=np.int32)
+        for i, t in enumerate(tables[g]):
+            bt[i, :len(t)] = np.maximum(t, 0)          # released pages are never read
+        page_of = bt[req, pos // ps]
+        seg(8 + 2 * g)[:] = page_of * ps + pos % ps
+        seg(9 + 2 * g)[:] = bt.reshape(-1)
+    dev = buf.to(device, non_blocking=True)
+    d = lambda i: dev[int(offs[i]):int(offs[i + 1])]
+    return StepBatch(
+        num_tokens=T, num_requests=R, num_wanted=W,
+        max_query_len=int(counts.max()), max_context_len=int((start_arr + counts).max()),
+        token_ids=d(0), positions=d(1), req_of_token=d(2), want_rows=d(3), cu_seqlens=d(4),
+        context_lens=d(5), start_pos=d(6), state_slots=d(7),
+        slot_mapping=[d(8 + 2 * g) for g in range(G)],
+        block_table=[d(9 + 2 * g).view(R, max_blocks[g]) for g in range(G)],
+        err_flag=err_flag, host_cu_seqlens=cu, host_start_pos=start_arr, host_state_slots=slots,
+        request_ids=[e.request_id for e in entries],
+    )

@@ -1,0 +1,215 @@
+"""Python entry points of the hand-written sm_100a kernels.
+
+Each function checks its arguments (device, dtype, contiguity, sizes), calls
+the ``extern "C"`` launcher on the current CUDA stream and raises on any
+error.  There is no CPU path and no library fallback: without a CUDA device,
+or if a library fails to build, these raise.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_int, c_float, c_void_p, c_longlong
+
+import torch
+
+from . import native
+
+F32, BF16 = 0, 1
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"unsupported dtype {t.dtype}: kernels take float32 or bfloat16")
+
+
+def _check(t: torch.Tensor, name: str, dtype=None) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor (there is no CPU path)")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+
+
+def _ptr(t) -> c_void_p:
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ok(code: int, what: str) -> None:
+    if code == 0:
+        return
+    if code == 10001:
+        raise KernelError(f"{what}: the kernel refuses these sizes or dtypes")
+    raise KernelError(f"{what}: CUDA error {code}")
+
+
+def _fn(lib_name: str, fn_name: str):
+    fn = getattr(native.load(lib_name), fn_name)
+    fn.restype = c_int
+    return fn
+
+
+def embedding(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+    """residual [T, H] float32 = table[ids]."""
+    _check(ids, "ids", torch.int32)
+    _check(table, "table")
+    T, (V, H) = ids.numel(), table.shape
+    out = torch.empty((T, H), dtype=torch.float32, device=table.device)
+    _ok(_fn("embedding", "rg_embedding")(_ptr(ids), _ptr(table), c_int(_dtype_code(table)), _ptr(out),
+                                         c_int(T), c_int(H), c_int(V), _stream()), "embedding")
+    return out
+
+
+def add_rmsnorm(resid: torch.Tensor, pending, weight: torch.Tensor, eps: float, out_dtype,
+                rows: torch.Tensor | None = None) -> torch.Tensor:
+    """resid += pending (in place, 32-bit), then RMSNorm of resid.  With
+    ``rows`` (int32 indices) only those rows are normed and resid is untouched."""
+    _check(resid, "resid", torch.float32)
+    _check(weight, "weight", torch.float32)
+    T, H = resid.shape
+    if weight.numel() != H:
+        raise KernelError(f"norm weight has {weight.numel()} elements, rows have {H}")
+    if pending is not None:
+        _check(pending, "pending")
+        if pending.shape != resid.shape:
+            raise KernelError(f"pending {tuple(pending.shape)} vs residual {tuple(resid.shape)}")
+    n_out = T
+    if rows is not None:
+        _check(rows, "rows", torch.int32)
+        n_out = rows.numel()
+    out = torch.empty((n_out, H), dtype=out_dtype, device=resid.device)
+    _ok(_fn("norm", "rg_add_rmsnorm")(
+        _ptr(resid), _ptr(pending), c_int(_dtype_code(pending) if pending is not None else 0), _ptr(weight),
+        c_float(eps), _ptr(out), c_int(_dtype_code(out)), _ptr(rows), c_int(n_out), c_int(H), _stream()),
+        "add_rmsnorm")
+    return out
+
+
+def residual_add(resid: torch.Tensor, pending: torch.Tensor) -> None:
+    _check(resid, "resid", torch.float32)
+    _check(pending, "pending")
+    if pending.shape != resid.shape:
+        raise KernelError(f"pending {tuple(pending.shape)} vs residual {tuple(resid.shape)}")
+    _ok(_fn("norm", "rg_residual_add")(_ptr(resid), _ptr(pending), c_int(_dtype_code(pending)),
+                                       c_longlong(resid.numel()), _stream()), "residual_add")
+
+
+def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
+    """[T, 2I] -> [T, I]: silu(first half) * second half."""
+    _check(gate_up, "gate_up")
+    T, two_i = gate_up.shape
+    if two_i % 2:
+        raise KernelError("silu_mul: last dimension must be even")
+    out = torch.empty((T, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
+    _ok(_fn("activation", "rg_silu_mul")(_ptr(gate_up), _ptr(out), c_int(_dtype_code(gate_up)),
+                                         c_int(T), c_int(two_i // 2), _stream()), "silu_mul")
+    return out
+
+
+def rope_cache_write(qkv: torch.Tensor, table, positions: torch.Tensor, slots, kv_cache,
+                     nh: int, nkv: int, d: int, page_size: int, err_flag=None) -> None:
+    """Rotate the q and k heads of qkv [T, (nh+2nkv)d] in place by ``table``
+    [max_pos, d] (None: no rotation) and write k, v to the paged cache
+    [NP, 2, nkv, page_size, d] at ``slots`` (None: no write)."""
+    _check(qkv, "qkv")
+    _check(positions, "positions", torch.int32)
+    T = qkv.shape[0]
+    if qkv.shape[1] != (nh + 2 * nkv) * d:
+        raise KernelError(f"qkv row has {qkv.shape[1]} elements, expected {(nh + 2 * nkv) * d}")
+    max_pos = 1 << 30
+    if table is not None:
+        _check(table, "rope table", torch.float32)
+        if table.shape[1] != d:
+            raise KernelError(f"rope table is for head size {table.shape[1]}, heads have {d}")
+        max_pos = table.shape[0]
+    if slots is not None:
+        _check(slots, "slots", torch.int32)
+        _check(kv_cache, "kv_cache", qkv.dtype)
+        if tuple(kv_cache.shape[1:]) != (2, nkv, page_size, d):
+            raise KernelError(f"kv cache shape {tuple(kv_cache.shape)} does not match "
+                              f"[pages, 2, {nkv}, {page_size}, {d}]")
+    _ok(_fn("rope_cache", "rg_rope_cache")(
+        _ptr(qkv), c_int(_dtype_code(qkv)), _ptr(table), _ptr(positions), _ptr(slots),
+        _ptr(kv_cache if slots is not None else None), c_int(T), c_int(nh), c_int(nkv), c_int(d),
+        c_int(page_size), c_int(max_pos), _ptr(err_flag), _stream()), "rope_cache_write")
+
+
+def paged_attention_general(q: torch.Tensor, q_stride: int, kv_cache: torch.Tensor, block_table: torch.Tensor,
+                            req_of_token: torch.Tensor, positions: torch.Tensor, nh: int, nkv: int, d: int,
+                            window: int, scale: float) -> torch.Tensor:
+    """The general attention kernel: out [T, nh*d].  ``q`` may be a view whose
+    rows are ``q_stride`` elements apart (the q part of a fused qkv buffer)."""
+    if not q.is_cuda:
+        raise KernelError("q must be a CUDA tensor (there is no CPU path)")
+    _check(kv_cache, "kv_cache", q.dtype)
+    _check(block_table, "block_table", torch.int32)
+    _check(req_of_token, "req_of_token", torch.int32)
+    _check(positions, "positions", torch.int32)
+    T = positions.numel()
+    page_size = kv_cache.shape[3]
+    if tuple(kv_cache.shape[1:]) != (2, nkv, page_size, d):
+        raise KernelError(f"kv cache shape {tuple(kv_cache.shape)} does not match heads {nkv} x {d}")
+    if d > 256:
+        raise KernelError(f"head size {d} is above the kernels' limit of 256")
+    out = torch.empty((T, nh * d), dtype=q.dtype, device=q.device)
+    _ok(_fn("attention_general", "rg_paged_attention_general")(
+        _ptr(q), c_int(q_stride), _ptr(out), _ptr(kv_cache), c_int(_dtype_code(q)), _ptr(block_table),
+        c_int(block_table.shape[1]), _ptr(req_of_token), _ptr(positions), c_int(T), c_int(nh), c_int(nkv),
+        c_int(d), c_int(page_size), c_int(window or 0), c_float(scale), _stream()), "paged_attention_general")
+    return out
+
+
+def argmax(logits: torch.Tensor) -> torch.Tensor:
+    _check(logits, "logits", torch.float32)
+    rows, V = logits.shape
+    out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    _ok(_fn("sampling", "rg_argmax")(_ptr(logits), c_int(rows), c_int(V), _ptr(out), _stream()), "argmax")
+    return out
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k, top_p, seed: torch.Tensor,
+           counter: torch.Tensor) -> torch.Tensor:
+    """One token per row; rows with temperature <= 0 are greedy.  ``seed`` and
+    ``counter`` are int64 tensors read as unsigned 64-bit."""
+    _check(logits, "logits", torch.float32)
+    rows, V = logits.shape
+    _check(temperature, "temperature", torch.float32)
+    _check(seed, "seed", torch.int64)
+    _check(counter, "counter", torch.int64)
+    if top_k is not None:
+        _check(top_k, "top_k", torch.int32)
+    if top_p is not None:
+        _check(top_p, "top_p", torch.float32)
+    for name, t in (("temperature", temperature), ("seed", seed), ("counter", counter),
+                    ("top_k", top_k), ("top_p", top_p)):
+        if t is not None and t.numel() != rows:
+            raise KernelError(f"{name} has {t.numel()} entries for {rows} rows")
+    out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    _ok(_fn("sampling", "rg_sample")(_ptr(logits), c_int(rows), c_int(V), _ptr(temperature), _ptr(top_k),
+                                     _ptr(top_p), _ptr(seed), _ptr(counter), _ptr(out), _stream()), "sample")
+    return out
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype=None) -> torch.Tensor:
+    """y = x W^T, W stored [out, in]: the library matrix product (cuBLAS), as in
+    the reference, whose projections are library GEMMs
+    (crates/vllm-models/src/llama/attention.rs:94-96,133).  32-bit inputs run
+    in true 32-bit: the reduced-precision matrix mode is refused."""
+    if not x.is_cuda:
+        raise KernelError("linear: CUDA tensors only (there is no CPU path)")
+    if x.dtype == torch.float32 and torch.backends.cuda.matmul.allow_tf32:
+        raise KernelError("linear: TF32 is enabled; the 32-bit path must be true 32-bit")
+    if out_dtype is not None and out_dtype != x.dtype:
+        return torch.mm(x, weight.t(), out_dtype=out_dtype)
+    return torch.mm(x, weight.t())

@@ -1,0 +1,82 @@
+"""Grouped-query attention over the paged cache.
+
+q, k, v = x Wq^T, x Wk^T, x Wv^T (crates/vllm-models/src/llama/attention.rs:94-96);
+positions are encoded into q and k, k and v go to the cache, then every query
+attends its request's keys up to its own position (and not further back than
+the window, if there is one), and the result goes through Wo (:133).  The
+three projections are one matrix here, stacked by rows at load, which gives
+the same numbers as three products.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..cache.manager import PagedKVNeed
+from ..weights.loader import TensorSpec
+from .base import Mixer
+from .registry import register_mixer, POSITION_ENCODINGS
+
+
+class PagedAttention(Mixer):
+    """params: ``hidden_size``, ``num_heads``, ``num_kv_heads``, ``head_dim``,
+    ``window`` (0: none), ``scale`` (None: head_dim^-0.5), ``position``
+    (a PartSpec or None)."""
+
+    @classmethod
+    def tensor_specs(cls, p, prefix):
+        H, nh, nkv, d = p["hidden_size"], p["num_heads"], p["num_kv_heads"], p["head_dim"]
+        return {
+            prefix + "self_attn.q_proj.weight": TensorSpec((nh * d, H)),
+            prefix + "self_attn.k_proj.weight": TensorSpec((nkv * d, H)),
+            prefix + "self_attn.v_proj.weight": TensorSpec((nkv * d, H)),
+            prefix + "self_attn.o_proj.weight": TensorSpec((H, nh * d)),
+        }
+
+    @classmethod
+    def cache_need(cls, p):
+        return PagedKVNeed(p["num_kv_heads"], p["head_dim"], int(p.get("window") or 0))
+
+    def __init__(self, p, prefix, env, tensors):
+        super().__init__(p, prefix, env, tensors)
+        self.nh, self.nkv, self.d = p["num_heads"], p["num_kv_heads"], p["head_dim"]
+        if self.nh % self.nkv:
+            raise ValueError(f"{self.nh} heads cannot share {self.nkv} key/value heads")
+        if self.d > 256:
+            raise ValueError(f"head size {self.d} is above the attention kernels' limit of 256")
+        self.window = int(p.get("window") or 0)
+        self.scale = float(p["scale"]) if p.get("scale") is not None else float(self.d) ** -0.5
+        a = prefix + "self_attn."
+        self.w_qkv = torch.cat([tensors.get(a + "q_proj.weight", env.dtype),
+                                tensors.get(a + "k_proj.weight", env.dtype),
+                                tensors.get(a + "v_proj.weight", env.dtype)], dim=0).contiguous()
+        tensors.drop(a + "q_proj.weight", a + "k_proj.weight", a + "v_proj.weight")
+        self.w_o = tensors.get(a + "o_proj.weight", env.dtype)
+        pos = p.get("position")
+        self.position = None
+        if pos is not None:
+            self.position = tensors.shared_part(("position", pos), lambda: POSITION_ENCODINGS.get(pos.kind)(
+                pos.params, prefix, env, tensors))
+
+    def forward(self, x, batch, cache, writes=True):
+        nh, nkv, d = self.nh, self.nkv, self.d
+        qkv = ops.linear(x, self.w_qkv)
+        slots = batch.slot_mapping[cache.group]
+        kv_dest = (cache.kv, slots) if writes else None
+        wrote = False
+        if self.position is not None:
+            wrote = self.position.apply(qkv, batch, nh, nkv, d, kv_dest)
+        if writes and not wrote:
+            ops.rope_cache_write(qkv, None, batch.positions, slots, cache.kv, nh, nkv, d, cache.page_size,
+                                 batch.err_flag)
+        out = self.attend(qkv, batch, cache)
+        return ops.linear(out, self.w_o)
+
+    def attend(self, qkv, batch, cache):
+        """Pick the attention kernel for this step's shape and precision."""
+        return ops.paged_attention_general(
+            qkv, qkv.shape[1], cache.kv, batch.block_table[cache.group], batch.req_of_token, batch.positions,
+            self.nh, self.nkv, self.d, self.window, self.scale)
+
+
+register_mixer("paged_attention", PagedAttention)

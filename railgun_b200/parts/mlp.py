@@ -1,0 +1,39 @@
+"""Dense gated feed-forward: down(silu(gate(x)) * up(x))
+(crates/vllm-models/src/llama/architecture.rs:75-85).  gate and up are one
+matrix here, stacked by rows at load.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..weights.loader import TensorSpec
+from .base import FeedForward
+from .registry import register_feed_forward
+
+
+class SwiGLU(FeedForward):
+    """params: ``hidden_size``, ``intermediate_size``."""
+
+    @classmethod
+    def tensor_specs(cls, p, prefix):
+        H, I = p["hidden_size"], p["intermediate_size"]
+        return {
+            prefix + "mlp.gate_proj.weight": TensorSpec((I, H)),
+            prefix + "mlp.up_proj.weight": TensorSpec((I, H)),
+            prefix + "mlp.down_proj.weight": TensorSpec((H, I)),
+        }
+
+    def __init__(self, p, prefix, env, tensors):
+        super().__init__(p, prefix, env, tensors)
+        m = prefix + "mlp."
+        self.w_gate_up = torch.cat([tensors.get(m + "gate_proj.weight", env.dtype),
+                                    tensors.get(m + "up_proj.weight", env.dtype)], dim=0).contiguous()
+        tensors.drop(m + "gate_proj.weight", m + "up_proj.weight")
+        self.w_down = tensors.get(m + "down_proj.weight", env.dtype)
+
+    def forward(self, x, batch):
+        return ops.linear(ops.silu_mul(ops.linear(x, self.w_gate_up)), self.w_down)
+
+
+register_feed_forward("swiglu", SwiGLU)

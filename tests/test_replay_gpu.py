@@ -1,0 +1,128 @@
+"""Trace replay on the GPU against the plain implementation: every request
+whole, with the last 32 tokens decoded one by one, in portions of changing
+size, and mixed with other requests in a pool so small that pages are used
+again; in 32-bit and in bfloat16, for both tiny configurations."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+import helpers
+from plain_llama import PlainLlama
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = {"A": [5, 17, 33, 70, 100, 131, 64, 48], "B": [1, 9, 40, 63, 100, 200, 77, 129]}
+# Largest absolute logit difference allowed, as a fraction of the largest
+# absolute logit of the row's sequence.  32-bit differs from the 64-bit plain
+# implementation by accumulated rounding only; bfloat16 rounds activations to
+# 8 bits of mantissa between kernels.
+TOL = {"float32": 2e-5, "bfloat16": 3e-2}
+
+_oracle_cache: dict = {}
+
+
+def oracle(name):
+    if name not in _oracle_cache:
+        cfg = helpers.TINY[name][0]
+        reqs = {f"r{i}": p for i, p in enumerate(helpers.prompts(cfg["vocab_size"], LENGTHS[name], seed=11))}
+        plain = PlainLlama(helpers.model_dir(name))
+        _oracle_cache[name] = (reqs, {k: plain.forward(v) for k, v in reqs.items()})
+    return _oracle_cache[name]
+
+
+def make_trace(mode, reqs):
+    if mode == "whole":
+        return helpers.trace_whole(reqs)
+    if mode == "tail":
+        return helpers.trace_tail_decode(reqs, 32)
+    if mode == "portions":
+        return helpers.trace_portions(reqs)
+    if mode == "mixed":
+        return helpers.trace_mixed(reqs, max_live=4, seed=5)
+    raise ValueError(mode)
+
+
+def compare(rows, reqs, logits, dtype, what):
+    worst = 0.0
+    for name, toks in reqs.items():
+        ref = logits[name]
+        scale = np.abs(ref).max()
+        for p in range(len(toks)):
+            got = rows[(name, p)]
+            err = np.abs(got - ref[p]).max() / scale
+            if err > TOL[dtype]:
+                raise AssertionError(f"{what}: request {name} (length {len(toks)}) first differs at position {p}: "
+                                     f"relative error {err:.3e} > {TOL[dtype]:.1e}")
+            worst = max(worst, err)
+    return worst
+
+
+@pytest.mark.parametrize("mode", ["whole", "tail", "portions", "mixed"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_replay_matches_plain(name, dtype, mode, tmp_path):
+    from railgun_b200.engine.runner import ModelRunner
+    from railgun_b200.replay import Replayer
+    cfg, _, page = helpers.TINY[name]
+    reqs, logits = oracle(name)
+    steps = make_trace(mode, reqs)
+    max_tokens = helpers.peak_tokens(steps, 64)
+    runner = ModelRunner(helpers.model_dir(name), dtype=dtype, page_size=page, max_tokens=max_tokens,
+                         max_requests=4)
+    rp = Replayer(runner, tmp_path)
+    for s in steps:
+        rp.feed(s)
+    runner.alloc.check()
+    assert runner.alloc.num_requests() == 0
+    rows = helpers.collect(steps, tmp_path, cfg["vocab_size"])
+    worst = compare(rows, reqs, logits, dtype, f"tiny {name} {dtype} {mode}")
+    print(f"tiny {name} {dtype} {mode}: worst relative error {worst:.3e}")
+
+
+def test_pages_are_used_again(tmp_path):
+    """The mixed trace needs more pages over its life than the pool has."""
+    from railgun_b200.engine.runner import ModelRunner
+    from railgun_b200.replay import Replayer
+    cfg, _, page = helpers.TINY["B"]
+    reqs, _ = oracle("B")
+    steps = make_trace("mixed", reqs)
+    max_tokens = helpers.peak_tokens(steps, 64)
+    assert sum(-(-len(t) // page) for t in reqs.values()) * page > max_tokens
+    runner = ModelRunner(helpers.model_dir("B"), dtype="float32", page_size=page, max_tokens=max_tokens,
+                         max_requests=4)
+    rp = Replayer(runner, tmp_path)
+    seen_pages, reused = set(), False
+    for s in steps:
+        rp.feed(s)
+        for rid in list(rp._ids.values()):
+            for p in runner.alloc.block_table(rid, 0):
+                pass
+        live = {int(p) for rid in rp._ids.values() for p in runner.alloc.block_table(rid, 0)}
+        ended_pages = seen_pages - live
+        seen_pages |= live
+        reused = reused or bool(ended_pages)
+    assert reused
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(dtype, tmp_path):
+    """bin/trace_run as a user runs it: steps on standard input, files out."""
+    cfg, _, page = helpers.TINY["A"]
+    reqs, logits = oracle("A")
+    some = {k: reqs[k] for k in list(reqs)[:4]}
+    steps = helpers.trace_mixed(some, max_live=3, seed=1)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = tmp_path / "out"
+    proc = subprocess.run(
+        [sys.executable, os.path.join(root, "bin", "trace_run"), "--model", str(helpers.model_dir("A")),
+         "--dtype", dtype, "--out", str(out), "--max-tokens", str(helpers.peak_tokens(steps, 64))],
+        input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    done = [l for l in proc.stdout.splitlines() if l.startswith("done ")]
+    assert done == [f"done {s['step']}" for s in steps]
+    rows = helpers.collect(steps, out, cfg["vocab_size"])
+    compare(rows, some, logits, dtype, f"trace_run {dtype}")
