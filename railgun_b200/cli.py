@@ -1,0 +1,112 @@
+"""The command line: ``railgun generate`` and ``railgun random-weights``.
+
+``generate`` keeps the reference's options and meanings
+(crates/vllm-cli/src/generate.rs:29-53): ``--model/-m DIR``, ``--max-tokens``
+(default 128), ``--temperature`` (default 0.0 = greedy; honoured here, the
+reference parses and ignores it), ``--cuda-device N``, ``--show-token-ids``.
+Prompts are token ids (``--prompt-ids 1,2,3;4,5``): tokenizers are out of
+scope, so ``--prompt/-p TEXT`` is replaced.  The engine options of the
+reference's ``serve`` (crates/vllm-cli/src/serve.rs:44-77) are accepted with
+their names and defaults.  It prints the generated ids and a ``[stats]`` line
+with tokens per second, as the reference does (generate.rs:99-111).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+import time
+
+
+def make_parser() -> argparse.ArgumentParser:
+    ap = argparse.ArgumentParser(prog="railgun", description="a small B200 inference engine")
+    sub = ap.add_subparsers(dest="command", required=True)
+
+    g = sub.add_parser("generate", help="generate tokens from prompt token ids")
+    g.add_argument("-m", "--model", required=True, help="model folder (config.json + *.safetensors)")
+    g.add_argument("--prompt-ids", required=True,
+                   help="prompt token ids, comma separated; several prompts separated by ';'")
+    g.add_argument("--max-tokens", type=int, default=128, help="maximum number of new tokens")
+    g.add_argument("--temperature", type=float, default=0.0, help="sampling temperature (0.0 = greedy)")
+    g.add_argument("--top-p", type=float, default=1.0)
+    g.add_argument("--top-k", type=int, default=0)
+    g.add_argument("--seed", type=int, default=0, help="seed of the requests' random draws")
+    g.add_argument("--stop-token-ids", default="", help="comma separated ids that end generation")
+    g.add_argument("--cuda-device", type=int, default=0, help="CUDA device ordinal (there is no CPU path)")
+    g.add_argument("--show-token-ids", action="store_true", help="print prompt ids beside the generated ids")
+    g.add_argument("--dtype", default="bf16", choices=["bf16", "f32", "bfloat16", "float32"])
+    g.add_argument("--max-num-seqs", type=int, default=256)
+    g.add_argument("--max-num-batched-tokens", type=int, default=4096)
+    g.add_argument("--block-size", type=int, default=16)
+    g.add_argument("--num-gpu-blocks", type=int, default=1000)
+    g.add_argument("--max-model-len", type=int, default=4096)
+    g.add_argument("--max-prefill-chunk", type=int, default=0)
+
+    r = sub.add_parser("random-weights", help="write a model folder with seeded random weights")
+    r.add_argument("--config", required=True, help="a config.json to take the sizes from")
+    r.add_argument("--seed", type=int, default=0)
+    r.add_argument("--out", required=True, help="folder to write config.json and model.safetensors into")
+    r.add_argument("--std", type=float, default=0.02)
+    return ap
+
+
+def _ids(text: str) -> list:
+    return [int(t) for t in text.replace(" ", "").split(",") if t != ""]
+
+
+def run_generate(args) -> int:
+    from .engine.engine import Engine
+    from .engine.request import SamplingParams
+
+    prompts = [_ids(p) for p in args.prompt_ids.split(";") if p.strip()]
+    if not prompts or any(not p for p in prompts):
+        print("error: --prompt-ids needs at least one token id per prompt", file=sys.stderr)
+        return 2
+    t0 = time.time()
+    engine = Engine(args.model, dtype=args.dtype, cuda_device=args.cuda_device, block_size=args.block_size,
+                    num_gpu_blocks=args.num_gpu_blocks, max_num_seqs=args.max_num_seqs,
+                    max_num_batched_tokens=args.max_num_batched_tokens, max_model_len=args.max_model_len,
+                    max_prefill_chunk=args.max_prefill_chunk)
+    load_ms = (time.time() - t0) * 1e3
+    params = [SamplingParams(max_new_tokens=args.max_tokens, temperature=args.temperature, top_p=args.top_p,
+                             top_k=args.top_k, stop_token_ids=_ids(args.stop_token_ids), seed=args.seed + i)
+              for i in range(len(prompts))]
+    t0 = time.time()
+    outs = engine.generate(prompts, params)
+    dt = time.time() - t0
+    for p, o in zip(prompts, outs):
+        if args.show_token_ids:
+            print(f"prompt ids: {p}")
+        print(",".join(str(t) for t in o.token_ids))
+        if o.error:
+            print(f"[error] request {o.request_id}: {o.error}", file=sys.stderr)
+    n = sum(len(o.token_ids) for o in outs)
+    print(f"[stats] {n} tokens in {dt * 1e3:.1f} ms = {n / dt:.1f} tok/s (load {load_ms:.0f} ms)")
+    return 0
+
+
+def run_random_weights(args) -> int:
+    from .config.base import read_json
+    from .config.registry import architecture_of
+    from .weights.random_init import write_random_model
+
+    data = read_json(args.config)
+    archs = data.get("architectures") or []
+    if not archs:
+        print("error: the config has no 'architectures'", file=sys.stderr)
+        return 2
+    arch = architecture_of(archs[0])
+    out = write_random_model(arch.config_from_dict(data, args.config), args.seed, args.out, std=args.std)
+    print(json.dumps({"written": str(out)}))
+    return 0
+
+
+def main(argv=None) -> int:
+    args = make_parser().parse_args(argv)
+    if args.command == "generate":
+        return run_generate(args)
+    return run_random_weights(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,104 @@
+"""The Python entry point: ``Engine(model_dir, ...).generate(prompt_ids, params)``.
+
+The loop is the reference's engine loop without the async plumbing
+(crates/vllm-engine/src/engine.rs:82-163): schedule -> one model step on the
+packed batch -> sample at each request's last position -> update the
+scheduler -> collect finished requests.  Option names are the reference's
+(crates/vllm-cli/src/serve.rs:44-77, docs/cli-configuration.md:7-27):
+``dtype``, ``max_num_seqs``, ``max_num_batched_tokens``, ``block_size``,
+``num_gpu_blocks``, ``max_model_len``.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+from ..sampling.sampler import Sampler
+from .batch import StepEntry
+from .request import RequestOutput, SamplingParams
+from .runner import ModelRunner
+from .scheduler import Scheduler, SchedulerConfig
+
+
+class Engine:
+    def __init__(self, model_dir, dtype="bfloat16", cuda_device: int = 0, block_size: int = 16,
+                 num_gpu_blocks: int = 1000, max_num_seqs: int = 256, max_num_batched_tokens: int = 4096,
+                 max_model_len: int = 4096, max_prefill_chunk: int = 0):
+        self.runner = ModelRunner(model_dir, dtype=dtype, device=f"cuda:{cuda_device}", page_size=block_size,
+                                  max_tokens=num_gpu_blocks * block_size, max_requests=max_num_seqs)
+        max_model_len = min(max_model_len, self.runner.model.spec.max_position)
+        self.scheduler = Scheduler(self.runner.alloc, SchedulerConfig(
+            max_num_batched_tokens=max_num_batched_tokens, max_num_seqs=max_num_seqs,
+            max_prefill_chunk=max_prefill_chunk, max_model_len=max_model_len))
+        self.sampler = Sampler(self.runner.device)
+        self._params: dict = {}
+        self._next_id = 1
+        self.steps_run = 0
+
+    # ---- low level --------------------------------------------------------------------------
+    def add_request(self, prompt_ids, params: SamplingParams | None = None) -> int:
+        params = params or SamplingParams()
+        params.validate()
+        vocab = self.runner.model.vocab_size
+        if any((t < 0 or t >= vocab) for t in prompt_ids):
+            raise ValueError(f"prompt token ids must be in [0, {vocab})")
+        rid = self._next_id
+        self._next_id += 1
+        self.scheduler.add_request(rid, prompt_ids, params.max_new_tokens, params.stop_token_ids)
+        self._params[rid] = params
+        return rid
+
+    def step(self) -> list:
+        """One scheduler decision and one model step.  Returns the (request id,
+        sampled token) pairs of this step, or None if nothing could be scheduled."""
+        entries = self.scheduler.schedule()
+        if not entries:
+            return None
+        batch = [StepEntry(e.request_id, e.tokens, [len(e.tokens) - 1] if e.want_last else []) for e in entries]
+        logits = self.runner.step(batch)
+        self.steps_run += 1
+        wanted = [e.request_id for e in entries if e.want_last]
+        if logits is None:
+            self.scheduler.update([], [])
+            return []
+        tokens = self.sampler.sample(logits, [self._params[r] for r in wanted],
+                                     [self.scheduler.num_generated(r) for r in wanted])
+        self.scheduler.update(wanted, tokens)
+        return list(zip(wanted, tokens.tolist()))
+
+    def abort(self, request_id: int) -> None:
+        self.scheduler.abort(request_id)
+
+    def collect(self, request_id: int) -> RequestOutput:
+        """The outcome of a finished request; the engine forgets it."""
+        out = RequestOutput(request_id, self.scheduler.outputs(request_id),
+                            self.scheduler.finish_reason(request_id), self.scheduler.error(request_id),
+                            self.scheduler.num_preemptions(request_id))
+        self.scheduler.forget(request_id)
+        self._params.pop(request_id, None)
+        return out
+
+    def has_unfinished(self) -> bool:
+        return self.scheduler.num_waiting + self.scheduler.num_running > 0
+
+    def stats(self) -> dict:
+        return dict(num_waiting=self.scheduler.num_waiting, num_running=self.scheduler.num_running,
+                    num_free_blocks=self.runner.alloc.free_pages(0), steps=self.steps_run)
+
+    # ---- the call a user makes --------------------------------------------------------------
+    def generate(self, prompt_ids, params=None) -> list:
+        """Generate for every prompt (lists of token ids); ``params`` is one
+        SamplingParams for all or a list with one per prompt.  Returns a
+        RequestOutput per prompt, in order."""
+        if prompt_ids and isinstance(prompt_ids[0], (int, np.integer)):
+            prompt_ids = [prompt_ids]
+        if params is None or isinstance(params, SamplingParams):
+            params = [params or SamplingParams()] * len(prompt_ids)
+        if len(params) != len(prompt_ids):
+            raise ValueError(f"{len(prompt_ids)} prompts but {len(params)} parameter sets")
+        rids = [self.add_request(list(p), sp) for p, sp in zip(prompt_ids, params)]
+        while self.has_unfinished():
+            finished_before = len(self.scheduler.finished())
+            if (self.step() is None and len(self.scheduler.finished()) == finished_before
+                    and not self.scheduler.preempted()):
+                raise RuntimeError("the scheduler can make no progress: no request fits the cache")
+        return [self.collect(r) for r in rids]

@@ -58,9 +58,14 @@ def _find(tool: str, extra: list[str]) -> str:
     raise NativeBuildError(f"{tool} not found; it is needed to build the native libraries")
 
 
+_build_dir_cache: list = []
+
+
 def _build_dir() -> Path:
     """In-tree ``_native/`` when writable, else a per-user folder under the
     system's temporary directory."""
+    if _build_dir_cache:
+        return _build_dir_cache[0]
     env = os.environ.get("RAILGUN_B200_BUILD_DIR")
     candidates = [Path(env)] if env else []
     candidates.append(Path(__file__).resolve().parent / "_native")
@@ -68,9 +73,10 @@ def _build_dir() -> Path:
     for c in candidates:
         try:
             c.mkdir(parents=True, exist_ok=True)
-            probe = c / f".w{os.getpid()}"
+            probe = c / f".w{os.getpid()}_{threading.get_ident()}"
             probe.write_text("")
             probe.unlink()
+            _build_dir_cache.append(c)
             return c
         except OSError:
             continue

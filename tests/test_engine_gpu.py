@@ -1,0 +1,176 @@
+"""Generation through the Python entry point and the command line: greedy
+against the plain implementation, seeded temperature sampling, preemption,
+long decoding and the first tokens of a sequence."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+import helpers
+import plain_llama as P
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def margin_ok(plain, prompt, out, min_margin):
+    """True while the plain model's top-2 margin along ``out`` stays above ``min_margin``."""
+    ids = list(prompt)
+    for t in out:
+        lg = np.sort(plain.forward(ids)[-1])
+        if lg[-1] - lg[-2] < min_margin:
+            return False
+        ids.append(t)
+    return True
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_matches_plain(name, dtype):
+    from railgun_b200.engine.engine import Engine
+    from railgun_b200.engine.request import SamplingParams
+    cfg, _, page = helpers.TINY[name]
+    lengths = [5, 17, 33] if name == "A" else [1, 9, 40, 63, 100]
+    n_new = 8 if name == "A" else 12
+    prompts = helpers.prompts(cfg["vocab_size"], lengths, seed=1 if name == "A" else 3)
+    plain = P.PlainLlama(helpers.model_dir(name))
+    eng = Engine(helpers.model_dir(name), dtype=dtype, block_size=page, num_gpu_blocks=64, max_num_seqs=8,
+                 max_num_batched_tokens=64, max_prefill_chunk=32 if name == "B" else 0, max_model_len=256)
+    outs = eng.generate(prompts, SamplingParams(max_new_tokens=n_new))
+    checked = 0
+    for p, o in zip(prompts, outs):
+        assert o.finish_reason == "max_tokens" and len(o.token_ids) == n_new
+        ref = plain.greedy(p, n_new)
+        if dtype == "float32" or margin_ok(plain, p, ref, 0.05 * 20):
+            assert o.token_ids == ref
+            checked += 1
+    assert checked >= 1
+    assert eng.stats()["num_free_blocks"] == 64 and not eng.has_unfinished()
+
+
+def test_first_tokens_of_a_sequence():
+    """Prompts of one and two tokens, and the first generated tokens, in one batch."""
+    from railgun_b200.engine.engine import Engine
+    from railgun_b200.engine.request import SamplingParams
+    cfg, _, page = helpers.TINY["A"]
+    plain = P.PlainLlama(helpers.model_dir("A"))
+    eng = Engine(helpers.model_dir("A"), dtype="float32", block_size=page, num_gpu_blocks=32, max_num_seqs=8)
+    prompts = [[7], [200, 3], [0], [255, 255, 255]]
+    outs = eng.generate(prompts, SamplingParams(max_new_tokens=3))
+    for p, o in zip(prompts, outs):
+        assert o.token_ids == plain.greedy(p, 3)
+
+
+def test_long_decoding_and_stop_token():
+    """A short prompt decoded for 200 tokens, token by token, across many pages."""
+    from railgun_b200.engine.engine import Engine
+    from railgun_b200.engine.request import SamplingParams
+    cfg, _, page = helpers.TINY["B"]
+    plain = P.PlainLlama(helpers.model_dir("B"))
+    prompt = helpers.prompts(cfg["vocab_size"], [6], seed=12)[0]
+    eng = Engine(helpers.model_dir("B"), dtype="float32", block_size=page, num_gpu_blocks=40, max_num_seqs=2,
+                 max_model_len=512)
+    out = eng.generate([prompt], SamplingParams(max_new_tokens=200))[0]
+    assert len(out.token_ids) == 200
+    # teacher-forced check: every generated token is the plain argmax given the tokens before it
+    logits = plain.forward(prompt + out.token_ids)
+    for i, t in enumerate(out.token_ids):
+        row = logits[len(prompt) - 1 + i]
+        assert row[t] >= np.sort(row)[-1] - 1e-4 * np.abs(row).max(), f"generated token {i} is not the argmax"
+    # the same request with a stop token ends there, stop token kept
+    stop = out.token_ids[20]
+    first = out.token_ids.index(stop)
+    again = eng.generate([prompt], SamplingParams(max_new_tokens=200, stop_token_ids=[stop]))[0]
+    assert again.finish_reason == "stop_token" and again.token_ids == out.token_ids[:first + 1]
+
+
+def test_temperature_sampling_is_seeded_and_batch_invariant():
+    from railgun_b200.engine.engine import Engine
+    from railgun_b200.engine.request import SamplingParams
+    cfg, _, page = helpers.TINY["B"]
+    prompts = helpers.prompts(cfg["vocab_size"], [9, 40, 63, 20], seed=3)
+    params = [SamplingParams(max_new_tokens=12, temperature=0.8, seed=100 + i) if i % 2 else
+              SamplingParams(max_new_tokens=12) for i in range(4)]
+    mk = lambda: Engine(helpers.model_dir("B"), dtype="float32", block_size=page, num_gpu_blocks=64, max_num_seqs=8,
+                        max_prefill_chunk=32)
+    together = mk().generate(prompts, params)
+    eng = mk()
+    alone = [eng.generate([p], sp)[0] for p, sp in zip(prompts, params)]
+    for a, b in zip(together, alone):
+        assert a.token_ids == b.token_ids
+    other_seed = mk().generate([prompts[1]], SamplingParams(max_new_tokens=12, temperature=0.8, seed=999))[0]
+    assert other_seed.token_ids != together[1].token_ids
+    # each sampled token is what the plain sampler draws from the plain logits with the same seed and counter
+    plain = P.PlainLlama(helpers.model_dir("B"))
+    ids = list(prompts[1])
+    for k, t in enumerate(together[1].token_ids):
+        row = plain.forward(ids)[-1]
+        p = P.filtered_probs(row, 0.8)
+        c = np.cumsum(p)
+        u = P.uniform_from_counter(101, k)
+        assert c[t] - p[t] - 1e-4 <= u <= c[t] + 1e-4
+        ids.append(t)
+
+
+def test_preemption_does_not_change_the_outputs():
+    from railgun_b200.engine.engine import Engine
+    from railgun_b200.engine.request import SamplingParams
+    cfg, _, page = helpers.TINY["A"]
+    prompts = helpers.prompts(cfg["vocab_size"], [30, 28, 25], seed=17)
+    params = [SamplingParams(max_new_tokens=40, temperature=0.7 if i == 1 else 0.0, seed=5) for i in range(3)]
+    roomy = Engine(helpers.model_dir("A"), dtype="float32", block_size=page, num_gpu_blocks=64, max_num_seqs=4,
+                   max_model_len=256).generate(prompts, params)
+    tight_engine = Engine(helpers.model_dir("A"), dtype="float32", block_size=page, num_gpu_blocks=9, max_num_seqs=4,
+                          max_model_len=256)
+    tight = tight_engine.generate(prompts, params)
+    assert sum(o.num_preemptions for o in tight) >= 1 and sum(o.num_preemptions for o in roomy) == 0
+    for a, b in zip(roomy, tight):
+        assert a.token_ids == b.token_ids and b.finish_reason == "max_tokens"
+    tight_engine.runner.alloc.check()
+    # a request that cannot fit the pool even alone ends with an error, the others go on
+    eng = Engine(helpers.model_dir("A"), dtype="float32", block_size=page, num_gpu_blocks=3, max_num_seqs=4,
+                 max_model_len=256)
+    outs = eng.generate([prompts[0], [1, 2, 3] * 20], SamplingParams(max_new_tokens=4))
+    assert outs[0].finish_reason == "max_tokens"
+    assert outs[1].finish_reason == "error" and "out of KV cache blocks" in outs[1].error
+
+
+def test_engine_refuses_bad_requests():
+    from railgun_b200.engine.engine import Engine
+    from railgun_b200.engine.request import SamplingParams
+    from railgun_b200.engine.scheduler import SchedulerError
+    eng = Engine(helpers.model_dir("A"), dtype="float32", num_gpu_blocks=16, max_model_len=64)
+    with pytest.raises(ValueError):
+        eng.add_request([1, 256])                         # id outside the vocabulary
+    with pytest.raises(SchedulerError):
+        eng.add_request([1] * 60, SamplingParams(max_new_tokens=10))
+    with pytest.raises(ValueError):
+        eng.add_request([1], SamplingParams(temperature=-1.0))
+
+
+def test_generate_command(tmp_path):
+    cfg, _, page = helpers.TINY["A"]
+    plain = P.PlainLlama(helpers.model_dir("A"))
+    proc = subprocess.run(
+        [sys.executable, os.path.join(ROOT, "bin", "railgun"), "generate", "--model", str(helpers.model_dir("A")),
+         "--prompt-ids", "5,6,7;100,2", "--max-tokens", "6", "--dtype", "f32", "--show-token-ids",
+         "--num-gpu-blocks", "32"], capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    lines = proc.stdout.strip().splitlines()
+    assert lines[0] == "prompt ids: [5, 6, 7]"
+    assert lines[1] == ",".join(map(str, plain.greedy([5, 6, 7], 6)))
+    assert lines[3] == ",".join(map(str, plain.greedy([100, 2], 6)))
+    assert lines[-1].startswith("[stats] 12 tokens") and "tok/s" in lines[-1]
+
+
+def test_random_weights_command(tmp_path):
+    proc = subprocess.run(
+        [sys.executable, "-m", "railgun_b200", "random-weights", "--config",
+         str(helpers.model_dir("B") / "config.json"), "--seed", "2", "--out", str(tmp_path / "m"), "--std", "0.1"],
+        capture_output=True, text=True, timeout=600, cwd=ROOT)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    a = P.read_safetensors(tmp_path / "m" / "model.safetensors")
+    b = P.read_safetensors(helpers.model_dir("B") / "model.safetensors")
+    assert set(a) == set(b) and all(np.array_equal(a[k], b[k]) for k in a)

@@ -1,0 +1,295 @@
+"""Each kernel alone against a plain PyTorch reference of the same operation,
+at sizes other than the engine's (widths and vocabularies that are no power of
+two, head sizes in steps of 16, any number of heads and groups)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as P
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def rel_err(got, ref):
+    got, ref = got.double().cpu(), ref.double().cpu()
+    return float((got - ref).abs().max() / ref.abs().max().clamp_min(1e-30))
+
+
+TOL = {torch.float32: 2e-6, torch.bfloat16: 1e-2}
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embedding(dtype):
+    from railgun_b200 import ops
+    g = torch.Generator().manual_seed(0)
+    table = torch.randn(1000, 200, generator=g).to(dtype).to(DEV)
+    ids = torch.randint(0, 1000, (77,), generator=g, dtype=torch.int32).to(DEV)
+    out = ops.embedding(ids, table)
+    assert out.dtype == torch.float32 and torch.equal(out, table[ids.long()].float())
+
+
+@pytest.mark.parametrize("H", [96, 200, 2048, 5000])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_add_rmsnorm(H, dtype):
+    from railgun_b200 import ops
+    g = torch.Generator().manual_seed(H)
+    T = 13
+    resid = torch.randn(T, H, generator=g).to(DEV)
+    pend = torch.randn(T, H, generator=g).to(dtype).to(DEV)
+    w = (1 + 0.1 * torch.randn(H, generator=g)).to(DEV)
+    eps = 1e-5
+    ref_sum = resid.double() + pend.double()
+    ref = ref_sum / torch.sqrt((ref_sum ** 2).mean(-1, keepdim=True) + eps) * w.double()
+    r = resid.clone()
+    out = ops.add_rmsnorm(r, pend, w, eps, dtype)
+    assert out.dtype == dtype and rel_err(out, ref) < TOL[dtype]
+    assert rel_err(r, ref_sum) < 1e-7                         # the residual stream holds the 32-bit sum
+    # no pending: plain norm, residual untouched
+    r = resid.clone()
+    out = ops.add_rmsnorm(r, None, w, eps, dtype)
+    ref0 = resid.double() / torch.sqrt((resid.double() ** 2).mean(-1, keepdim=True) + eps) * w.double()
+    assert rel_err(out, ref0) < TOL[dtype] and torch.equal(r, resid)
+    # selected rows only, residual untouched
+    rows = torch.tensor([12, 0, 5, 5], dtype=torch.int32, device=DEV)
+    r = resid.clone()
+    out = ops.add_rmsnorm(r, pend, w, eps, dtype, rows=rows)
+    assert out.shape == (4, H) and rel_err(out, ref[rows.long()]) < TOL[dtype] and torch.equal(r, resid)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_residual_add_and_silu_mul(dtype):
+    from railgun_b200 import ops
+    g = torch.Generator().manual_seed(3)
+    resid = torch.randn(9, 176, generator=g).to(DEV)
+    pend = torch.randn(9, 176, generator=g).to(dtype).to(DEV)
+    r = resid.clone()
+    ops.residual_add(r, pend)
+    assert rel_err(r, resid.double() + pend.double()) < 1e-7
+    for I in (176, 1000):
+        gu = (3 * torch.randn(11, 2 * I, generator=g)).to(dtype).to(DEV)
+        out = ops.silu_mul(gu)
+        a, b = gu[:, :I].double(), gu[:, I:].double()
+        assert out.shape == (11, I) and rel_err(out, a / (1 + torch.exp(-a)) * b) < TOL[dtype]
+
+
+def make_paged_case(R, ctx_lens, q_lens, nh, nkv, d, page, dtype, seed, shuffle=True, spare_pages=5):
+    """Random cache contents behind shuffled block tables; the step's queries
+    are the last q_lens[r] positions of each request."""
+    g = torch.Generator().manual_seed(seed)
+    blocks = [-(-c // page) for c in ctx_lens]
+    NP = sum(blocks) + spare_pages
+    perm = torch.randperm(NP, generator=g).tolist() if shuffle else list(range(NP))
+    tables, k = [], 0
+    for b in blocks:
+        tables.append(perm[k:k + b])
+        k += b
+    MB = max(blocks)
+    bt = torch.zeros(R, MB, dtype=torch.int32)
+    for r, t in enumerate(tables):
+        bt[r, :len(t)] = torch.tensor(t, dtype=torch.int32)
+    kv = torch.randn(NP, 2, nkv, page, d, generator=g).to(dtype)
+    positions, req = [], []
+    for r in range(R):
+        positions += list(range(ctx_lens[r] - q_lens[r], ctx_lens[r]))
+        req += [r] * q_lens[r]
+    T = len(positions)
+    q = torch.randn(T, nh, d, generator=g).to(dtype)
+    return dict(kv=kv, bt=bt, tables=tables, positions=positions, req=req, q=q, T=T)
+
+
+def attention_reference(case, nh, nkv, d, page, window, scale):
+    kv, q = case["kv"].double(), case["q"].double()
+    out = torch.zeros(case["T"], nh, d, dtype=torch.float64)
+    for t, (p, r) in enumerate(zip(case["positions"], case["req"])):
+        lo = max(0, p - window + 1) if window else 0
+        idx = torch.arange(lo, p + 1)
+        pages = torch.tensor(case["tables"][r])[idx // page]
+        K = kv[pages, 0, :, idx % page, :]                      # [n, nkv, d]
+        V = kv[pages, 1, :, idx % page, :]
+        for h in range(nh):
+            kh = h // (nh // nkv)
+            s = (K[:, kh, :] @ q[t, h]) * scale
+            pr = torch.softmax(s, dim=0)
+            out[t, h] = pr @ V[:, kh, :]
+    return out.reshape(case["T"], nh * d)
+
+
+ATT_CASES = [
+    # nh, nkv, d, page, ctx_lens, q_lens, window
+    (4, 2, 16, 16, [5, 33, 17], [5, 1, 4], 0),
+    (6, 2, 48, 8, [70, 9, 130, 1], [1, 9, 7, 1], 0),
+    (5, 5, 64, 16, [300, 41], [1, 41], 0),
+    (8, 1, 128, 32, [257, 64, 100], [2, 1, 33], 0),
+    (3, 1, 256, 16, [50, 20], [3, 20], 0),
+    (4, 2, 80, 16, [200, 77, 150], [1, 30, 2], 24),
+    (2, 2, 112, 4, [37], [37], 0),
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("case_id", range(len(ATT_CASES)))
+def test_paged_attention_general(case_id, dtype):
+    from railgun_b200 import ops
+    nh, nkv, d, page, ctx, ql, window = ATT_CASES[case_id]
+    c = make_paged_case(len(ctx), ctx, ql, nh, nkv, d, page, dtype, seed=case_id)
+    scale = d ** -0.5
+    ref = attention_reference(c, nh, nkv, d, page, window, scale)
+    q = c["q"].reshape(c["T"], nh * d).contiguous().to(DEV)
+    out = ops.paged_attention_general(
+        q, nh * d, c["kv"].to(DEV), c["bt"].to(DEV), torch.tensor(c["req"], dtype=torch.int32, device=DEV),
+        torch.tensor(c["positions"], dtype=torch.int32, device=DEV), nh, nkv, d, window, scale)
+    assert rel_err(out, ref) < (5e-6 if dtype == torch.float32 else 1e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_finds_a_far_key_among_hundreds(dtype):
+    """One key far back is made to dominate; losing it (a wrong page, an
+    off-by-one at a page's edge) would change the output completely."""
+    from railgun_b200 import ops
+    nh, nkv, d, page = 4, 2, 64, 16
+    ctx = [700]
+    for needle in (0, 15, 16, 351, 699 - 1):
+        c = make_paged_case(1, ctx, [1], nh, nkv, d, page, dtype, seed=needle)
+        pg, off = c["tables"][0][needle // page], needle % page
+        c["kv"][pg, 0] *= 0.05                                  # quieten that page's other keys
+        c["kv"][pg, 0, :, off, :] = (c["q"][0, ::2, :] * 4).to(dtype)   # key = 4 x the query of heads 0 and 2
+        ref = attention_reference(c, nh, nkv, d, page, 0, d ** -0.5)
+        vneedle = c["kv"][pg, 1, :, off, :].double()
+        assert (ref.reshape(nh, d)[0] - vneedle[0]).abs().max() < 0.05       # the needle's value comes out
+        out = ops.paged_attention_general(
+            c["q"].reshape(1, nh * d).to(DEV), nh * d, c["kv"].to(DEV), c["bt"].to(DEV),
+            torch.zeros(1, dtype=torch.int32, device=DEV), torch.tensor([699], dtype=torch.int32, device=DEV),
+            nh, nkv, d, 0, d ** -0.5)
+        assert rel_err(out, ref) < (5e-6 if dtype == torch.float32 else 1e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,d,page", [(5, 1, 48, 8), (4, 2, 16, 16), (3, 3, 128, 32)])
+def test_rope_and_cache_write(nh, nkv, d, page, dtype):
+    from railgun_b200 import ops
+    from railgun_b200.parts.rope import rope_table
+    g = torch.Generator().manual_seed(d)
+    T, NP, max_pos = 21, 9, 300
+    scaling = dict(factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0, original_max_position_embeddings=64)
+    table = rope_table(d, 500000.0, scaling, max_pos)
+    inv = P.rope_inv_freq(d, 500000.0, dict(scaling, rope_type="llama3"))
+    ang = np.arange(max_pos)[:, None] * inv[None, :]
+    assert np.abs(table[:, :d // 2].double().numpy() - np.cos(ang)).max() < 1e-6      # the table is the plain angles
+    assert np.abs(table[:, d // 2:].double().numpy() - np.sin(ang)).max() < 1e-6
+    qkv = torch.randn(T, (nh + 2 * nkv) * d, generator=g).to(dtype)
+    positions = torch.randint(0, max_pos, (T,), generator=g, dtype=torch.int32)
+    slots = torch.randperm(NP * page, generator=g)[:T].to(torch.int32)
+    slots[3] = -1                                               # a token whose keys are not stored
+    kv = torch.zeros(NP, 2, nkv, page, d, dtype=dtype)
+    x = qkv.double().numpy().reshape(T, nh + 2 * nkv, d)
+    ref_q = P.rope(x[:, :nh], positions.numpy(), inv)
+    ref_k = P.rope(x[:, nh:nh + nkv], positions.numpy(), inv)
+    ref_v = x[:, nh + nkv:]
+    qkv_d, kv_d = qkv.to(DEV), kv.to(DEV)
+    ops.rope_cache_write(qkv_d, table.to(DEV), positions.to(DEV), slots.to(DEV), kv_d, nh, nkv, d, page)
+    got = qkv_d.cpu().double().numpy().reshape(T, nh + 2 * nkv, d)
+    tol = 2e-6 if dtype == torch.float32 else 1e-2
+    assert np.abs(got[:, :nh] - ref_q).max() / np.abs(ref_q).max() < tol
+    assert np.array_equal(got[:, nh + nkv:], ref_v)             # v untouched
+    kvc = kv_d.cpu().double().numpy()
+    written = np.zeros((NP, page), dtype=bool)
+    for t in range(T):
+        s = int(slots[t])
+        if s < 0:
+            continue
+        pg, off = divmod(s, page)
+        written[pg, off] = True
+        assert np.abs(kvc[pg, 0, :, off] - ref_k[t]).max() / np.abs(ref_k).max() < tol
+        assert np.array_equal(kvc[pg, 1, :, off], ref_v[t])
+    assert not kvc[~written].any()                              # nothing else was touched
+    # no table: no rotation, still written
+    qkv_d2, kv_d2 = qkv.to(DEV), kv.to(DEV)
+    ops.rope_cache_write(qkv_d2, None, positions.to(DEV), slots.to(DEV), kv_d2, nh, nkv, d, page)
+    assert torch.equal(qkv_d2.cpu(), qkv)
+    s0 = int(slots[0])
+    assert torch.equal(kv_d2.cpu()[s0 // page, 0, :, s0 % page].reshape(-1), qkv[0, nh * d:(nh + nkv) * d])
+
+
+@pytest.mark.parametrize("V", [1000, 128256])
+def test_argmax_with_ties(V):
+    from railgun_b200 import ops
+    g = torch.Generator().manual_seed(V)
+    logits = torch.randn(5, V, generator=g)
+    logits[1, 700] = logits[1, 33] = 9.0                        # a tie: the lowest index wins
+    logits[2, V - 1] = 11.0
+    logits[3, 0] = 12.0
+    out = ops.argmax(logits.to(DEV)).cpu()
+    ref = torch.tensor([int(np.argmax(r.numpy())) for r in logits], dtype=torch.int32)
+    assert torch.equal(out, ref) and out[1] == 33
+
+
+def _plain_interval(logits, temperature, top_k, top_p, tok):
+    p = P.filtered_probs(logits, temperature, top_k, top_p)
+    c = np.cumsum(p)
+    return (c[tok] - p[tok]) / c[-1], c[tok] / c[-1], p
+
+
+@pytest.mark.parametrize("V", [500, 128256])
+def test_temperature_top_k_top_p_sampling(V):
+    from railgun_b200 import ops
+    rng = np.random.default_rng(V)
+    rows = 64
+    logits = (rng.normal(size=(rows, V)) * 2.5).astype(np.float32)
+    temperature = rng.choice([0.0, 0.5, 0.8, 1.3], size=rows).astype(np.float32)
+    top_k = rng.choice([0, 1, 5, 50, V + 10], size=rows).astype(np.int32)
+    top_p = rng.choice([1.0, 0.9, 0.5, 0.2], size=rows).astype(np.float32)
+    seed = rng.integers(0, 2 ** 62, size=rows)
+    counter = rng.integers(0, 1000, size=rows)
+    dev = lambda a, dt: torch.tensor(a, dtype=dt, device=DEV)
+    args = (dev(logits, torch.float32), dev(temperature, torch.float32), dev(top_k, torch.int32),
+            dev(top_p, torch.float32), dev(seed, torch.int64), dev(counter, torch.int64))
+    out = ops.sample(*args).cpu().numpy()
+    again = ops.sample(*args).cpu().numpy()
+    assert np.array_equal(out, again)                           # same seed and counter: same token
+    exact = 0
+    for i in range(rows):
+        if temperature[i] == 0.0:
+            assert out[i] == int(np.argmax(logits[i]))
+            continue
+        lo, hi, p = _plain_interval(logits[i], float(temperature[i]), int(top_k[i]), float(top_p[i]), int(out[i]))
+        assert p[out[i]] > 0, f"row {i}: token {out[i]} is outside the kept set"
+        u = P.uniform_from_counter(int(seed[i]), int(counter[i]))
+        slack = 1e-4                                            # 32-bit sums over the vocabulary
+        assert lo - slack <= u <= hi + slack, f"row {i}: u={u} not in [{lo}, {hi}]"
+        exact += int(out[i] == P.sample(logits[i], float(temperature[i]), int(seed[i]), int(counter[i]),
+                                        int(top_k[i]), float(top_p[i])))
+    assert exact >= 0.9 * (temperature > 0).sum()
+    # a batch of one gives the same token as the row in the big batch
+    one = ops.sample(*(a[7:8].contiguous() for a in args)).cpu().numpy()
+    assert one[0] == out[7]
+
+
+def test_sampling_follows_the_distribution():
+    from railgun_b200 import ops
+    rng = np.random.default_rng(9)
+    V, n = 40, 4000
+    row = (rng.normal(size=V) * 2).astype(np.float32)
+    logits = torch.tensor(np.tile(row, (n, 1)), device=DEV)
+    t = torch.full((n,), 0.9, device=DEV)
+    out = ops.sample(logits, t, None, None, torch.full((n,), 5, dtype=torch.int64, device=DEV),
+                     torch.arange(n, dtype=torch.int64, device=DEV)).cpu().numpy()
+    freq = np.bincount(out, minlength=V) / n
+    assert np.abs(freq - P.filtered_probs(row, 0.9)).max() < 0.03
+
+
+def test_kernels_refuse_what_they_cannot_do():
+    from railgun_b200 import ops
+    with pytest.raises(ops.KernelError):
+        ops.embedding(torch.zeros(3, dtype=torch.int32), torch.zeros(4, 4))          # CPU tensors: no CPU path
+    with pytest.raises(ops.KernelError):
+        ops.silu_mul(torch.zeros(3, 4, dtype=torch.float16, device=DEV))             # unsupported dtype
+    with pytest.raises(ops.KernelError):
+        ops.add_rmsnorm(torch.zeros(2, 8, device=DEV), None, torch.ones(7, device=DEV), 1e-5, torch.float32)
+    kv = torch.zeros(2, 2, 1, 16, 272, device=DEV)
+    with pytest.raises(ops.KernelError):                                               # head size above the limit
+        ops.paged_attention_general(torch.zeros(1, 272, device=DEV), 272, kv, torch.zeros(1, 1, dtype=torch.int32, device=DEV),
+                                    torch.zeros(1, dtype=torch.int32, device=DEV),
+                                    torch.zeros(1, dtype=torch.int32, device=DEV), 1, 1, 272, 0, 1.0)
