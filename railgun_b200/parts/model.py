@@ -48,11 +48,9 @@ class TensorBank:
 
     def get(self, name: str, dtype=None):
         t = self._raw[name]
-        if dtype is None or t.dtype == dtype:
-            return t.to(self.device)
-        key = (name, dtype)
+        key = (name, dtype or t.dtype)
         if key not in self._cast:
-            self._cast[key] = t.to(device=self.device, dtype=dtype)
+            self._cast[key] = t.to(device=self.device, dtype=key[1])
         return self._cast[key]
 
     def drop(self, *names):

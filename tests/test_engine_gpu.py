@@ -15,15 +15,13 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def margin_ok(plain, prompt, out, min_margin):
-    """True while the plain model's top-2 margin along ``out`` stays above ``min_margin``."""
-    ids = list(prompt)
-    for t in out:
-        lg = np.sort(plain.forward(ids)[-1])
-        if lg[-1] - lg[-2] < min_margin:
-            return False
-        ids.append(t)
-    return True
+def assert_greedy_consistent(plain, prompt, out, tol):
+    """Teacher-forced: every generated token's plain logit is the row's
+    maximum, up to ``tol`` of the largest absolute logit."""
+    logits = plain.forward(list(prompt) + list(out))
+    for i, t in enumerate(out):
+        row = logits[len(prompt) - 1 + i]
+        assert row[t] >= row.max() - tol * np.abs(logits).max(), f"generated token {i} ({t}) is not the argmax"
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -39,14 +37,12 @@ def test_greedy_generation_matches_plain(name, dtype):
     eng = Engine(helpers.model_dir(name), dtype=dtype, block_size=page, num_gpu_blocks=64, max_num_seqs=8,
                  max_num_batched_tokens=64, max_prefill_chunk=32 if name == "B" else 0, max_model_len=256)
     outs = eng.generate(prompts, SamplingParams(max_new_tokens=n_new))
-    checked = 0
+    exact = 0
     for p, o in zip(prompts, outs):
         assert o.finish_reason == "max_tokens" and len(o.token_ids) == n_new
-        ref = plain.greedy(p, n_new)
-        if dtype == "float32" or margin_ok(plain, p, ref, 0.05 * 20):
-            assert o.token_ids == ref
-            checked += 1
-    assert checked >= 1
+        assert_greedy_consistent(plain, p, o.token_ids, 1e-4 if dtype == "float32" else 6e-2)
+        exact += int(o.token_ids == plain.greedy(p, n_new))
+    assert exact >= (len(prompts) if dtype == "float32" else 1)
     assert eng.stats()["num_free_blocks"] == 64 and not eng.has_unfinished()
 
 

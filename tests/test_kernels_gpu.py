@@ -204,7 +204,8 @@ def test_rope_and_cache_write(nh, nkv, d, page, dtype):
         written[pg, off] = True
         assert np.abs(kvc[pg, 0, :, off] - ref_k[t]).max() / np.abs(ref_k).max() < tol
         assert np.array_equal(kvc[pg, 1, :, off], ref_v[t])
-    assert not kvc[~written].any()                              # nothing else was touched
+    untouched = np.transpose(kvc, (0, 3, 1, 2, 4))[~written]    # [page, offset] first
+    assert not untouched.any()                                  # nothing else was touched
     # no table: no rotation, still written
     qkv_d2, kv_d2 = qkv.to(DEV), kv.to(DEV)
     ops.rope_cache_write(qkv_d2, None, positions.to(DEV), slots.to(DEV), kv_d2, nh, nkv, d, page)
