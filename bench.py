@@ -1,0 +1,274 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+The default run has the layer sizes of Llama 3.2 1B with random weights:
+decode at batch 8 with 1,024 tokens of context per request (the headline
+``value``, decoded tokens per second), the same through the Python entry point
+with host tokens in and out (``e2e``), decode at batch 1 and 64 (``points``),
+one 2,048-token prefill (``prefill``) and the decode step's memory roofline
+(``roofline``).  One JSON line is printed.  A step is one decode step.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+LLAMA_3_2_1B = dict(
+    architectures=["LlamaForCausalLM"], hidden_size=2048, num_attention_heads=32, num_key_value_heads=8,
+    head_dim=64, num_hidden_layers=16, intermediate_size=8192, vocab_size=128256, rope_theta=500000.0,
+    rope_scaling=dict(rope_type="llama3", factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                      original_max_position_embeddings=8192),
+    tie_word_embeddings=True, rms_norm_eps=1e-5, max_position_embeddings=8192, torch_dtype="bfloat16")
+CONTEXT = 1024            # tokens each decoding request holds
+PREFILL_TOKENS = 2048
+FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0)     # used only if MEASURED_PEAKS.json is absent
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            data = json.load(open(path))
+            return dict(hbm_gbs=float(data["hbm_gbs"]), bf16_tflops=float(data["bf16_tflops"]),
+                        bf16_tflops_sustained=float(data.get("bf16_tflops_sustained", data["bf16_tflops"]))), "measured"
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS, bf16_tflops_sustained=1400.0), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while timing runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index=0):
+        self.samples, self.proc = [], None
+        self.index = index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 6 and parts[0].isdigit():
+                self.samples.append(parts)
+
+    def __exit__(self, *exc):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        sm = sorted(int(s[0]) for s in self.samples)
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.samples)]
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": int(self.samples[0][1]), "reasons": reasons}
+
+
+def model_folder(cfg_dict, seed=0):
+    """The model folder with random weights (written once per machine into the temporary folder)."""
+    from railgun_b200.config.llama import LlamaConfig
+    from railgun_b200.weights.random_init import write_random_model
+    tag = f"rg_bench_L{cfg_dict['num_hidden_layers']}_H{cfg_dict['hidden_size']}_V{cfg_dict['vocab_size']}_s{seed}"
+    d = os.path.join(tempfile.gettempdir(), tag)
+    if not (os.path.exists(os.path.join(d, "model.safetensors")) and os.path.exists(os.path.join(d, "config.json"))):
+        tmp = d + f".tmp{os.getpid()}"
+        write_random_model(LlamaConfig.from_dict(cfg_dict), seed, tmp)
+        if os.path.exists(d):
+            import shutil
+            shutil.rmtree(d, ignore_errors=True)
+        os.replace(tmp, d)
+    return d
+
+
+def decode_bytes(cfg, batch, context, kv_bytes_per_token):
+    """Bytes a decode step has to read: every weight once, and the cache of the live requests."""
+    H, I, V, L = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"], cfg["num_hidden_layers"]
+    nh, nkv, d = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    per_layer = (nh + 2 * nkv) * d * H + nh * d * H + 3 * I * H + 2 * H
+    weights = (L * per_layer + V * H + H) * 2
+    if not cfg["tie_word_embeddings"]:
+        weights += V * H * 2
+    return weights + batch * context * kv_bytes_per_token
+
+
+def prefill_flops(cfg, T):
+    H, I, V, L = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"], cfg["num_hidden_layers"]
+    nh, nkv, d = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    linear = 2 * T * L * ((nh + 2 * nkv) * d * H + nh * d * H + 3 * I * H)
+    attn = L * nh * 2 * 2 * d * (T * (T + 1) // 2)          # causal: QK^T and PV
+    return linear + attn + 2 * V * H
+
+
+def run_ours(args):
+    import numpy as np
+    import torch
+    from railgun_b200.engine.batch import StepEntry
+    from railgun_b200.engine.engine import Engine
+    from railgun_b200.engine.request import SamplingParams
+    from railgun_b200 import ops
+
+    cfg = dict(LLAMA_3_2_1B)
+    full_layers = cfg["num_hidden_layers"]
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    pk, pk_src = peaks()
+    mdir = model_folder(cfg)
+    page = 16
+    pool_tokens = 64 * 8192                                # the cache pool: 64 sequences x 8,192 tokens
+    eng = Engine(mdir, dtype="bfloat16", block_size=page, num_gpu_blocks=pool_tokens // page, max_num_seqs=64,
+                 max_num_batched_tokens=8192, max_model_len=8192)
+    runner = eng.runner
+    V = cfg["vocab_size"]
+    rng = np.random.default_rng(0)
+    kv_per_token = runner.cache.bytes_per_token()
+    launches = ops.launch_counter()
+
+    def fill_contexts(batch, first_id):
+        """Prefill ``batch`` requests of CONTEXT tokens each; returns their ids and first sampled tokens."""
+        ids = list(range(first_id, first_id + batch))
+        toks = []
+        for rid in ids:
+            prompt = rng.integers(0, V, size=CONTEXT).tolist()
+            lg = runner.step([StepEntry(rid, prompt, [CONTEXT - 1])])
+            toks.append(int(ops.argmax(lg).item()))
+        return ids, toks
+
+    def time_decode(batch, steps, warmup, first_id):
+        ids, toks = fill_contexts(batch, first_id)
+        state = runner.decode_state(ids, toks, max_steps=steps + warmup)
+        for _ in range(warmup):
+            runner.decode_step(state)
+        torch.cuda.synchronize()
+        n0 = launches.value
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(steps):
+            runner.decode_step(state)
+        t1.record()
+        torch.cuda.synchronize()
+        ms = t0.elapsed_time(t1) / steps
+        n_launch = launches.value - n0
+        runner.decode_finish(state)
+        runner.end(ids)
+        return batch / ms * 1e3, ms, n_launch
+
+    with ClockSampler() as clocks:
+        tok_s, ms_step, n_launch = time_decode(8, args.steps, args.warmup, 1000)
+    clock_summary = clocks.summary()
+    points = {}
+    for b in (1, 64):
+        points[f"decode_b{b}"] = round(time_decode(b, max(10, args.steps // 2), args.warmup, 2000 + 100 * b)[0], 1)
+
+    # prefill of 2,048 tokens, logits at the last position
+    prompt = rng.integers(0, V, size=PREFILL_TOKENS).tolist()
+    pf_ms = []
+    for i in range(args.warmup + 5):
+        torch.cuda.synchronize()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        runner.step([StepEntry(5000 + i, prompt, [PREFILL_TOKENS - 1])])
+        t1.record()
+        torch.cuda.synchronize()
+        runner.end([5000 + i])
+        if i >= args.warmup:
+            pf_ms.append(t0.elapsed_time(t1))
+    pf = sorted(pf_ms)[len(pf_ms) // 2]
+    flops = prefill_flops(cfg, PREFILL_TOKENS)
+
+    # end to end through the entry point: host tokens in, host tokens out, every step
+    prompts = [rng.integers(0, V, size=CONTEXT).tolist() for _ in range(8)]
+    e2e_steps = args.steps
+    for p in prompts:
+        eng.add_request(p, SamplingParams(max_new_tokens=e2e_steps + args.warmup + 1))
+    while True:                                            # until all eight prompts are in the cache
+        out = eng.step()
+        if out is not None and len(out) == 8:
+            break
+    for _ in range(args.warmup):
+        eng.step()
+    torch.cuda.synchronize()
+    w0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        eng.step()
+    torch.cuda.synchronize()
+    e2e_ms = (time.perf_counter() - w0) * 1e3 / e2e_steps
+    h2d, d2h = eng.runner.last_h2d_bytes, 8 * 4
+
+    bytes_step = decode_bytes(cfg, 8, CONTEXT + args.warmup + args.steps // 2, kv_per_token)
+    achieved = bytes_step / (ms_step * 1e-3) / 1e9
+    line = {
+        "metric": "decode tok/s at batch 8 (Llama 3.2 1B sizes, 1,024-token contexts)",
+        "value": round(tok_s, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: seeded random weights and uniform random token ids",
+        "impl": "ours",
+        "config": {
+            "model": "Llama-3.2-1B sizes, random weights", "layers": cfg["num_hidden_layers"],
+            "layers_of_named_config": full_layers, "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
+            "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+            "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "global_batch": 8,
+            "seq_len": CONTEXT, "block_size": page, "kv_pool_tokens": pool_tokens, "parallelism": "none (1 GPU)",
+            "l2": "inputs larger than L2 (2.5 GB of weights per step)", "peaks": pk_src,
+        },
+        "e2e": {"value": round(8 / e2e_ms * 1e3, 1), "unit": "tok/s", "ms_per_step": round(e2e_ms, 4),
+                "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
+        "gpu_launches": int(n_launch),
+        "prefill": {"value": round(PREFILL_TOKENS / pf * 1e3, 1), "tokens": PREFILL_TOKENS, "ms": round(pf, 3),
+                    "frac": round(flops / (pf * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points,
+        "clocks": clock_summary,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the named configuration (0: all)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference is a Rust workspace on the candle crates: pip finds neither setup.py nor "
+                          "pyproject.toml, and cargo/rustc are not installed"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    args.warmup = max(3, args.warmup)
+    return run_ours(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

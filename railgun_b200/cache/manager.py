@@ -72,6 +72,8 @@ def _lib():
         lib.rg_cache_can_reserve.argtypes = [c_void_p, c_longlong, c_int, c_int]
         lib.rg_cache_table.argtypes = [c_void_p, c_longlong, c_int, c_void_p, c_int]
         lib.rg_cache_free_pages.argtypes = [c_void_p, c_int]
+        lib.rg_cache_pack_decode.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+        lib.rg_cache_advance.argtypes = [c_void_p, c_void_p, c_int, c_int]
         for name in ("free_slots", "num_requests", "check"):
             getattr(lib, f"rg_cache_{name}").argtypes = [c_void_p]
         lib.rg_sched_create.restype = c_void_p
@@ -178,6 +180,19 @@ class PageAllocator:
             self._buf = np.empty(max(n, 2 * self._buf.size), dtype=np.int32)
             n = self._lib.rg_cache_table(self._h, req_id, group, self._buf.ctypes.data, self._buf.size)
         return self._buf[:n].copy()
+
+    def pack_decode(self, ids: np.ndarray, B: int, MB: int, out: np.ndarray) -> None:
+        """Reserve one more token for each request in ``ids`` (int64) and write
+        the decode step's positions, slots and block tables into ``out``
+        (int32; layout in csrc/host/runtime.cpp, rg_cache_pack_decode)."""
+        code = self._lib.rg_cache_pack_decode(self._h, ids.ctypes.data, ids.size, B, MB, out.ctypes.data)
+        if code:
+            self._raise(code, "pack_decode")
+
+    def advance(self, ids: np.ndarray, n: int = 1) -> None:
+        code = self._lib.rg_cache_advance(self._h, ids.ctypes.data, ids.size, n)
+        if code:
+            self._raise(code, "advance")
 
     def free_pages(self, group: int = 0) -> int:
         return self._lib.rg_cache_free_pages(self._h, group)

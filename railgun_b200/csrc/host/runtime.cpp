@@ -46,6 +46,63 @@ int rg_cache_table(void* h, long long id, int group, int* out, int cap) {
     if (n && cap > 0) std::memcpy(out, t.data(), sizeof(int) * (size_t)(n < cap ? n : cap));
     return n;
 }
+// Packs a pure-decode step (one new token per request) for `R` requests into `out`, laid out for a static
+// batch of `B` rows and block tables `MB` wide:
+//   positions[B] | context_lens[B] | start_pos[B] | state_slots[B] | per group: slots[B] | per group: table[B*MB]
+// Rows R..B-1 are padding: position 0, context 1, slot -1 (nothing is written), table of zeros.
+// Pages for the new token are reserved here.  Returns 0, or a negative status (nothing half-reserved matters:
+// a failed request keeps what it had).
+int rg_cache_pack_decode(void* h, const long long* ids, int R, int B, int MB, int* out) {
+    try {
+        CacheManager* c = (CacheManager*)h;
+        const int G = c->num_groups();
+        int* positions = out;
+        int* context = out + B;
+        int* start = out + 2 * B;
+        int* slots_state = out + 3 * B;
+        int* slot_map = out + 4 * B;                       // G blocks of B
+        int* tables = out + (4 + G) * B;                   // G blocks of B*MB
+        std::memset(out, 0, sizeof(int) * ((size_t)(4 + G) * B + (size_t)G * B * MB));
+        for (int b = R; b < B; ++b) {
+            context[b] = 1;
+            for (int g = 0; g < G; ++g) slot_map[g * B + b] = -1;
+        }
+        for (int b = 0; b < R; ++b) {
+            const CacheRequest* r = c->find(ids[b]);
+            if (!r) return CACHE_UNKNOWN_REQUEST;
+            const int pos = r->num_computed;
+            const int st = c->reserve(ids[b], pos + 1);
+            if (st != CACHE_OK) return st;
+            r = c->find(ids[b]);
+            positions[b] = pos;
+            context[b] = pos + 1;
+            start[b] = pos;
+            slots_state[b] = r->slot;
+            for (int g = 0; g < G; ++g) {
+                const std::vector<int>& t = r->tables[g];
+                const int ps = c->group(g).page_size;
+                if ((int)t.size() > MB) return CACHE_BAD_ARGUMENT;
+                int* row = tables + ((size_t)g * B + b) * MB;
+                for (size_t i = 0; i < t.size(); ++i) row[i] = t[i] < 0 ? 0 : t[i];
+                slot_map[g * B + b] = t[pos / ps] * ps + pos % ps;
+            }
+        }
+        return CACHE_OK;
+    } catch (...) { return CACHE_CORRUPT; }
+}
+// Every listed request now holds `n` more tokens.
+int rg_cache_advance(void* h, const long long* ids, int R, int n) {
+    try {
+        CacheManager* c = (CacheManager*)h;
+        for (int b = 0; b < R; ++b) {
+            const CacheRequest* r = c->find(ids[b]);
+            if (!r) return CACHE_UNKNOWN_REQUEST;
+            const int st = c->commit(ids[b], r->num_computed + n);
+            if (st != CACHE_OK) return st;
+        }
+        return CACHE_OK;
+    } catch (...) { return CACHE_CORRUPT; }
+}
 int rg_cache_free_pages(void* h, int group) { return ((CacheManager*)h)->free_pages(group); }
 int rg_cache_free_slots(void* h) { return ((CacheManager*)h)->free_slots(); }
 int rg_cache_num_requests(void* h) { return ((CacheManager*)h)->num_requests(); }

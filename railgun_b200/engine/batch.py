@@ -52,6 +52,8 @@ class StepBatch:
     host_start_pos: np.ndarray | None = None
     host_state_slots: np.ndarray | None = None
     request_ids: list = field(default_factory=list)
+    h2d_bytes: int = 0
+    decode_only: bool = False        # every request brings exactly one token
 
 
 def build_step_batch(entries, alloc, page_sizes, vocab_size: int, max_position: int, device,
@@ -144,5 +146,6 @@ def build_step_batch(entries, alloc, page_sizes, vocab_size: int, max_position: 
         slot_mapping=[d(8 + 2 * g) for g in range(G)],
         block_table=[d(9 + 2 * g).view(R, max_blocks[g]) for g in range(G)],
         err_flag=err_flag, host_cu_seqlens=cu, host_start_pos=start_arr, host_state_slots=slots,
-        request_ids=[e.request_id for e in entries],
+        request_ids=[e.request_id for e in entries], h2d_bytes=int(offs[-1]) * 4,
+        decode_only=bool(counts.max() == 1),
     )

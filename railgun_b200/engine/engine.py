@@ -60,8 +60,11 @@ class Engine:
         if logits is None:
             self.scheduler.update([], [])
             return []
-        tokens = self.sampler.sample(logits, [self._params[r] for r in wanted],
-                                     [self.scheduler.num_generated(r) for r in wanted])
+        params = [self._params[r] for r in wanted]
+        if self.runner.last_greedy is not None and all(p.temperature == 0.0 for p in params):
+            tokens = self.runner.last_greedy.cpu().numpy()      # the decode graph already took the argmax
+        else:
+            tokens = self.sampler.sample(logits, params, [self.scheduler.num_generated(r) for r in wanted])
         self.scheduler.update(wanted, tokens)
         return list(zip(wanted, tokens.tolist()))
 

@@ -9,6 +9,7 @@ crates/vllm-models/src/llama/architecture.rs:141-156).
 """
 from __future__ import annotations
 
+import numpy as np
 import torch
 
 from ..cache.manager import CacheManager
@@ -17,7 +18,9 @@ from ..parts.base import CacheView
 from ..parts.model import DecoderModel, TensorBank, expected_tensors
 from ..parts.spec import BuildEnv
 from ..weights.loader import load_weights
-from .batch import StepEntry, build_step_batch
+from .. import ops
+from ..cache.manager import CacheError
+from .batch import BatchError, StepBatch, StepEntry, build_step_batch
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
            "f32": torch.float32}
@@ -62,15 +65,76 @@ def build_model(model_dir, dtype, device, spec_override=None):
     return arch, cfg, model
 
 
+_BATCH_BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256, 384, 512)
+
+
+def _bucket(n: int, buckets) -> int:
+    for b in buckets:
+        if n <= b:
+            return b
+    return n
+
+
+class StaticDecodeBatch:
+    """Device buffers of fixed address for decode steps of up to ``B`` requests
+    whose contexts stay within ``MB`` pages, with the pinned host buffer that
+    is copied into them in one transfer.  A graph captured over these buffers
+    can be replayed for any such step.  Layout (int32): token ids | positions |
+    context lengths | start positions | state slots | per group slot mapping |
+    per group block table [B, MB]."""
+
+    def __init__(self, runner, B: int, MB: int):
+        dev = runner.device
+        G = len(runner.page_sizes)
+        self.B, self.MB, self.G = B, MB, G
+        n_ints = (5 + G) * B + G * B * MB
+        self.host = torch.zeros(n_ints, dtype=torch.int32, pin_memory=True)
+        self.host_np = self.host.numpy()
+        self.dev = torch.zeros(n_ints, dtype=torch.int32, device=dev)
+        seg = lambda i: self.dev[i * B:(i + 1) * B]
+        ar = torch.arange(B + 1, dtype=torch.int32, device=dev)
+        tables_off = (5 + G) * B
+        self.batch = StepBatch(
+            num_tokens=B, num_requests=B, num_wanted=B, max_query_len=1,
+            max_context_len=MB * (runner.page_sizes[0] if G else 1),
+            token_ids=seg(0), positions=seg(1), req_of_token=ar[:B], want_rows=ar[:B], cu_seqlens=ar,
+            context_lens=seg(2), start_pos=seg(3), state_slots=seg(4),
+            slot_mapping=[seg(5 + g) for g in range(G)],
+            block_table=[self.dev[tables_off + g * B * MB:tables_off + (g + 1) * B * MB].view(B, MB)
+                         for g in range(G)],
+            err_flag=runner.err_flag, decode_only=True)
+        self.step_graph = None
+
+    def upload(self) -> int:
+        self.dev.copy_(self.host, non_blocking=True)
+        return self.host.numel() * 4
+
+
+class CapturedStep:
+    def __init__(self, graph, logits, sampled, launches):
+        self.graph, self.logits, self.sampled, self.launches = graph, logits, sampled, launches
+
+
+class DecodeState:
+    """Several decode steps in a row on the device for a fixed set of requests."""
+
+    def __init__(self, ids, static, captured, out_tokens, step_counter, max_steps):
+        self.ids, self.static, self.captured = ids, static, captured
+        self.out_tokens, self.step_counter, self.max_steps = out_tokens, step_counter, max_steps
+        self.steps_done = 0
+
+
 class ModelRunner:
     """A model on one GPU with its cache.
 
     ``max_tokens``: tokens the cache pool holds; ``max_requests``: requests
     live at a time; ``page_size``: tokens per page (the reference's
-    ``--block-size``, default 16, crates/vllm-scheduler/src/scheduler.rs:53)."""
+    ``--block-size``, default 16, crates/vllm-scheduler/src/scheduler.rs:53).
+    ``use_graphs``: steps in which every request brings exactly one token and
+    wants its logits are replayed from a captured CUDA graph."""
 
     def __init__(self, model_dir, dtype="bfloat16", device="cuda:0", page_size: int = 16,
-                 max_tokens: int = 16384, max_requests: int = 64, spec_override=None):
+                 max_tokens: int = 16384, max_requests: int = 64, spec_override=None, use_graphs: bool = True):
         if not torch.cuda.is_available():
             raise RuntimeError("railgun_b200 runs on a CUDA device only; none is available")
         self.device = torch.device(device)
@@ -86,17 +150,32 @@ class ModelRunner:
         self.views = _CacheViews(self.cache)
         self.page_sizes = [g.page_size for g in self.cache.groups]
         self.err_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
+        # graphs need every part to work from device-side descriptions only; parts with state of their own
+        # that plan on the host (none of the built-in ones) switch them off
+        self.use_graphs = bool(use_graphs) and not self.cache.state and len(self.page_sizes) >= 1
+        self._static: dict = {}
+        self._graph_pool = None
+        self._ctx_hint = 0
+        self.last_h2d_bytes = 0
+        self.last_greedy = None
 
     @property
     def alloc(self):
         return self.cache.alloc
 
+    # ---- the step function -----------------------------------------------------------------------
     def step(self, entries) -> torch.Tensor | None:
         """Run one batch; float32 logits [wanted, vocab] in the order of the
-        entries and of each entry's ``want``, or None if nothing is wanted."""
+        entries and of each entry's ``want``, or None if nothing is wanted.
+        The result may be a view of a buffer the next step overwrites."""
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
+        self.last_greedy = None
+        if self.use_graphs and entries and all(
+                len(e.tokens) == 1 and list(e.want) == [0] and self.alloc.has(e.request_id) for e in entries):
+            return self._step_decode_graph(entries)
         batch = build_step_batch(entries, self.alloc, self.page_sizes, self.model.vocab_size,
                                  self.model.spec.max_position, self.device, self.err_flag)
+        self.last_h2d_bytes = batch.h2d_bytes
         logits = self.model.forward(batch, self.views)
         for e, start in zip(entries, batch.host_start_pos):
             self.alloc.commit(e.request_id, int(start) + len(e.tokens))
@@ -112,3 +191,120 @@ class ModelRunner:
         if int(self.err_flag.item()):
             self.err_flag.zero_()
             raise RuntimeError("a kernel met a position outside its table")
+
+    # ---- decode steps from captured graphs -----------------------------------------------------------
+    def _static_for(self, n_requests: int, max_context: int) -> StaticDecodeBatch:
+        B = _bucket(n_requests, _BATCH_BUCKETS)
+        page = self.page_sizes[0]
+        ctx_bucket = 1024
+        while ctx_bucket < max_context:
+            ctx_bucket *= 2
+        key = (B, -(-ctx_bucket // page))
+        if key not in self._static:
+            self._static[key] = StaticDecodeBatch(self, *key)
+        return self._static[key]
+
+    def _capture(self, static: StaticDecodeBatch, loop=None) -> CapturedStep:
+        """Capture one decode step over the static buffers: forward, greedy
+        tokens and, with ``loop`` = (out_tokens, step_counter), the feedback of
+        those tokens so that the next replay is the next step."""
+        counter = ops.launch_counter()
+
+        def body():
+            logits = self.model.forward(static.batch, self.views)
+            sampled = ops.argmax(logits)
+            if loop is not None:
+                b = static.batch
+                ops.decode_advance(b.token_ids, sampled, b.positions, b.context_lens, b.start_pos,
+                                   b.slot_mapping[0], b.block_table[0], self.page_sizes[0], loop[0], loop[1])
+            return logits, sampled
+
+        # a first run outside capture, so that libraries set themselves up before it
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            saved = static.dev.clone()
+            body()
+            static.dev.copy_(saved)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        if self._graph_pool is None:
+            self._graph_pool = torch.cuda.graph_pool_handle()
+        graph = torch.cuda.CUDAGraph()
+        n0 = counter.value
+        with torch.cuda.graph(graph, pool=self._graph_pool):
+            logits, sampled = body()
+        launches = counter.value - n0
+        counter.value = n0
+        return CapturedStep(graph, logits, sampled, launches)
+
+    def _step_decode_graph(self, entries) -> torch.Tensor:
+        R = len(entries)
+        ids = np.fromiter((e.request_id for e in entries), dtype=np.int64, count=R)
+        tokens = np.fromiter((e.tokens[0] for e in entries), dtype=np.int32, count=R)
+        if len(set(ids.tolist())) != R:
+            raise BatchError("a request appears twice in one step")
+        if tokens.min() < 0 or tokens.max() >= self.model.vocab_size:
+            raise BatchError(f"token ids must be in [0, {self.model.vocab_size})")
+        ctx = max(self._ctx_hint + 1, 1)
+        while True:
+            static = self._static_for(R, ctx)
+            try:
+                self.alloc.pack_decode(ids, static.B, static.MB, static.host_np[static.B:])
+                break
+            except CacheError as e:
+                if "bad argument" in str(e) and ctx < self.model.spec.max_position:
+                    ctx = min(2 * max(ctx, 1024), self.model.spec.max_position)
+                    continue
+                raise
+        B = static.B
+        self._ctx_hint = int(static.host_np[2 * B:2 * B + R].max())
+        if self._ctx_hint > self.model.spec.max_position:
+            raise BatchError(f"position {self._ctx_hint - 1} is beyond the model's max_position_embeddings "
+                             f"{self.model.spec.max_position}")
+        static.host_np[:R] = tokens
+        static.host_np[R:B] = 0
+        self.last_h2d_bytes = static.upload()
+        if static.step_graph is None:
+            static.step_graph = self._capture(static)
+        cap = static.step_graph
+        cap.graph.replay()
+        ops.launch_counter().value += cap.launches
+        self.alloc.advance(ids, 1)
+        self.last_greedy = cap.sampled[:R]
+        return cap.logits[:R]
+
+    def decode_state(self, request_ids, first_tokens, max_steps: int) -> DecodeState:
+        """Prepare ``max_steps`` decode steps that run on the device without
+        the host in between, for requests already in the cache; their pages
+        are reserved now.  Greedy sampling."""
+        ids = np.asarray(request_ids, dtype=np.int64)
+        R = len(ids)
+        ctx = [self.alloc.num_computed(int(r)) for r in ids]
+        if max(ctx) + max_steps > self.model.spec.max_position:
+            raise BatchError("decode_state: the steps would run beyond max_position_embeddings")
+        for r, c in zip(ids, ctx):
+            self.alloc.reserve(int(r), c + max_steps)
+        static = self._static_for(R, max(ctx) + max_steps)
+        self.alloc.pack_decode(ids, static.B, static.MB, static.host_np[static.B:])
+        static.host_np[:R] = np.asarray(first_tokens, dtype=np.int32)
+        static.host_np[R:static.B] = 0
+        static.upload()
+        out_tokens = torch.zeros((max_steps, static.B), dtype=torch.int32, device=self.device)
+        step_counter = torch.zeros(1, dtype=torch.int32, device=self.device)
+        cap = self._capture(static, loop=(out_tokens, step_counter))
+        step_counter.zero_()
+        return DecodeState(ids, static, cap, out_tokens, step_counter, max_steps)
+
+    def decode_step(self, state: DecodeState) -> None:
+        if state.steps_done >= state.max_steps:
+            raise RuntimeError("decode_state: no reserved steps are left")
+        state.captured.graph.replay()
+        ops.launch_counter().value += state.captured.launches
+        state.steps_done += 1
+
+    def decode_finish(self, state: DecodeState) -> np.ndarray:
+        """Tell the cache what the device did; returns the generated tokens [steps, requests]."""
+        self.alloc.advance(state.ids, state.steps_done)
+        done, state.steps_done, state.max_steps = state.steps_done, 0, 0
+        return state.out_tokens[:done, :len(state.ids)].cpu().numpy()
