@@ -228,11 +228,9 @@ class ModelRunner:
             static.dev.copy_(saved)
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
-        if self._graph_pool is None:
-            self._graph_pool = torch.cuda.graph_pool_handle()
         graph = torch.cuda.CUDAGraph()
         n0 = counter.value
-        with torch.cuda.graph(graph, pool=self._graph_pool):
+        with torch.cuda.graph(graph):
             logits, sampled = body()
         launches = counter.value - n0
         counter.value = n0
