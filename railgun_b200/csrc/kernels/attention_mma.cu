@@ -1,0 +1,525 @@
+// Tensor-core attention over the paged cache, bfloat16 storage, 32-bit softmax
+// and accumulation: a flash-style kernel for portions of prompts and a split
+// kernel with its reduction for single decoded tokens.
+//
+// Both read K and V only through block tables (the step's own keys are
+// written before they run) and mask by absolute position, so the result for a
+// position does not depend on how the tokens were cut into steps.
+//
+//   s_j = scale * q.k_j ; m = max_j s_j ; p_j = exp(s_j - m) ; out = sum p_j v_j / sum p_j
+//   kv_head = head / (nh / nkv)
+// (crates/vllm-cuda/src/kernels/paged_attention.cu:40,66-69,103-107).  The
+// split kernel is the counterpart of the reference's partition + reduce pair:
+// per partition an unnormalised output with its max and sum, then
+// out = sum_p e^{m_p - M} o_p / sum_p e^{m_p - M} l_p
+// (crates/vllm-cuda/src/kernels/paged_attention_v2_partition.cu:60-107,
+// crates/vllm-cuda/src/kernels/paged_attention_v2_reduce.cu:50-90); the
+// reference's fixed 256-token partitions and 512-partition cap become a split
+// count chosen by the caller.  The prefill kernel has no counterpart: the
+// reference has no causal mask inside a portion of a prompt.
+//
+// Head sizes: any multiple of 16 up to 256, compiled in three register-size
+// classes (<= 64, <= 128, <= 256).  Any page size.  K/V tiles are gathered
+// row by row with cp.async (each key's page is looked up in the block table).
+#include "common.cuh"
+
+#define BN 64              // keys per tile
+#define NTHREADS 128       // 4 warps
+#define PAD 8              // bf16 elements of padding per shared-memory row: conflict-free ldmatrix for any d % 16 == 0
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+    const uint32_t d = smem_u32(dst);
+    const int n = valid ? 16 : 0;          // 0: the 16 bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src), "r"(n));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+// D[16x8] += A[16x16] B[16x8], bf16 operands, fp32 accumulators
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Gather BN keys (rows key0 .. key0+BN-1 of a request) of K and V for one kv head into shared memory.
+// Rows at or beyond key_end are zero-filled.  sK, sV: [BN][d + PAD].
+__device__ __forceinline__ void load_kv_tile(bf16* sK, bf16* sV, const bf16* __restrict__ kv_cache,
+                                             const int* __restrict__ bt, int key0, int key_end, int kvh, int nkv,
+                                             int d, int page_size) {
+    const int row = threadIdx.x >> 1, half = threadIdx.x & 1;     // 128 threads: 64 rows x 2
+    const int key = key0 + row;
+    const bool valid = key < key_end;
+    const bf16* ksrc = kv_cache;
+    const bf16* vsrc = kv_cache;
+    if (valid) {
+        const int page = bt[key / page_size], off = key % page_size;
+        const size_t page_elems = (size_t)2 * nkv * page_size * d;
+        ksrc = kv_cache + (size_t)page * page_elems + ((size_t)kvh * page_size + off) * d;
+        vsrc = ksrc + (size_t)nkv * page_size * d;
+    }
+    const int stride = d + PAD;
+    const int chunks = d >> 3;
+    for (int c = half; c < chunks; c += 2) {
+        cp_async16(sK + row * stride + c * 8, ksrc + c * 8, valid);
+        cp_async16(sV + row * stride + c * 8, vsrc + c * 8, valid);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Prefill: one CTA per (query tile of up to 64 consecutive positions of one request, head).
+// tiles: [NT][3] = first token row, number of rows, request index.
+// ---------------------------------------------------------------------------------------------------
+template <int DMAX>
+__global__ void __launch_bounds__(NTHREADS)
+prefill_attention_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
+                         const bf16* __restrict__ kv_cache, const int* __restrict__ block_table, int max_blocks,
+                         const int* __restrict__ tiles, const int* __restrict__ positions, int nh, int nkv, int d,
+                         int page_size, int window, float scale_log2) {
+    constexpr int KD = DMAX / 16;          // k-steps over the head dimension
+    constexpr int ND = DMAX / 8;           // n-tiles of the output
+    constexpr bool Q_IN_REGS = DMAX <= 128;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int stride = d + PAD;
+    bf16* sQ = reinterpret_cast<bf16*>(smem_raw);                 // [64][stride]
+    bf16* sKV = sQ + 64 * stride;                                 // 2 stages x (K [BN][stride], V [BN][stride])
+    const int stage_elems = 2 * BN * stride;
+
+    const int tile = blockIdx.x, h = blockIdx.y;
+    const int row0 = tiles[tile * 3 + 0], nrows = tiles[tile * 3 + 1], r = tiles[tile * 3 + 2];
+    const int kvh = h / (nh / nkv);
+    const int* bt = block_table + (size_t)r * max_blocks;
+    const int p0 = positions[row0];
+    const int hi = p0 + nrows - 1;                                 // last key any row of the tile attends
+    const int lo = window > 0 ? max(0, p0 - window + 1) : 0;
+    const int kt0 = lo / BN, kt1 = hi / BN;
+    const int d16 = d >> 4, d8 = d >> 3;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // Q tile -> shared memory (rows beyond nrows are zeros)
+    {
+        const int chunks = d8;
+        for (int idx = threadIdx.x; idx < 64 * chunks; idx += NTHREADS) {
+            const int row = idx / chunks, c = idx - row * chunks;
+            const bool valid = row < nrows;
+            const bf16* src = valid ? q + (size_t)(row0 + row) * q_stride + (size_t)h * d + c * 8 : q;
+            cp_async16(sQ + row * stride + c * 8, src, valid);
+        }
+    }
+    load_kv_tile(sKV, sKV + BN * stride, kv_cache, bt, kt0 * BN, hi + 1, kvh, nkv, d, page_size);
+    cp_async_commit();
+
+    uint32_t qf[Q_IN_REGS ? KD : 1][4];
+    float o[ND][4];
+#pragma unroll
+    for (int i = 0; i < ND; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;      // rows g and g + 8 of this warp's 16
+    const int g = lane >> 2, tq = lane & 3;
+    const int prow0 = p0 + warp * 16 + g, prow1 = prow0 + 8;       // absolute positions of the two rows
+    // ldmatrix source coordinates
+    const int a_row = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, a_col = (lane >> 4) * 8;
+    const int b_key = (lane & 7) + (lane >> 4) * 8, b_dim = ((lane >> 3) & 1) * 8;          // K as B operand
+    const int v_key = (lane & 7) + ((lane >> 3) & 1) * 8, v_dim = (lane >> 4) * 8;          // V as B operand (.trans)
+
+    for (int kt = kt0; kt <= kt1; ++kt) {
+        const int stage = (kt - kt0) & 1;
+        bf16* sK = sKV + stage * stage_elems;
+        bf16* sV = sK + BN * stride;
+        if (kt + 1 <= kt1) {
+            bf16* nK = sKV + (stage ^ 1) * stage_elems;
+            load_kv_tile(nK, nK + BN * stride, kv_cache, bt, (kt + 1) * BN, hi + 1, kvh, nkv, d, page_size);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        if (Q_IN_REGS && kt == kt0) {
+#pragma unroll
+            for (int kd = 0; kd < KD; ++kd)
+                if (kd < d16) ldmatrix_x4(qf[kd], sQ + a_row * stride + kd * 16 + a_col);
+        }
+        // this warp's rows attend nothing in this tile?  (all keys after its last row, or before its first row's window)
+        const int key_base = kt * BN;
+        const int wfirst = p0 + warp * 16, wlast = wfirst + 15;      // warp-uniform: every lane takes the same branch
+        const bool skip = key_base > wlast || (window > 0 && key_base + BN - 1 < wfirst - window + 1);
+        if (!skip) {
+            float s[BN / 8][4];
+#pragma unroll
+            for (int j = 0; j < BN / 8; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f; }
+#pragma unroll
+            for (int kd = 0; kd < KD; ++kd) {
+                if (kd < d16) {
+                    uint32_t a[4];
+                    if (Q_IN_REGS) { a[0] = qf[kd][0]; a[1] = qf[kd][1]; a[2] = qf[kd][2]; a[3] = qf[kd][3]; }
+                    else ldmatrix_x4(a, sQ + a_row * stride + kd * 16 + a_col);
+#pragma unroll
+                    for (int j2 = 0; j2 < BN / 16; ++j2) {
+                        uint32_t b[4];
+                        ldmatrix_x4(b, sK + (j2 * 16 + b_key) * stride + kd * 16 + b_dim);
+                        mma_bf16(s[2 * j2], a, b[0], b[1]);
+                        mma_bf16(s[2 * j2 + 1], a, b[2], b[3]);
+                    }
+                }
+            }
+            // mask by absolute position, scale into the log2 domain
+            float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < BN / 8; ++j) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int key = key_base + j * 8 + tq * 2 + (e & 1);
+                    const int prow = (e < 2) ? prow0 : prow1;
+                    const bool ok = key <= prow && (window <= 0 || key > prow - window);
+                    const float v = ok ? s[j][e] * scale_log2 : -INFINITY;
+                    s[j][e] = v;
+                    if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
+                }
+            }
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+            const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+            const float ms0 = mn0 == -INFINITY ? 0.f : mn0, ms1 = mn1 == -INFINITY ? 0.f : mn1;
+            const float al0 = exp2f(m0 - ms0), al1 = exp2f(m1 - ms1);
+            m0 = mn0; m1 = mn1;
+            float rs0 = 0.f, rs1 = 0.f;
+#pragma unroll
+            for (int j = 0; j < BN / 8; ++j) {
+                s[j][0] = exp2f(s[j][0] - ms0); s[j][1] = exp2f(s[j][1] - ms0);
+                s[j][2] = exp2f(s[j][2] - ms1); s[j][3] = exp2f(s[j][3] - ms1);
+                rs0 += s[j][0] + s[j][1];
+                rs1 += s[j][2] + s[j][3];
+            }
+            l0 = l0 * al0 + rs0;                                   // per-thread partial sums; reduced at the end
+            l1 = l1 * al1 + rs1;
+#pragma unroll
+            for (int i = 0; i < ND; ++i) { o[i][0] *= al0; o[i][1] *= al0; o[i][2] *= al1; o[i][3] *= al1; }
+            // O += P V
+#pragma unroll
+            for (int kk = 0; kk < BN / 16; ++kk) {
+                uint32_t a[4];
+                a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+                a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+                a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+                a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+                for (int n2 = 0; n2 < ND / 2; ++n2) {
+                    if (n2 < d16) {
+                        uint32_t b[4];
+                        ldmatrix_x4_trans(b, sV + (kk * 16 + v_key) * stride + n2 * 16 + v_dim);
+                        mma_bf16(o[2 * n2], a, b[0], b[1]);
+                        mma_bf16(o[2 * n2 + 1], a, b[2], b[3]);
+                    }
+                }
+            }
+        }
+        __syncthreads();                                            // the stage may be overwritten next iteration
+    }
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    const float inv0 = l0 > 0.f ? 1.f / l0 : 0.f, inv1 = l1 > 0.f ? 1.f / l1 : 0.f;
+    const int lr0 = warp * 16 + g, lr1 = lr0 + 8;
+#pragma unroll
+    for (int i = 0; i < ND; ++i) {
+        if (i < d8) {
+            const int col = i * 8 + tq * 2;
+            if (lr0 < nrows)
+                *reinterpret_cast<uint32_t*>(out + ((size_t)(row0 + lr0) * nh + h) * d + col) =
+                    pack_bf16(o[i][0] * inv0, o[i][1] * inv0);
+            if (lr1 < nrows)
+                *reinterpret_cast<uint32_t*>(out + ((size_t)(row0 + lr1) * nh + h) * d + col) =
+                    pack_bf16(o[i][2] * inv1, o[i][3] * inv1);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Decode: one CTA per (split of the context, kv head x tile of up to 16 query heads of its group, token).
+// The four warps take 16 keys each of every 64-key tile and are combined at the end; the CTA writes an
+// unnormalised partial output with its max (log2 domain) and sum into the scratch arrays
+//   part_o [n_tokens][nh][num_splits][d] (float), part_ml [n_tokens][nh][num_splits][2] (float).
+// ---------------------------------------------------------------------------------------------------
+#define DEC_STAGES 3
+
+template <int DMAX>
+__global__ void __launch_bounds__(NTHREADS)
+decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ kv_cache,
+                        const int* __restrict__ block_table, int max_blocks, const int* __restrict__ rows,
+                        const int* __restrict__ req_of_token, const int* __restrict__ positions,
+                        float* __restrict__ part_o, float* __restrict__ part_ml, int nh, int nkv, int d,
+                        int page_size, int window, float scale_log2, int num_splits, int head_tiles) {
+    constexpr int KD = DMAX / 16;
+    constexpr int ND = DMAX / 8;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int stride = d + PAD;
+    bf16* sQ = reinterpret_cast<bf16*>(smem_raw);                  // [16][stride]
+    bf16* sKV = sQ + 16 * stride;                                  // DEC_STAGES x (K, V)
+    const int stage_elems = 2 * BN * stride;
+
+    const int split = blockIdx.z;
+    const int kvh = blockIdx.y / head_tiles, ht = blockIdx.y - kvh * head_tiles;
+    const int ti = blockIdx.x;
+    const int t = rows ? rows[ti] : ti;
+    const int group = nh / nkv;
+    const int h0 = kvh * group + ht * 16;
+    const int nheads = min(16, group - ht * 16);
+    const int r = req_of_token[t];
+    const int pos = positions[t];
+    const int* bt = block_table + (size_t)r * max_blocks;
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int lo_al = (lo / BN) * BN;
+    const int n_keys = pos + 1 - lo_al;
+    const int per_split = ((n_keys + num_splits - 1) / num_splits + BN - 1) / BN * BN;
+    const int k_begin = lo_al + split * per_split;
+    const int k_end = min(pos + 1, k_begin + per_split);
+    const int d16 = d >> 4, d8 = d >> 3;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, tq = lane & 3;
+
+    if (k_begin >= k_end) {                                         // an empty split: zero weight in the reduction
+        for (int i = threadIdx.x; i < nheads; i += NTHREADS) {
+            float* ml = part_ml + (((size_t)ti * nh + h0 + i) * num_splits + split) * 2;
+            ml[0] = -INFINITY;
+            ml[1] = 0.f;
+        }
+        return;
+    }
+    const int n_tiles = (k_end - k_begin + BN - 1) / BN;
+
+    for (int idx = threadIdx.x; idx < 16 * d8; idx += NTHREADS) {
+        const int row = idx / d8, c = idx - row * d8;
+        const bool valid = row < nheads;
+        const bf16* src = valid ? q + (size_t)t * q_stride + (size_t)(h0 + row) * d + c * 8 : q;
+        cp_async16(sQ + row * stride + c * 8, src, valid);
+    }
+#pragma unroll
+    for (int st = 0; st < DEC_STAGES - 1; ++st) {
+        if (st < n_tiles) {
+            bf16* sK = sKV + st * stage_elems;
+            load_kv_tile(sK, sK + BN * stride, kv_cache, bt, k_begin + st * BN, k_end, kvh, nkv, d, page_size);
+        }
+        cp_async_commit();
+    }
+
+    float o[ND][4];
+#pragma unroll
+    for (int i = 0; i < ND; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    const int a_row = (lane & 7) + ((lane >> 3) & 1) * 8, a_col = (lane >> 4) * 8;
+    const int b_key = (lane & 7) + (lane >> 4) * 8, b_dim = ((lane >> 3) & 1) * 8;
+    const int v_key = (lane & 7) + ((lane >> 3) & 1) * 8, v_dim = (lane >> 4) * 8;
+
+    for (int it = 0; it < n_tiles; ++it) {
+        const int stage = it % DEC_STAGES;
+        bf16* sK = sKV + stage * stage_elems;
+        bf16* sV = sK + BN * stride;
+        {
+            const int nt = it + DEC_STAGES - 1;
+            if (nt < n_tiles) {
+                bf16* nK = sKV + (nt % DEC_STAGES) * stage_elems;
+                load_kv_tile(nK, nK + BN * stride, kv_cache, bt, k_begin + nt * BN, k_end, kvh, nkv, d, page_size);
+            }
+            cp_async_commit();
+            cp_async_wait<DEC_STAGES - 1>();
+        }
+        __syncthreads();
+        const int key_base = k_begin + it * BN + warp * 16;          // this warp's 16 keys
+        if (key_base < k_end && key_base + 15 >= lo) {
+            float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+            for (int kd = 0; kd < KD; ++kd) {
+                if (kd < d16) {
+                    uint32_t a[4], b[4];
+                    ldmatrix_x4(a, sQ + a_row * stride + kd * 16 + a_col);
+                    ldmatrix_x4(b, sK + (warp * 16 + b_key) * stride + kd * 16 + b_dim);
+                    mma_bf16(s[0], a, b[0], b[1]);
+                    mma_bf16(s[1], a, b[2], b[3]);
+                }
+            }
+            float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int key = key_base + j * 8 + tq * 2 + (e & 1);
+                    const bool ok = key < k_end && key >= lo;
+                    const float v = ok ? s[j][e] * scale_log2 : -INFINITY;
+                    s[j][e] = v;
+                    if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
+                }
+            }
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+            const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+            const float ms0 = mn0 == -INFINITY ? 0.f : mn0, ms1 = mn1 == -INFINITY ? 0.f : mn1;
+            const float al0 = exp2f(m0 - ms0), al1 = exp2f(m1 - ms1);
+            m0 = mn0; m1 = mn1;
+            float rs0 = 0.f, rs1 = 0.f;
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                s[j][0] = exp2f(s[j][0] - ms0); s[j][1] = exp2f(s[j][1] - ms0);
+                s[j][2] = exp2f(s[j][2] - ms1); s[j][3] = exp2f(s[j][3] - ms1);
+                rs0 += s[j][0] + s[j][1];
+                rs1 += s[j][2] + s[j][3];
+            }
+            l0 = l0 * al0 + rs0;
+            l1 = l1 * al1 + rs1;
+            uint32_t a[4];
+            a[0] = pack_bf16(s[0][0], s[0][1]);
+            a[1] = pack_bf16(s[0][2], s[0][3]);
+            a[2] = pack_bf16(s[1][0], s[1][1]);
+            a[3] = pack_bf16(s[1][2], s[1][3]);
+#pragma unroll
+            for (int n2 = 0; n2 < ND / 2; ++n2) {
+                if (n2 < d16) {
+                    o[2 * n2][0] *= al0; o[2 * n2][1] *= al0; o[2 * n2][2] *= al1; o[2 * n2][3] *= al1;
+                    o[2 * n2 + 1][0] *= al0; o[2 * n2 + 1][1] *= al0; o[2 * n2 + 1][2] *= al1; o[2 * n2 + 1][3] *= al1;
+                    uint32_t b[4];
+                    ldmatrix_x4_trans(b, sV + (warp * 16 + v_key) * stride + n2 * 16 + v_dim);
+                    mma_bf16(o[2 * n2], a, b[0], b[1]);
+                    mma_bf16(o[2 * n2 + 1], a, b[2], b[3]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+
+    // combine the four warps through shared memory (the K/V stages are free now)
+    float* cO = reinterpret_cast<float*>(sKV);                       // [4 warps][16 rows][d]
+    float* cML = cO + 4 * 16 * d;                                    // [4][16][2]
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < ND; ++i) {
+        if (i < d8) {
+            const int col = i * 8 + tq * 2;
+            cO[(warp * 16 + g) * d + col] = o[i][0];
+            cO[(warp * 16 + g) * d + col + 1] = o[i][1];
+            cO[(warp * 16 + g + 8) * d + col] = o[i][2];
+            cO[(warp * 16 + g + 8) * d + col + 1] = o[i][3];
+        }
+    }
+    if (tq == 0) {
+        cML[((warp * 16 + g) << 1)] = m0;      cML[((warp * 16 + g) << 1) + 1] = l0;
+        cML[((warp * 16 + g + 8) << 1)] = m1;  cML[((warp * 16 + g + 8) << 1) + 1] = l1;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < nheads * d; idx += NTHREADS) {
+        const int row = idx / d, col = idx - row * d;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, cML[(w * 16 + row) * 2]);
+        const float Ms = M == -INFINITY ? 0.f : M;
+        float acc = 0.f, L = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float sc = exp2f(cML[(w * 16 + row) * 2] - Ms);
+            acc += sc * cO[(w * 16 + row) * d + col];
+            L += sc * cML[(w * 16 + row) * 2 + 1];
+        }
+        const size_t base = ((size_t)ti * nh + h0 + row) * num_splits + split;
+        part_o[base * d + col] = acc;
+        if (col == 0) { part_ml[base * 2] = M; part_ml[base * 2 + 1] = L; }
+    }
+}
+
+// out[t, h, :] = sum_s 2^{m_s - M} o_s / sum_s 2^{m_s - M} l_s
+__global__ void decode_reduce_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                     bf16* __restrict__ out, const int* __restrict__ rows, int nh, int d,
+                                     int num_splits) {
+    const int ti = blockIdx.x, h = blockIdx.y;
+    const int t = rows ? rows[ti] : ti;
+    const size_t base = ((size_t)ti * nh + h) * num_splits;
+    float M = -INFINITY;
+    for (int s = 0; s < num_splits; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
+    const float Ms = M == -INFINITY ? 0.f : M;
+    float L = 0.f;
+    for (int s = 0; s < num_splits; ++s) L += exp2f(part_ml[(base + s) * 2] - Ms) * part_ml[(base + s) * 2 + 1];
+    const float inv = L > 0.f ? 1.f / L : 0.f;
+    for (int c = threadIdx.x; c < d; c += blockDim.x) {
+        float acc = 0.f;
+        for (int s = 0; s < num_splits; ++s) {
+            const float w = exp2f(part_ml[(base + s) * 2] - Ms);
+            if (w > 0.f) acc += w * part_o[(base + s) * d + c];
+        }
+        out[((size_t)t * nh + h) * d + c] = __float2bfloat16_rn(acc * inv);
+    }
+}
+
+static size_t prefill_smem(int d) { return (size_t)(64 + 2 * 2 * BN) * (d + PAD) * sizeof(bf16); }
+static size_t decode_smem(int d) {
+    const size_t stages = (size_t)(16 + DEC_STAGES * 2 * BN) * (d + PAD) * sizeof(bf16);
+    const size_t combine = (size_t)16 * (d + PAD) * sizeof(bf16) + (size_t)(4 * 16 * d + 4 * 16 * 2) * sizeof(float);
+    return stages > combine ? stages : combine;
+}
+
+template <typename K> static int allow_smem(K kernel, size_t bytes) {
+    if (bytes <= 48 * 1024) return 0;
+    return (int)cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+}
+
+extern "C" int rg_prefill_attention(const void* q, int q_stride, void* out, const void* kv_cache,
+                                    const int* block_table, int max_blocks, const int* tiles, int n_tiles,
+                                    const int* positions, int nh, int nkv, int d, int page_size, int window,
+                                    float scale, void* stream) {
+    if (n_tiles <= 0) return 0;
+    if (d % 16 || d < 16 || d > 256 || nh % nkv || nh > 65535) return RG_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    const float scale_log2 = scale * 1.4426950408889634f;
+    const size_t smem = prefill_smem(d);
+    dim3 grid(n_tiles, nh);
+#define RG_PREFILL(DM) { int e = allow_smem(prefill_attention_kernel<DM>, smem); if (e) return e; \
+    prefill_attention_kernel<DM><<<grid, NTHREADS, smem, s>>>((const bf16*)q, q_stride, (bf16*)out, \
+        (const bf16*)kv_cache, block_table, max_blocks, tiles, positions, nh, nkv, d, page_size, window, scale_log2); }
+    if (d <= 64) RG_PREFILL(64) else if (d <= 128) RG_PREFILL(128) else RG_PREFILL(256)
+#undef RG_PREFILL
+    return RG_LAUNCH_RESULT();
+}
+
+// Scratch the caller provides: part_o floats = n_tokens * nh * num_splits * d; part_ml = n_tokens * nh * num_splits * 2.
+extern "C" int rg_decode_attention(const void* q, int q_stride, void* out, const void* kv_cache,
+                                   const int* block_table, int max_blocks, const int* rows, int n_tokens,
+                                   const int* req_of_token, const int* positions, float* part_o, float* part_ml,
+                                   int nh, int nkv, int d, int page_size, int window, float scale, int num_splits,
+                                   void* stream) {
+    if (n_tokens <= 0) return 0;
+    if (d % 16 || d < 16 || d > 256 || nh % nkv || num_splits < 1) return RG_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    const float scale_log2 = scale * 1.4426950408889634f;
+    const size_t smem = decode_smem(d);
+    const int group = nh / nkv;
+    const int head_tiles = (group + 15) / 16;
+    if (num_splits > 65535 || nkv * head_tiles > 65535) return RG_ERR_UNSUPPORTED;
+    dim3 grid(n_tokens, nkv * head_tiles, num_splits);
+#define RG_DECODE(DM) { int e = allow_smem(decode_attention_kernel<DM>, smem); if (e) return e; \
+    decode_attention_kernel<DM><<<grid, NTHREADS, smem, s>>>((const bf16*)q, q_stride, (const bf16*)kv_cache, \
+        block_table, max_blocks, rows, req_of_token, positions, part_o, part_ml, nh, nkv, d, page_size, window, \
+        scale_log2, num_splits, head_tiles); }
+    if (d <= 64) RG_DECODE(64) else if (d <= 128) RG_DECODE(128) else RG_DECODE(256)
+#undef RG_DECODE
+    int e = (int)cudaGetLastError();
+    if (e) return e;
+    dim3 rgrid(n_tokens, nh);
+    decode_reduce_kernel<<<rgrid, d >= 128 ? 128 : 64, 0, s>>>(part_o, part_ml, (bf16*)out, rows, nh, d, num_splits);
+    return RG_LAUNCH_RESULT();
+}

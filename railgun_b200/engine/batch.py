@@ -17,6 +17,9 @@ import numpy as np
 import torch
 
 
+ATTENTION_TILE_ROWS = 64      # query rows per tile of the prefill attention kernel
+
+
 class BatchError(ValueError):
     """A step that cannot run: bad token ids, positions or requests."""
 
@@ -54,6 +57,12 @@ class StepBatch:
     request_ids: list = field(default_factory=list)
     h2d_bytes: int = 0
     decode_only: bool = False        # every request brings exactly one token
+    # how attention splits the step: requests with several tokens in tiles of up to 64 consecutive
+    # positions, [n, 3] = first row, rows, request; requests with one token as a list of rows
+    prefill_tiles: torch.Tensor | None = None
+    num_prefill_tiles: int = 0
+    decode_rows: torch.Tensor | None = None
+    num_decode_rows: int = 0
 
 
 def build_step_batch(entries, alloc, page_sizes, vocab_size: int, max_position: int, device,
@@ -106,9 +115,19 @@ def build_step_batch(entries, alloc, page_sizes, vocab_size: int, max_position: 
     tables = [[alloc.block_table(e.request_id, g) for e in entries] for g in range(G)]
     max_blocks = [max(1, max(len(t) for t in tables[g])) for g in range(G)]
 
+    tiles, dec_rows = [], []
+    off = 0
+    for i, c in enumerate(counts):
+        c = int(c)
+        if c == 1:
+            dec_rows.append(off)
+        else:
+            tiles += [(off + k, min(ATTENTION_TILE_ROWS, c - k), i) for k in range(0, c, ATTENTION_TILE_ROWS)]
+        off += c
     sizes = [T, T, T, W, R + 1, R, R, R]
     for g in range(G):
         sizes += [T, R * max_blocks[g]]
+    sizes += [3 * len(tiles), len(dec_rows)]
     offs = np.concatenate([[0], np.cumsum(sizes)])
     buf = torch.empty(int(offs[-1]), dtype=torch.int32, pin_memory=torch.cuda.is_available())
     host = buf.numpy()
@@ -136,6 +155,10 @@ def build_step_batch(entries, alloc, page_sizes, vocab_size: int, max_position: 
         page_of = bt[req, pos // ps]
         seg(8 + 2 * g)[:] = page_of * ps + pos % ps
         seg(9 + 2 * g)[:] = bt.reshape(-1)
+    if tiles:
+        seg(8 + 2 * G)[:] = np.asarray(tiles, dtype=np.int32).reshape(-1)
+    if dec_rows:
+        seg(9 + 2 * G)[:] = np.asarray(dec_rows, dtype=np.int32)
     dev = buf.to(device, non_blocking=True)
     d = lambda i: dev[int(offs[i]):int(offs[i + 1])]
     return StepBatch(
@@ -148,4 +171,6 @@ def build_step_batch(entries, alloc, page_sizes, vocab_size: int, max_position: 
         err_flag=err_flag, host_cu_seqlens=cu, host_start_pos=start_arr, host_state_slots=slots,
         request_ids=[e.request_id for e in entries], h2d_bytes=int(offs[-1]) * 4,
         decode_only=bool(counts.max() == 1),
+        prefill_tiles=d(8 + 2 * G).view(-1, 3) if tiles else None, num_prefill_tiles=len(tiles),
+        decode_rows=d(9 + 2 * G) if dec_rows else None, num_decode_rows=len(dec_rows),
     )

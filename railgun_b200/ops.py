@@ -191,6 +191,71 @@ def paged_attention_general(q: torch.Tensor, q_stride: int, kv_cache: torch.Tens
     return out
 
 
+def _check_paged(q, kv_cache, block_table, nkv, d):
+    if not q.is_cuda:
+        raise KernelError("q must be a CUDA tensor (there is no CPU path)")
+    if q.dtype != torch.bfloat16:
+        raise KernelError(f"the tensor-core attention kernels take bfloat16, got {q.dtype}")
+    _check(kv_cache, "kv_cache", q.dtype)
+    _check(block_table, "block_table", torch.int32)
+    page_size = kv_cache.shape[3]
+    if tuple(kv_cache.shape[1:]) != (2, nkv, page_size, d):
+        raise KernelError(f"kv cache shape {tuple(kv_cache.shape)} does not match heads {nkv} x {d}")
+    if d % 16 or not 16 <= d <= 256:
+        raise KernelError(f"the tensor-core attention kernels take head sizes 16, 32, ..., 256; got {d}")
+    return page_size
+
+
+def prefill_attention(q, q_stride: int, out, kv_cache, block_table, tiles, positions, nh: int, nkv: int, d: int,
+                      window: int, scale: float) -> None:
+    """Flash-style attention for requests that bring several tokens: ``tiles``
+    [n, 3] = (first row, rows <= 64, request index).  Writes the tiles' rows of
+    ``out`` [T, nh*d]."""
+    page_size = _check_paged(q, kv_cache, block_table, nkv, d)
+    _check(tiles, "tiles", torch.int32)
+    _check(positions, "positions", torch.int32)
+    _check(out, "out", q.dtype)
+    _ok(_fn("attention_mma", "rg_prefill_attention")(
+        _ptr(q), c_int(q_stride), _ptr(out), _ptr(kv_cache), _ptr(block_table), c_int(block_table.shape[1]),
+        _ptr(tiles), c_int(tiles.shape[0]), _ptr(positions), c_int(nh), c_int(nkv), c_int(d), c_int(page_size),
+        c_int(window or 0), c_float(scale), _stream()), "prefill_attention")
+
+
+def decode_splits(n_tokens: int, kv_tiles: int, max_context: int) -> int:
+    """How many parts each context is cut into: enough thread blocks to fill
+    the GPU (about 592 of this kernel are resident), at least 64 keys each."""
+    want = -(-592 // max(1, n_tokens * kv_tiles))
+    return max(1, min(want, -(-max_context // 64), 256))
+
+
+def decode_attention(q, q_stride: int, out, kv_cache, block_table, rows, n_tokens: int, req_of_token, positions,
+                     nh: int, nkv: int, d: int, window: int, scale: float, num_splits: int,
+                     scratch=None) -> None:
+    """Split attention for single tokens: token rows ``rows`` (None: rows
+    0..n_tokens-1) each attend their request's context.  Partial results go
+    through scratch memory (allocated here unless given) and are reduced into
+    ``out`` [T, nh*d]."""
+    page_size = _check_paged(q, kv_cache, block_table, nkv, d)
+    _check(req_of_token, "req_of_token", torch.int32)
+    _check(positions, "positions", torch.int32)
+    _check(out, "out", q.dtype)
+    if rows is not None:
+        _check(rows, "rows", torch.int32)
+    if scratch is None:
+        part_o = torch.empty((n_tokens, nh, num_splits, d), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((n_tokens, nh, num_splits, 2), dtype=torch.float32, device=q.device)
+    else:
+        part_o, part_ml = scratch
+        if part_o.numel() < n_tokens * nh * num_splits * d or part_ml.numel() < n_tokens * nh * num_splits * 2:
+            raise KernelError("decode_attention: the scratch buffers are too small")
+    _COUNTER.value += 1                      # the launcher runs two kernels: partial results, then the reduction
+    _ok(_fn("attention_mma", "rg_decode_attention")(
+        _ptr(q), c_int(q_stride), _ptr(out), _ptr(kv_cache), _ptr(block_table), c_int(block_table.shape[1]),
+        _ptr(rows), c_int(n_tokens), _ptr(req_of_token), _ptr(positions), _ptr(part_o), _ptr(part_ml),
+        c_int(nh), c_int(nkv), c_int(d), c_int(page_size), c_int(window or 0), c_float(scale),
+        c_int(num_splits), _stream()), "decode_attention")
+
+
 def argmax(logits: torch.Tensor) -> torch.Tensor:
     _check(logits, "logits", torch.float32)
     rows, V = logits.shape

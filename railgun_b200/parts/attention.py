@@ -73,10 +73,33 @@ class PagedAttention(Mixer):
         return ops.linear(out, self.w_o)
 
     def attend(self, qkv, batch, cache):
-        """Pick the attention kernel for this step's shape and precision."""
-        return ops.paged_attention_general(
-            qkv, qkv.shape[1], cache.kv, batch.block_table[cache.group], batch.req_of_token, batch.positions,
-            self.nh, self.nkv, self.d, self.window, self.scale)
+        """Pick the attention kernels for this step's shape and precision:
+        bfloat16 with a head size in steps of 16 runs on the tensor cores
+        (requests with several tokens through the flash-style kernel, single
+        tokens through the split kernel); everything else, and all of the
+        32-bit path, through the general kernel."""
+        nh, nkv, d = self.nh, self.nkv, self.d
+        table = batch.block_table[cache.group]
+        if qkv.dtype != torch.bfloat16 or d % 16:
+            return ops.paged_attention_general(qkv, qkv.shape[1], cache.kv, table, batch.req_of_token,
+                                               batch.positions, nh, nkv, d, self.window, self.scale)
+        out = torch.empty((qkv.shape[0], nh * d), dtype=qkv.dtype, device=qkv.device)
+        kv_tiles = nkv * (-(-(nh // nkv) // 16))
+        if batch.decode_only:
+            n = batch.num_tokens
+            ops.decode_attention(qkv, qkv.shape[1], out, cache.kv, table, None, n, batch.req_of_token,
+                                 batch.positions, nh, nkv, d, self.window, self.scale,
+                                 ops.decode_splits(n, kv_tiles, batch.max_context_len))
+            return out
+        if batch.num_prefill_tiles:
+            ops.prefill_attention(qkv, qkv.shape[1], out, cache.kv, table, batch.prefill_tiles, batch.positions,
+                                  nh, nkv, d, self.window, self.scale)
+        if batch.num_decode_rows:
+            n = batch.num_decode_rows
+            ops.decode_attention(qkv, qkv.shape[1], out, cache.kv, table, batch.decode_rows, n, batch.req_of_token,
+                                 batch.positions, nh, nkv, d, self.window, self.scale,
+                                 ops.decode_splits(n, kv_tiles, batch.max_context_len))
+        return out
 
 
 register_mixer("paged_attention", PagedAttention)

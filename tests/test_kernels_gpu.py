@@ -294,3 +294,107 @@ def test_kernels_refuse_what_they_cannot_do():
         ops.paged_attention_general(torch.zeros(1, 272, device=DEV), 272, kv, torch.zeros(1, 1, dtype=torch.int32, device=DEV),
                                     torch.zeros(1, dtype=torch.int32, device=DEV),
                                     torch.zeros(1, dtype=torch.int32, device=DEV), 1, 1, 272, 0, 1.0)
+
+
+# ---- the tensor-core attention kernels (bfloat16) -------------------------------------------------------
+
+MMA_CASES = ATT_CASES + [
+    # nh, nkv, d, page, ctx_lens, q_lens, window
+    (32, 8, 64, 16, [1024, 130, 64, 65], [1, 130, 64, 3], 0),       # the 1B model's shape; a prompt over three tiles
+    (40, 2, 32, 16, [150, 90], [150, 1], 0),                        # 20 heads per kv head: two head tiles
+    (6, 3, 96, 16, [500], [200], 64),                               # window shorter than a key tile span
+    (4, 4, 16, 1, [70, 3], [70, 3], 0),                             # a page per token
+    (2, 1, 160, 16, [333, 47], [77, 47], 100),
+    (16, 8, 128, 64, [2000, 1], [1, 1], 0),
+]
+
+
+def _tiles_of(q_lens):
+    tiles, off = [], 0
+    for r, n in enumerate(q_lens):
+        for k in range(0, n, 64):
+            tiles.append((off + k, min(64, n - k), r))
+        off += n
+    return torch.tensor(tiles, dtype=torch.int32, device=DEV)
+
+
+@pytest.mark.parametrize("case_id", range(len(MMA_CASES)))
+def test_prefill_attention_mma(case_id):
+    from railgun_b200 import ops
+    nh, nkv, d, page, ctx, ql, window = MMA_CASES[case_id]
+    c = make_paged_case(len(ctx), ctx, ql, nh, nkv, d, page, torch.bfloat16, seed=100 + case_id)
+    scale = d ** -0.5
+    ref = attention_reference(c, nh, nkv, d, page, window, scale)
+    # q sits inside a wider buffer, as in the fused qkv projection
+    wide = torch.zeros(c["T"], (nh + 2 * nkv) * d, dtype=torch.bfloat16)
+    wide[:, :nh * d] = c["q"].reshape(c["T"], nh * d)
+    out = torch.full((c["T"], nh * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.prefill_attention(wide.to(DEV), wide.shape[1], out, c["kv"].to(DEV), c["bt"].to(DEV), _tiles_of(ql),
+                          torch.tensor(c["positions"], dtype=torch.int32, device=DEV), nh, nkv, d, window, scale)
+    assert rel_err(out, ref) < 1e-2
+
+
+@pytest.mark.parametrize("splits", [1, 3, 8])
+@pytest.mark.parametrize("case_id", range(len(MMA_CASES)))
+def test_decode_attention_mma(case_id, splits):
+    """Every token row treated as a single token attending up to its own position."""
+    from railgun_b200 import ops
+    nh, nkv, d, page, ctx, ql, window = MMA_CASES[case_id]
+    c = make_paged_case(len(ctx), ctx, ql, nh, nkv, d, page, torch.bfloat16, seed=200 + case_id)
+    scale = d ** -0.5
+    ref = attention_reference(c, nh, nkv, d, page, window, scale)
+    T = c["T"]
+    q = c["q"].reshape(T, nh * d).contiguous().to(DEV)
+    out = torch.full((T, nh * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+    req = torch.tensor(c["req"], dtype=torch.int32, device=DEV)
+    pos = torch.tensor(c["positions"], dtype=torch.int32, device=DEV)
+    ops.decode_attention(q, nh * d, out, c["kv"].to(DEV), c["bt"].to(DEV), None, T, req, pos, nh, nkv, d, window,
+                         scale, splits)
+    assert rel_err(out, ref) < 1e-2
+    # a subset of rows, in another order, through the row list: the other rows stay untouched
+    if T >= 3:
+        rows = torch.tensor([T - 1, 0, T // 2], dtype=torch.int32, device=DEV)
+        out2 = torch.full((T, nh * d), 7.0, dtype=torch.bfloat16, device=DEV)
+        ops.decode_attention(q, nh * d, out2, c["kv"].to(DEV), c["bt"].to(DEV), rows, 3, req, pos, nh, nkv, d,
+                             window, scale, splits)
+        sel = rows.long().cpu()
+        assert rel_err(out2[sel], ref[sel]) < 1e-2
+        rest = torch.ones(T, dtype=torch.bool)
+        rest[sel] = False
+        assert (out2.cpu()[rest] == 7.0).all()
+
+
+@pytest.mark.parametrize("kernel", ["prefill", "decode"])
+def test_mma_attention_finds_a_far_key(kernel):
+    from railgun_b200 import ops
+    nh, nkv, d, page = 4, 2, 64, 16
+    for needle in (0, 15, 16, 63, 64, 351, 698):
+        c = make_paged_case(1, [700], [1], nh, nkv, d, page, torch.bfloat16, seed=needle)
+        pg, off = c["tables"][0][needle // page], needle % page
+        c["kv"][pg, 0] *= 0.05
+        c["kv"][pg, 0, :, off, :] = (c["q"][0, ::2, :] * 4).to(torch.bfloat16)
+        ref = attention_reference(c, nh, nkv, d, page, 0, d ** -0.5)
+        q = c["q"].reshape(1, nh * d).to(DEV)
+        out = torch.zeros(1, nh * d, dtype=torch.bfloat16, device=DEV)
+        pos = torch.tensor([699], dtype=torch.int32, device=DEV)
+        if kernel == "prefill":
+            ops.prefill_attention(q, nh * d, out, c["kv"].to(DEV), c["bt"].to(DEV),
+                                  torch.tensor([[0, 1, 0]], dtype=torch.int32, device=DEV), pos, nh, nkv, d, 0, d ** -0.5)
+        else:
+            ops.decode_attention(q, nh * d, out, c["kv"].to(DEV), c["bt"].to(DEV), None, 1,
+                                 torch.zeros(1, dtype=torch.int32, device=DEV), pos, nh, nkv, d, 0, d ** -0.5, 5)
+        assert rel_err(out, ref) < 1e-2
+
+
+def test_mma_attention_refuses_other_head_sizes_and_dtypes():
+    from railgun_b200 import ops
+    kv = torch.zeros(2, 2, 1, 16, 24, dtype=torch.bfloat16, device=DEV)
+    z = torch.zeros(1, dtype=torch.int32, device=DEV)
+    with pytest.raises(ops.KernelError):
+        ops.decode_attention(torch.zeros(1, 24, dtype=torch.bfloat16, device=DEV), 24,
+                             torch.zeros(1, 24, dtype=torch.bfloat16, device=DEV), kv, z.view(1, 1), None, 1, z, z,
+                             1, 1, 24, 0, 1.0, 1)
+    kv32 = torch.zeros(2, 2, 1, 16, 32, device=DEV)
+    with pytest.raises(ops.KernelError):
+        ops.prefill_attention(torch.zeros(1, 32, device=DEV), 32, torch.zeros(1, 32, device=DEV), kv32, z.view(1, 1),
+                              torch.tensor([[0, 1, 0]], dtype=torch.int32, device=DEV), z, 1, 1, 32, 0, 1.0)
