@@ -523,3 +523,77 @@ extern "C" int rg_decode_attention(const void* q, int q_stride, void* out, const
     decode_reduce_kernel<<<rgrid, d >= 128 ? 128 : 64, 0, s>>>(part_o, part_ml, (bf16*)out, rows, nh, d, num_splits);
     return RG_LAUNCH_RESULT();
 }
+
+// ---------------------------------------------------------------------------------------------------
+// The same split decode attention for callers that cannot allocate: scratch in a fixed device array.
+// Declaration, limits and rules of use: attention_static_scratch.h.
+// ---------------------------------------------------------------------------------------------------
+#include <cstdio>
+#include <mutex>
+#include "attention_static_scratch.h"
+
+// In host code this name is a stand-in for the symbol, not a device address; kernels get the address that
+// cudaGetSymbolAddress returns for the current device.
+static __device__ __align__(256) unsigned char rg_static_scratch[RG_STATIC_SCRATCH_BYTES];
+
+#define RG_MAX_DEVICES 64
+static float* rg_static_scratch_ptr[RG_MAX_DEVICES];
+static std::mutex rg_static_scratch_mutex;
+
+static void rg_set_error(char* text, int cap, const char* msg) {
+    if (text && cap > 0) snprintf(text, (size_t)cap, "%s", msg);
+}
+
+extern "C" int rg_decode_attention_static_scratch(
+        const void* q, int q_stride, void* out, const void* kv_cache, const int* block_table, int max_blocks,
+        const int* rows, int n_tokens, const int* req_of_token, const int* positions,
+        int num_heads, int num_kv_heads, int head_dim, int page_size, int window, float scale, int num_splits,
+        void* stream, char* error_text, int error_cap) {
+    if (n_tokens <= 0) return 0;
+    if (num_splits < 1 || num_heads < 1 || head_dim < 1) {
+        rg_set_error(error_text, error_cap, "num_splits, num_heads and head_dim must be positive");
+        return RG_ERR_UNSUPPORTED;
+    }
+    // part_o floats, rounded up to 64 floats (256 bytes), then part_ml
+    const unsigned long long slots = (unsigned long long)n_tokens * num_heads * num_splits;
+    const unsigned long long o_floats = (slots * head_dim + 63ull) / 64ull * 64ull;
+    const unsigned long long need = (o_floats + slots * 2ull) * sizeof(float);
+    if (need > RG_STATIC_SCRATCH_BYTES) {
+        char msg[256];
+        snprintf(msg, sizeof msg,
+                 "scratch of %llu bytes needed (n_tokens %d x heads %d x splits %d x (head_dim %d + 2) floats) "
+                 "but the fixed array holds %u: use fewer splits or tokens per call",
+                 need, n_tokens, num_heads, num_splits, head_dim, (unsigned)RG_STATIC_SCRATCH_BYTES);
+        rg_set_error(error_text, error_cap, msg);
+        return RG_ERR_SCRATCH_TOO_LARGE;
+    }
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= RG_MAX_DEVICES) {
+        rg_set_error(error_text, error_cap, "cannot tell the current device");
+        return e != cudaSuccess ? (int)e : RG_ERR_UNSUPPORTED;
+    }
+    float* base;
+    {
+        std::lock_guard<std::mutex> lock(rg_static_scratch_mutex);
+        if (rg_static_scratch_ptr[dev] == nullptr) {              // first call on this device: look the address up
+            void* p = nullptr;
+            e = cudaGetSymbolAddress(&p, rg_static_scratch);
+            if (e != cudaSuccess || p == nullptr) {
+                rg_set_error(error_text, error_cap, "cudaGetSymbolAddress failed for the scratch array");
+                return e != cudaSuccess ? (int)e : RG_ERR_UNSUPPORTED;
+            }
+            rg_static_scratch_ptr[dev] = (float*)p;
+        }
+        base = rg_static_scratch_ptr[dev];
+    }
+    const int code = rg_decode_attention(q, q_stride, out, kv_cache, block_table, max_blocks, rows, n_tokens,
+                                         req_of_token, positions, base, base + o_floats, num_heads, num_kv_heads,
+                                         head_dim, page_size, window, scale, num_splits, stream);
+    if (code == RG_ERR_UNSUPPORTED)
+        rg_set_error(error_text, error_cap, "the kernels refuse these sizes (head_dim 16..256 in steps of 16, "
+                                            "num_heads a multiple of num_kv_heads)");
+    else if (code != 0)
+        rg_set_error(error_text, error_cap, cudaGetErrorString((cudaError_t)code));
+    return code;
+}
