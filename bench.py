@@ -178,6 +178,29 @@ def run_ours(args):
         runner.end(ids)
         return batch / ms * 1e3, ms, n_launch
 
+    if args.mode == "decode":                              # a short run of one decode batch (for profiling)
+        tok_s, ms_step, n_launch = time_decode(args.batch, args.steps, args.warmup, 1000)
+        print(json.dumps({"mode": "decode", "batch": args.batch, "tok_s": round(tok_s, 1),
+                          "ms_per_step": round(ms_step, 4), "gpu_launches": n_launch,
+                          "layers": cfg["num_hidden_layers"]}))
+        return 0
+    if args.mode == "prefill":
+        prompt = rng.integers(0, V, size=args.tokens).tolist()
+        times = []
+        for i in range(args.warmup + args.steps):
+            torch.cuda.synchronize()
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            runner.step([StepEntry(7000 + i, prompt, [args.tokens - 1])])
+            t1.record()
+            torch.cuda.synchronize()
+            runner.end([7000 + i])
+            times.append(t0.elapsed_time(t1))
+        ms = sorted(times[args.warmup:])[len(times[args.warmup:]) // 2]
+        print(json.dumps({"mode": "prefill", "tokens": args.tokens, "ms": round(ms, 3),
+                          "tok_s": round(args.tokens / ms * 1e3, 1), "layers": cfg["num_hidden_layers"],
+                          "frac": round(prefill_flops(cfg, args.tokens) / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}))
+        return 0
     with ClockSampler() as clocks:
         tok_s, ms_step, n_launch = time_decode(8, args.steps, args.warmup, 1000)
     clock_summary = clocks.summary()
@@ -257,6 +280,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the named configuration (0: all)")
+    ap.add_argument("--mode", default="all", choices=["all", "decode", "prefill"],
+                    help="all: the contract's line; decode / prefill: one short measurement (for profiling)")
+    ap.add_argument("--batch", type=int, default=8, help="--mode decode: requests in the batch")
+    ap.add_argument("--tokens", type=int, default=PREFILL_TOKENS, help="--mode prefill: prompt length")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":

@@ -1,0 +1,170 @@
+// Weight-streaming matrix product for decode: y[M, N] = x[M, K] W[N, K]^T with M <= 64.
+//
+// At these sizes the product is bound by reading W once from HBM, so the
+// kernel is built around keeping many 16-byte loads of W in flight and nothing
+// else: the weight rows take the tensor core's M side (swap-AB: 16 rows of W
+// per mma, the batch on the 8-wide N side), both operand fragments come
+// straight from 16-byte global loads (the k index is permuted the same way in
+// both operands, which a dot product does not notice), W never touches shared
+// memory and bypasses L1.  The warps of a block split K and are summed through
+// shared memory in a fixed order, so a row's result depends neither on the
+// batch it is in nor on anything but its own inputs.
+//
+// Epilogues: plain (bf16 or fp32 out), and SiLU-mul for the gate|up
+// projection stored interleaved (rows 16t..16t+7 gate, 16t+8..16t+15 the
+// matching up rows), out[m, 8t + j] = silu(gate) * up in 32-bit
+// (crates/vllm-models/src/llama/architecture.rs:81-85).  The reference runs
+// these products through cuBLAS (crates/vllm-models/src/llama/attention.rs:94-96,133).
+#include "common.cuh"
+
+#define EPI_NONE 0
+#define EPI_SILU_MUL 1
+
+__device__ __forceinline__ uint4 ld_stream16(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint4 ld_cached16(const void* p) {
+    return __ldg(reinterpret_cast<const uint4*>(p));
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// One block: 16 rows of W (n0 .. n0+15), all of K split over NW warps in interleaved 128-wide pieces.
+// MT: batch rows / 8 (rounded up).  x rows are ldx elements apart.  K % 8 == 0.
+template <int MT, int NW, int EPI, typename OUT>
+__global__ void __launch_bounds__(NW * 32)
+skinny_gemm_kernel(const bf16* __restrict__ W, const bf16* __restrict__ x, int ldx, OUT* __restrict__ out, int ldo,
+                   int M, int N, int K) {
+    extern __shared__ float red[];                     // [NW][16][8 * MT]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, tq = lane & 3;
+    const int n0 = blockIdx.x * 16;
+    const int r0 = n0 + g, r1 = n0 + g + 8;
+    const bool v0 = r0 < N, v1 = r1 < N;
+    const bf16* w0 = W + (size_t)(v0 ? r0 : 0) * K + tq * 8;
+    const bf16* w1 = W + (size_t)(v1 ? r1 : 0) * K + tq * 8;
+    const bf16* xr[MT];
+    bool xv[MT];
+#pragma unroll
+    for (int j = 0; j < MT; ++j) {
+        const int m = j * 8 + g;
+        xv[j] = m < M;
+        xr[j] = x + (size_t)(xv[j] ? m : 0) * ldx + tq * 8;
+    }
+    float acc[MT][4];
+#pragma unroll
+    for (int j = 0; j < MT; ++j) { acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f; }
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+
+    for (int kb = warp * 128; kb < K; kb += NW * 128) {
+        uint4 a[4], b[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {                  // 8 loads of W in flight per thread
+            const int k = kb + c * 32;
+            const bool kin = k + tq * 8 < K;
+            a[c] = (kin && v0) ? ld_stream16(w0 + k) : zero;
+            b[c] = (kin && v1) ? ld_stream16(w1 + k) : zero;
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const int k = kb + c * 32;
+            const bool kin = k + tq * 8 < K;
+#pragma unroll
+            for (int j = 0; j < MT; ++j) {
+                const uint4 xq = (kin && xv[j]) ? ld_cached16(xr[j] + k) : zero;
+                mma16816(acc[j], a[c].x, b[c].x, a[c].y, b[c].y, xq.x, xq.y);
+                mma16816(acc[j], a[c].z, b[c].z, a[c].w, b[c].w, xq.z, xq.w);
+            }
+        }
+    }
+    // the warps' partial sums -> shared memory, summed in warp order
+    constexpr int COLS = 8 * MT;
+    float* mine = red + (size_t)warp * 16 * COLS;
+#pragma unroll
+    for (int j = 0; j < MT; ++j) {
+        const int col = j * 8 + tq * 2;
+        mine[g * COLS + col] = acc[j][0];
+        mine[g * COLS + col + 1] = acc[j][1];
+        mine[(g + 8) * COLS + col] = acc[j][2];
+        mine[(g + 8) * COLS + col + 1] = acc[j][3];
+    }
+    __syncthreads();
+    if (EPI == EPI_NONE) {
+        for (int idx = threadIdx.x; idx < 16 * COLS; idx += NW * 32) {
+            const int m = idx >> 4, row = idx & 15;    // consecutive threads -> consecutive n: coalesced stores
+            if (m < M && n0 + row < N) {
+                float s = 0.f;
+#pragma unroll
+                for (int w = 0; w < NW; ++w) s += red[((size_t)w * 16 + row) * COLS + m];
+                out[(size_t)m * ldo + n0 + row] = from_f32<OUT>(s);
+            }
+        }
+    } else {
+        for (int idx = threadIdx.x; idx < 8 * COLS; idx += NW * 32) {
+            const int m = idx >> 3, j = idx & 7;
+            if (m < M && n0 + j + 8 < N) {
+                float gate = 0.f, up = 0.f;
+#pragma unroll
+                for (int w = 0; w < NW; ++w) {
+                    gate += red[((size_t)w * 16 + j) * COLS + m];
+                    up += red[((size_t)w * 16 + j + 8) * COLS + m];
+                }
+                out[(size_t)m * ldo + (n0 >> 1) + j] = from_f32<OUT>(gate / (1.f + expf(-gate)) * up);
+            }
+        }
+    }
+}
+
+template <int MT, int NW, int EPI, typename OUT>
+static int launch_skinny(const bf16* W, const bf16* x, int ldx, OUT* out, int ldo, int M, int N, int K,
+                         cudaStream_t s) {
+    const size_t smem = (size_t)NW * 16 * 8 * MT * sizeof(float);
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(skinny_gemm_kernel<MT, NW, EPI, OUT>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    skinny_gemm_kernel<MT, NW, EPI, OUT><<<(N + 15) / 16, NW * 32, smem, s>>>(W, x, ldx, out, ldo, M, N, K);
+    return RG_LAUNCH_RESULT();
+}
+
+template <int EPI, typename OUT>
+static int dispatch_skinny(const bf16* W, const bf16* x, int ldx, OUT* out, int ldo, int M, int N, int K,
+                           cudaStream_t s) {
+    // more warps per block when a block's 16 rows are long or the blocks are few, so that enough loads are in flight
+    const long long blocks = (N + 15) / 16;
+    const bool wide = K >= 4096 || blocks < 2 * 148;
+#define RG_SK(MT_) (wide ? launch_skinny<MT_, 16, EPI, OUT>(W, x, ldx, out, ldo, M, N, K, s) \
+                         : launch_skinny<MT_, 4, EPI, OUT>(W, x, ldx, out, ldo, M, N, K, s))
+    if (M <= 8) return RG_SK(1);
+    if (M <= 16) return RG_SK(2);
+    if (M <= 32) return RG_SK(4);
+    return RG_SK(8);
+#undef RG_SK
+}
+
+// out_dtype: RG_DTYPE_BF16 or RG_DTYPE_F32.  epilogue: 0 plain (out [M, N]); 1 SiLU-mul over interleaved gate|up rows
+// (out [M, N / 2]).  Refuses M > 64, K % 8 != 0 and, for the SiLU-mul epilogue, N % 16 != 0.
+extern "C" int rg_skinny_gemm(const void* W, const void* x, int ldx, void* out, int ldo, int out_dtype, int epilogue,
+                              int M, int N, int K, void* stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (M > 64 || K % 8 || K <= 0 || ldx % 8) return RG_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    const bf16* w = (const bf16*)W;
+    const bf16* xx = (const bf16*)x;
+    if (epilogue == EPI_SILU_MUL) {
+        if (N % 16 || out_dtype != RG_DTYPE_BF16) return RG_ERR_UNSUPPORTED;
+        return dispatch_skinny<EPI_SILU_MUL, bf16>(w, xx, ldx, (bf16*)out, ldo, M, N, K, s);
+    }
+    if (epilogue != EPI_NONE) return RG_ERR_UNSUPPORTED;
+    if (out_dtype == RG_DTYPE_BF16) return dispatch_skinny<EPI_NONE, bf16>(w, xx, ldx, (bf16*)out, ldo, M, N, K, s);
+    if (out_dtype == RG_DTYPE_F32) return dispatch_skinny<EPI_NONE, float>(w, xx, ldx, (float*)out, ldo, M, N, K, s);
+    return RG_ERR_UNSUPPORTED;
+}

@@ -201,9 +201,53 @@ __global__ void sample_kernel(const float* __restrict__ logits, int V,
     }
 }
 
-extern "C" int rg_argmax(const float* logits, int rows, int V, int* out, void* stream) {
+// Two stages for wide rows: each block takes one piece of a row, then one block per row takes the best piece.
+__global__ void argmax_partial_kernel(const float* __restrict__ logits, int V, int chunk,
+                                      float* __restrict__ pv, int* __restrict__ pi) {
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    const float* row = logits + (size_t)blockIdx.y * V;
+    const int b = blockIdx.x * chunk, e = min(V, b + chunk);
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = b + threadIdx.x; i < e; i += blockDim.x) {
+        const float v = row[i];
+        if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+    }
+    block_argmax(best, bi, sv, si);
+    if (threadIdx.x == 0) {
+        pv[blockIdx.y * gridDim.x + blockIdx.x] = best;
+        pi[blockIdx.y * gridDim.x + blockIdx.x] = bi;
+    }
+}
+__global__ void argmax_final_kernel(const float* __restrict__ pv, const int* __restrict__ pi, int n,
+                                    int* __restrict__ out) {
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const float v = pv[blockIdx.x * n + i];
+        const int idx = pi[blockIdx.x * n + i];
+        if (v > best || (v == best && idx < bi)) { best = v; bi = idx; }
+    }
+    block_argmax(best, bi, sv, si);
+    if (threadIdx.x == 0) out[blockIdx.x] = bi == 0x7fffffff ? 0 : bi;
+}
+
+// pieces > 1: pv/pi are scratch of rows * pieces entries each.
+extern "C" int rg_argmax(const float* logits, int rows, int V, int* out, float* pv, int* pi, int pieces,
+                         void* stream) {
     if (rows <= 0) return 0;
-    argmax_kernel<<<rows, SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(logits, V, out);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (pieces <= 1 || pv == nullptr || pi == nullptr) {
+        argmax_kernel<<<rows, SAMPLE_THREADS, 0, s>>>(logits, V, out);
+        return RG_LAUNCH_RESULT();
+    }
+    const int chunk = (V + pieces - 1) / pieces;
+    dim3 grid(pieces, rows);
+    argmax_partial_kernel<<<grid, 256, 0, s>>>(logits, V, chunk, pv, pi);
+    argmax_final_kernel<<<rows, 64, 0, s>>>(pv, pi, pieces, out);
     return RG_LAUNCH_RESULT();
 }
 

@@ -126,15 +126,58 @@ def residual_add(resid: torch.Tensor, pending: torch.Tensor) -> None:
                                        c_longlong(resid.numel()), _stream()), "residual_add")
 
 
-def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
-    """[T, 2I] -> [T, I]: silu(first half) * second half."""
+def silu_mul(gate_up: torch.Tensor, interleaved: bool = False) -> torch.Tensor:
+    """[T, 2I] -> [T, I]: silu(gate) * up.  Plain storage: gate is the first
+    half of a row, up the second.  ``interleaved``: blocks of 8 gate columns
+    followed by their 8 up columns (the storage ``interleave_gate_up`` makes)."""
     _check(gate_up, "gate_up")
     T, two_i = gate_up.shape
-    if two_i % 2:
-        raise KernelError("silu_mul: last dimension must be even")
+    if two_i % 2 or (interleaved and two_i % 16):
+        raise KernelError("silu_mul: last dimension must be even (a multiple of 16 when interleaved)")
     out = torch.empty((T, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
-    _ok(_fn("activation", "rg_silu_mul")(_ptr(gate_up), _ptr(out), c_int(_dtype_code(gate_up)),
-                                         c_int(T), c_int(two_i // 2), _stream()), "silu_mul")
+    name = "rg_silu_mul_interleaved" if interleaved else "rg_silu_mul"
+    _ok(_fn("activation", name)(_ptr(gate_up), _ptr(out), c_int(_dtype_code(gate_up)),
+                                c_int(T), c_int(two_i // 2), _stream()), "silu_mul")
+    return out
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """Stack gate [I, K] and up [I, K] as blocks of 8 gate rows followed by the
+    8 matching up rows, so that one 16-row tensor-core tile holds a gate
+    element and its up element in the same thread (I % 8 == 0)."""
+    I, K = gate.shape
+    if I % 8 or up.shape != gate.shape:
+        raise KernelError("interleave_gate_up: both [I, K] with I a multiple of 8")
+    return torch.stack([gate.view(I // 8, 8, K), up.view(I // 8, 8, K)], dim=1).reshape(2 * I, K).contiguous()
+
+
+SKINNY_MAX_ROWS = 64
+
+
+def skinny_gemm_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    """Can the weight-streaming decode product take this shape?"""
+    return (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dim() == 2
+            and 0 < x.shape[0] <= SKINNY_MAX_ROWS and x.shape[1] % 8 == 0 and x.stride(1) == 1
+            and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and weight.is_contiguous())
+
+
+def skinny_gemm(x: torch.Tensor, weight: torch.Tensor, out_dtype=None, silu_mul: bool = False) -> torch.Tensor:
+    """y = x W^T for up to 64 rows of x, reading W once at memory speed.
+    ``silu_mul``: W is interleaved gate|up storage and y = silu(gate) * up."""
+    if not skinny_gemm_ok(x, weight):
+        raise KernelError(f"skinny_gemm refuses x {tuple(x.shape)} {x.dtype}, W {tuple(weight.shape)} {weight.dtype}: "
+                          "bfloat16, at most 64 rows, K a multiple of 8")
+    M, K = x.shape
+    N = weight.shape[0]
+    if weight.shape[1] != K:
+        raise KernelError(f"skinny_gemm: x has {K} columns, W has {weight.shape[1]}")
+    out_dtype = out_dtype or torch.bfloat16
+    if silu_mul and (N % 16 or out_dtype != torch.bfloat16):
+        raise KernelError("skinny_gemm: the SiLU-mul epilogue needs N % 16 == 0 and bfloat16 output")
+    out = torch.empty((M, N // 2 if silu_mul else N), dtype=out_dtype, device=x.device)
+    _ok(_fn("gemm_skinny", "rg_skinny_gemm")(
+        _ptr(weight), _ptr(x), c_int(x.stride(0)), _ptr(out), c_int(out.shape[1]), c_int(_dtype_code(out)),
+        c_int(1 if silu_mul else 0), c_int(M), c_int(N), c_int(K), _stream()), "skinny_gemm")
     return out
 
 
@@ -257,10 +300,18 @@ def decode_attention(q, q_stride: int, out, kv_cache, block_table, rows, n_token
 
 
 def argmax(logits: torch.Tensor) -> torch.Tensor:
+    """Index of the largest logit of every row, ties to the lowest index."""
     _check(logits, "logits", torch.float32)
     rows, V = logits.shape
     out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
-    _ok(_fn("sampling", "rg_argmax")(_ptr(logits), c_int(rows), c_int(V), _ptr(out), _stream()), "argmax")
+    pieces = min(64, -(-V // 2048))            # wide rows are cut into pieces so that many blocks share a row
+    pv = pi = None
+    if pieces > 1:
+        pv = torch.empty((rows, pieces), dtype=torch.float32, device=logits.device)
+        pi = torch.empty((rows, pieces), dtype=torch.int32, device=logits.device)
+        _COUNTER.value += 1
+    _ok(_fn("sampling", "rg_argmax")(_ptr(logits), c_int(rows), c_int(V), _ptr(out), _ptr(pv), _ptr(pi),
+                                     c_int(pieces), _stream()), "argmax")
     return out
 
 
@@ -303,14 +354,18 @@ def decode_advance(token_ids, sampled, positions, context_lens, start_pos, slots
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype=None) -> torch.Tensor:
-    """y = x W^T, W stored [out, in]: the library matrix product (cuBLAS), as in
-    the reference, whose projections are library GEMMs
-    (crates/vllm-models/src/llama/attention.rs:94-96,133).  32-bit inputs run
-    in true 32-bit: the reduced-precision matrix mode is refused."""
+    """y = x W^T, W stored [out, in].  Up to 64 bfloat16 rows go through the
+    weight-streaming kernel of this package; everything else through the
+    library matrix product (cuBLAS), as in the reference, whose projections
+    are library GEMMs (crates/vllm-models/src/llama/attention.rs:94-96,133).
+    32-bit inputs run in true 32-bit: the reduced-precision matrix mode is
+    refused."""
     if not x.is_cuda:
         raise KernelError("linear: CUDA tensors only (there is no CPU path)")
     if x.dtype == torch.float32 and torch.backends.cuda.matmul.allow_tf32:
         raise KernelError("linear: TF32 is enabled; the 32-bit path must be true 32-bit")
+    if skinny_gemm_ok(x, weight):
+        return skinny_gemm(x, weight, out_dtype)             # decode: stream the weights once
     if out_dtype is not None and out_dtype != x.dtype:
         return torch.mm(x, weight.t(), out_dtype=out_dtype)
     return torch.mm(x, weight.t())

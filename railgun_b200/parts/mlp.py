@@ -27,13 +27,21 @@ class SwiGLU(FeedForward):
     def __init__(self, p, prefix, env, tensors):
         super().__init__(p, prefix, env, tensors)
         m = prefix + "mlp."
-        self.w_gate_up = torch.cat([tensors.get(m + "gate_proj.weight", env.dtype),
-                                    tensors.get(m + "up_proj.weight", env.dtype)], dim=0).contiguous()
+        gate, up = tensors.get(m + "gate_proj.weight", env.dtype), tensors.get(m + "up_proj.weight", env.dtype)
+        # bfloat16 with I % 8 == 0: gate and up rows interleaved in blocks of 8, which lets the decode
+        # product apply SiLU-mul in its epilogue; otherwise gate rows, then up rows
+        self.interleaved = env.dtype == torch.bfloat16 and p["intermediate_size"] % 8 == 0
+        self.w_gate_up = (ops.interleave_gate_up(gate, up) if self.interleaved
+                          else torch.cat([gate, up], dim=0).contiguous())
         tensors.drop(m + "gate_proj.weight", m + "up_proj.weight")
         self.w_down = tensors.get(m + "down_proj.weight", env.dtype)
 
     def forward(self, x, batch):
-        return ops.linear(ops.silu_mul(ops.linear(x, self.w_gate_up)), self.w_down)
+        if self.interleaved and ops.skinny_gemm_ok(x, self.w_gate_up):
+            act = ops.skinny_gemm(x, self.w_gate_up, silu_mul=True)
+        else:
+            act = ops.silu_mul(ops.linear(x, self.w_gate_up), interleaved=self.interleaved)
+        return ops.linear(act, self.w_down)
 
 
 register_feed_forward("swiglu", SwiGLU)

@@ -398,3 +398,58 @@ def test_mma_attention_refuses_other_head_sizes_and_dtypes():
     with pytest.raises(ops.KernelError):
         ops.prefill_attention(torch.zeros(1, 32, device=DEV), 32, torch.zeros(1, 32, device=DEV), kv32, z.view(1, 1),
                               torch.tensor([[0, 1, 0]], dtype=torch.int32, device=DEV), z, 1, 1, 32, 0, 1.0)
+
+
+# ---- the weight-streaming decode product ---------------------------------------------------------------
+
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16, 29, 64])
+@pytest.mark.parametrize("N,K", [(48, 64), (500, 96), (2048, 2048), (1000, 176), (3072, 8192), (250, 4104)])
+def test_skinny_gemm(M, N, K):
+    from railgun_b200 import ops
+    g = torch.Generator().manual_seed(M * 1000 + N + K)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(N, K, generator=g) / K ** 0.5).to(torch.bfloat16).to(DEV)
+    ref = x.double() @ w.double().T
+    out = ops.skinny_gemm(x, w)
+    assert out.dtype == torch.bfloat16 and rel_err(out, ref) < 1e-2
+    out32 = ops.skinny_gemm(x, w, out_dtype=torch.float32)
+    assert out32.dtype == torch.float32 and rel_err(out32, ref) < 2e-5      # exact products, 32-bit sums
+    # a row's result does not depend on the batch around it
+    alone = ops.skinny_gemm(x[M - 1:].contiguous(), w, out_dtype=torch.float32)
+    assert torch.equal(alone[0], out32[M - 1])
+    # x as a strided view (rows further apart than their length)
+    wide = torch.zeros(M, K + 64, dtype=torch.bfloat16, device=DEV)
+    wide[:, :K] = x
+    assert torch.equal(ops.skinny_gemm(wide[:, :K], w, out_dtype=torch.float32), out32)
+
+
+@pytest.mark.parametrize("M", [1, 8, 40])
+@pytest.mark.parametrize("I,K", [(176, 64), (256, 96), (8192, 2048)])
+def test_skinny_gemm_silu_mul_and_interleaved_storage(M, I, K):
+    from railgun_b200 import ops
+    g = torch.Generator().manual_seed(I + K + M)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+    gate = (torch.randn(I, K, generator=g) / K ** 0.5 * 2).to(torch.bfloat16).to(DEV)
+    up = (torch.randn(I, K, generator=g) / K ** 0.5 * 2).to(torch.bfloat16).to(DEV)
+    a, b = x.double() @ gate.double().T, x.double() @ up.double().T
+    ref = a / (1 + torch.exp(-a)) * b
+    w = ops.interleave_gate_up(gate, up)
+    assert torch.equal(w[:8], gate[:8]) and torch.equal(w[8:16], up[:8]) and torch.equal(w[16:24], gate[8:16])
+    fused = ops.skinny_gemm(x, w, silu_mul=True)
+    assert fused.shape == (M, I) and rel_err(fused, ref) < 1e-2
+    # the unfused route over the same storage (what longer batches take)
+    unfused = ops.silu_mul(torch.mm(x, w.t()), interleaved=True)
+    assert rel_err(unfused, ref) < 2e-2
+
+
+def test_skinny_gemm_refusals():
+    from railgun_b200 import ops
+    w = torch.zeros(32, 20, dtype=torch.bfloat16, device=DEV)
+    assert not ops.skinny_gemm_ok(torch.zeros(2, 20, dtype=torch.bfloat16, device=DEV), w)      # K % 8
+    assert not ops.skinny_gemm_ok(torch.zeros(65, 24, dtype=torch.bfloat16, device=DEV), w)     # too many rows
+    assert not ops.skinny_gemm_ok(torch.zeros(2, 24, device=DEV), w)                            # 32-bit
+    with pytest.raises(ops.KernelError):
+        ops.skinny_gemm(torch.zeros(2, 20, dtype=torch.bfloat16, device=DEV), w)
+    # linear() falls through to the library product for those
+    y = ops.linear(torch.ones(2, 20, dtype=torch.bfloat16, device=DEV), torch.ones(32, 20, dtype=torch.bfloat16, device=DEV))
+    assert y.shape == (2, 32) and float(y[0, 0]) == 20.0
