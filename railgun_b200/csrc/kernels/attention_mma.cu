@@ -56,18 +56,22 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// Gather BN keys (rows key0 .. key0+BN-1 of a request) of K and V for one kv head into shared memory.
-// Rows at or beyond key_end are zero-filled.  sK, sV: [BN][d + PAD].
-__device__ __forceinline__ void load_kv_tile(bf16* sK, bf16* sV, const bf16* __restrict__ kv_cache,
-                                             const int* __restrict__ bt, int key0, int key_end, int kvh, int nkv,
-                                             int d, int page_size) {
+// Gathering BN keys (rows key0 .. key0+BN-1 of a request) of K and V for one kv head into shared memory
+// is done row by row: thread t handles half of row t/2.  The page of a row is looked up one tile ahead
+// (lookup_page) so that the table read is off the critical path when the copies are issued (issue_kv_rows).
+// Rows at or beyond key_end have page -1 and are zero-filled.  sK, sV: [BN][d + PAD].
+__device__ __forceinline__ int lookup_page(const int* __restrict__ bt, int key0, int key_end, int page_size) {
+    const int key = key0 + (threadIdx.x >> 1);
+    return key < key_end ? bt[key / page_size] : -1;
+}
+__device__ __forceinline__ void issue_kv_rows(bf16* sK, bf16* sV, const bf16* __restrict__ kv_cache, int page,
+                                              int key0, int kvh, int nkv, int d, int page_size) {
     const int row = threadIdx.x >> 1, half = threadIdx.x & 1;     // 128 threads: 64 rows x 2
-    const int key = key0 + row;
-    const bool valid = key < key_end;
+    const bool valid = page >= 0;
     const bf16* ksrc = kv_cache;
     const bf16* vsrc = kv_cache;
     if (valid) {
-        const int page = bt[key / page_size], off = key % page_size;
+        const int off = (key0 + row) % page_size;
         const size_t page_elems = (size_t)2 * nkv * page_size * d;
         ksrc = kv_cache + (size_t)page * page_elems + ((size_t)kvh * page_size + off) * d;
         vsrc = ksrc + (size_t)nkv * page_size * d;
@@ -120,8 +124,10 @@ prefill_attention_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
             cp_async16(sQ + row * stride + c * 8, src, valid);
         }
     }
-    load_kv_tile(sKV, sKV + BN * stride, kv_cache, bt, kt0 * BN, hi + 1, kvh, nkv, d, page_size);
+    issue_kv_rows(sKV, sKV + BN * stride, kv_cache, lookup_page(bt, kt0 * BN, hi + 1, page_size), kt0 * BN, kvh, nkv,
+                  d, page_size);
     cp_async_commit();
+    int page_next = kt0 + 1 <= kt1 ? lookup_page(bt, (kt0 + 1) * BN, hi + 1, page_size) : -1;
 
     uint32_t qf[Q_IN_REGS ? KD : 1][4];
     float o[ND][4];
@@ -141,8 +147,9 @@ prefill_attention_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
         bf16* sV = sK + BN * stride;
         if (kt + 1 <= kt1) {
             bf16* nK = sKV + (stage ^ 1) * stage_elems;
-            load_kv_tile(nK, nK + BN * stride, kv_cache, bt, (kt + 1) * BN, hi + 1, kvh, nkv, d, page_size);
+            issue_kv_rows(nK, nK + BN * stride, kv_cache, page_next, (kt + 1) * BN, kvh, nkv, d, page_size);
             cp_async_commit();
+            page_next = kt + 2 <= kt1 ? lookup_page(bt, (kt + 2) * BN, hi + 1, page_size) : -1;
             cp_async_wait<1>();
         } else {
             cp_async_wait<0>();
@@ -250,12 +257,17 @@ prefill_attention_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
 }
 
 // ---------------------------------------------------------------------------------------------------
-// Decode: one CTA per (split of the context, kv head x tile of up to 16 query heads of its group, token).
-// The four warps take 16 keys each of every 64-key tile and are combined at the end; the CTA writes an
-// unnormalised partial output with its max (log2 domain) and sum into the scratch arrays
+// Decode: one CTA per (token, kv head x tile of up to 8 query heads of its group, split of the context).
+// The four warps take 16 keys each of every 64-key tile, each warp gathering and consuming its own rows
+// (no block-wide barrier in the loop), and are combined at the end; the CTA writes an unnormalised
+// partial output with its max (log2 domain) and sum into the scratch arrays
 //   part_o [n_tokens][nh][num_splits][d] (float), part_ml [n_tokens][nh][num_splits][2] (float).
+// Scores are S[head, key] = Q K^T (heads padded to the 16 rows of the tensor-core tile); the output is
+// accumulated transposed, O^T[dim, head] += V^T[dim, key] P^T[key, head], so that the softmax and the
+// rescaling only cost work for 8 head columns and P feeds the second product straight from registers.
 // ---------------------------------------------------------------------------------------------------
 #define DEC_STAGES 3
+#define DEC_HEADS 8        // query heads per CTA
 
 template <int DMAX>
 __global__ void __launch_bounds__(NTHREADS)
@@ -263,22 +275,25 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
                         const int* __restrict__ block_table, int max_blocks, const int* __restrict__ rows,
                         const int* __restrict__ req_of_token, const int* __restrict__ positions,
                         float* __restrict__ part_o, float* __restrict__ part_ml, int nh, int nkv, int d,
-                        int page_size, int window, float scale_log2, int num_splits, int head_tiles) {
+                        int page_size, int page_shift, int window, float scale_log2, int num_splits,
+                        int head_tiles) {
     constexpr int KD = DMAX / 16;
-    constexpr int ND = DMAX / 8;
+    constexpr bool Q_IN_REGS = DMAX <= 128;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int stride = d + PAD;
-    bf16* sQ = reinterpret_cast<bf16*>(smem_raw);                  // [16][stride]
-    bf16* sKV = sQ + 16 * stride;                                  // DEC_STAGES x (K, V)
     const int stage_elems = 2 * BN * stride;
+    bf16* sKV = reinterpret_cast<bf16*>(smem_raw);                 // DEC_STAGES x (K [BN][stride], V [BN][stride])
+    // Q [16][stride]: once its fragments are in registers it is not read again, so it may sit in the
+    // last stage, which is first filled inside the loop
+    bf16* sQ = Q_IN_REGS ? sKV + (DEC_STAGES - 1) * stage_elems : sKV + DEC_STAGES * stage_elems;
 
     const int split = blockIdx.z;
     const int kvh = blockIdx.y / head_tiles, ht = blockIdx.y - kvh * head_tiles;
     const int ti = blockIdx.x;
     const int t = rows ? rows[ti] : ti;
     const int group = nh / nkv;
-    const int h0 = kvh * group + ht * 16;
-    const int nheads = min(16, group - ht * 16);
+    const int h0 = kvh * group + ht * DEC_HEADS;
+    const int nheads = min(DEC_HEADS, group - ht * DEC_HEADS);
     const int r = req_of_token[t];
     const int pos = positions[t];
     const int* bt = block_table + (size_t)r * max_blocks;
@@ -302,28 +317,64 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
     }
     const int n_tiles = (k_end - k_begin + BN - 1) / BN;
 
+    // this thread's part of the gathering: half of row (threadIdx.x / 2) of every tile
+    const int my_row = threadIdx.x >> 1, my_half = threadIdx.x & 1;
+    const size_t page_elems = (size_t)2 * nkv * page_size * d;
+    const size_t v_off = (size_t)nkv * page_size * d;
+    const int chunks = d8;
+    auto page_of = [&](int key0) -> int {
+        const int key = key0 + my_row;
+        if (key >= k_end) return -1;
+        return bt[page_shift >= 0 ? key >> page_shift : key / page_size];
+    };
+    auto gather = [&](int stage, int page, int key0) {
+        bf16* sK = sKV + stage * stage_elems + my_row * stride;
+        bf16* sV = sK + BN * stride;
+        const bool valid = page >= 0;
+        const bf16* ksrc = kv_cache;
+        if (valid) {
+            const int key = key0 + my_row;
+            const int off = page_shift >= 0 ? key & (page_size - 1) : key % page_size;
+            ksrc = kv_cache + (size_t)page * page_elems + ((size_t)kvh * page_size + off) * d;
+        }
+        const bf16* vsrc = ksrc + (valid ? v_off : 0);
+        for (int c = my_half; c < chunks; c += 2) {
+            cp_async16(sK + c * 8, ksrc + c * 8, valid);
+            cp_async16(sV + c * 8, vsrc + c * 8, valid);
+        }
+    };
+
     for (int idx = threadIdx.x; idx < 16 * d8; idx += NTHREADS) {
         const int row = idx / d8, c = idx - row * d8;
         const bool valid = row < nheads;
         const bf16* src = valid ? q + (size_t)t * q_stride + (size_t)(h0 + row) * d + c * 8 : q;
         cp_async16(sQ + row * stride + c * 8, src, valid);
     }
+    cp_async_commit();
 #pragma unroll
     for (int st = 0; st < DEC_STAGES - 1; ++st) {
-        if (st < n_tiles) {
-            bf16* sK = sKV + st * stage_elems;
-            load_kv_tile(sK, sK + BN * stride, kv_cache, bt, k_begin + st * BN, k_end, kvh, nkv, d, page_size);
-        }
+        if (st < n_tiles) gather(st, page_of(k_begin + st * BN), k_begin + st * BN);
         cp_async_commit();
     }
+    int page_next = DEC_STAGES - 1 < n_tiles ? page_of(k_begin + (DEC_STAGES - 1) * BN) : -1;
 
-    float o[ND][4];
+    float oT[KD][4];                                                // O^T: dims (16 kd + g, + 8) x heads (2 tq, 2 tq + 1)
 #pragma unroll
-    for (int i = 0; i < ND; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
-    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    for (int i = 0; i < KD; ++i) { oT[i][0] = oT[i][1] = oT[i][2] = oT[i][3] = 0.f; }
+    float m_run = -INFINITY, l_run = 0.f;                           // of head g (lanes with g >= nheads carry padding)
     const int a_row = (lane & 7) + ((lane >> 3) & 1) * 8, a_col = (lane >> 4) * 8;
-    const int b_key = (lane & 7) + (lane >> 4) * 8, b_dim = ((lane >> 3) & 1) * 8;
-    const int v_key = (lane & 7) + ((lane >> 3) & 1) * 8, v_dim = (lane >> 4) * 8;
+    const int b_key = (lane & 7) + (lane >> 4) * 8, b_dim = ((lane >> 3) & 1) * 8;     // K as B operand
+    const int vt_key = (lane & 7) + (lane >> 4) * 8, vt_dim = ((lane >> 3) & 1) * 8;   // V^T as A operand (.trans)
+
+    uint32_t qf[Q_IN_REGS ? KD : 1][4];
+    cp_async_wait<DEC_STAGES - 1>();                                 // the Q group is the oldest: it has landed
+    __syncthreads();                                                 // Q was gathered by all threads
+    if (Q_IN_REGS) {
+#pragma unroll
+        for (int kd = 0; kd < KD; ++kd)
+            if (kd < d16) ldmatrix_x4(qf[kd], sQ + a_row * stride + kd * 16 + a_col);
+        __syncthreads();                                             // before the last stage is overwritten
+    }
 
     for (int it = 0; it < n_tiles; ++it) {
         const int stage = it % DEC_STAGES;
@@ -331,111 +382,95 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
         bf16* sV = sK + BN * stride;
         {
             const int nt = it + DEC_STAGES - 1;
-            if (nt < n_tiles) {
-                bf16* nK = sKV + (nt % DEC_STAGES) * stage_elems;
-                load_kv_tile(nK, nK + BN * stride, kv_cache, bt, k_begin + nt * BN, k_end, kvh, nkv, d, page_size);
-            }
+            if (nt < n_tiles) gather(nt % DEC_STAGES, page_next, k_begin + nt * BN);
             cp_async_commit();
+            page_next = nt + 1 < n_tiles ? page_of(k_begin + (nt + 1) * BN) : -1;
             cp_async_wait<DEC_STAGES - 1>();
         }
-        __syncthreads();
+        __syncwarp();
         const int key_base = k_begin + it * BN + warp * 16;          // this warp's 16 keys
         if (key_base < k_end && key_base + 15 >= lo) {
-            float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+            float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int kd = 0; kd < KD; ++kd) {
                 if (kd < d16) {
                     uint32_t a[4], b[4];
-                    ldmatrix_x4(a, sQ + a_row * stride + kd * 16 + a_col);
+                    if (Q_IN_REGS) { a[0] = qf[kd][0]; a[1] = qf[kd][1]; a[2] = qf[kd][2]; a[3] = qf[kd][3]; }
+                    else ldmatrix_x4(a, sQ + a_row * stride + kd * 16 + a_col);
                     ldmatrix_x4(b, sK + (warp * 16 + b_key) * stride + kd * 16 + b_dim);
-                    mma_bf16(s[0], a, b[0], b[1]);
-                    mma_bf16(s[1], a, b[2], b[3]);
+                    mma_bf16(s0, a, b[0], b[1]);
+                    mma_bf16(s1, a, b[2], b[3]);
                 }
             }
-            float mx0 = -INFINITY, mx1 = -INFINITY;
+            // head g, keys key_base + 2 tq + {0, 1} (s0) and + 8 (s1); rows 8..15 of the tile are padding
+            const int k0 = key_base + tq * 2;
+            const float v00 = (k0 < k_end && k0 >= lo) ? s0[0] * scale_log2 : -INFINITY;
+            const float v01 = (k0 + 1 < k_end && k0 + 1 >= lo) ? s0[1] * scale_log2 : -INFINITY;
+            const float v10 = (k0 + 8 < k_end && k0 + 8 >= lo) ? s1[0] * scale_log2 : -INFINITY;
+            const float v11 = (k0 + 9 < k_end && k0 + 9 >= lo) ? s1[1] * scale_log2 : -INFINITY;
+            float mx = fmaxf(fmaxf(v00, v01), fmaxf(v10, v11));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            const float mn = fmaxf(m_run, mx);
+            const float ms = mn == -INFINITY ? 0.f : mn;
+            const float alpha = exp2f(m_run - ms);
+            m_run = mn;
+            const float p00 = exp2f(v00 - ms), p01 = exp2f(v01 - ms), p10 = exp2f(v10 - ms), p11 = exp2f(v11 - ms);
+            l_run = l_run * alpha + (p00 + p01) + (p10 + p11);       // per-thread partial; summed over tq at the end
+            const uint32_t pb0 = pack_bf16(p00, p01), pb1 = pack_bf16(p10, p11);
+            if (__any_sync(0xffffffffu, alpha != 1.f)) {             // some head's max moved: rescale
+                const float al0 = __shfl_sync(0xffffffffu, alpha, (2 * tq) * 4);
+                const float al1 = __shfl_sync(0xffffffffu, alpha, (2 * tq + 1) * 4);
 #pragma unroll
-            for (int j = 0; j < 2; ++j) {
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int key = key_base + j * 8 + tq * 2 + (e & 1);
-                    const bool ok = key < k_end && key >= lo;
-                    const float v = ok ? s[j][e] * scale_log2 : -INFINITY;
-                    s[j][e] = v;
-                    if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
-                }
+                for (int kd = 0; kd < KD; ++kd) { oT[kd][0] *= al0; oT[kd][1] *= al1; oT[kd][2] *= al0; oT[kd][3] *= al1; }
             }
-            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
-            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
-            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
-            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-            const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
-            const float ms0 = mn0 == -INFINITY ? 0.f : mn0, ms1 = mn1 == -INFINITY ? 0.f : mn1;
-            const float al0 = exp2f(m0 - ms0), al1 = exp2f(m1 - ms1);
-            m0 = mn0; m1 = mn1;
-            float rs0 = 0.f, rs1 = 0.f;
 #pragma unroll
-            for (int j = 0; j < 2; ++j) {
-                s[j][0] = exp2f(s[j][0] - ms0); s[j][1] = exp2f(s[j][1] - ms0);
-                s[j][2] = exp2f(s[j][2] - ms1); s[j][3] = exp2f(s[j][3] - ms1);
-                rs0 += s[j][0] + s[j][1];
-                rs1 += s[j][2] + s[j][3];
-            }
-            l0 = l0 * al0 + rs0;
-            l1 = l1 * al1 + rs1;
-            uint32_t a[4];
-            a[0] = pack_bf16(s[0][0], s[0][1]);
-            a[1] = pack_bf16(s[0][2], s[0][3]);
-            a[2] = pack_bf16(s[1][0], s[1][1]);
-            a[3] = pack_bf16(s[1][2], s[1][3]);
-#pragma unroll
-            for (int n2 = 0; n2 < ND / 2; ++n2) {
-                if (n2 < d16) {
-                    o[2 * n2][0] *= al0; o[2 * n2][1] *= al0; o[2 * n2][2] *= al1; o[2 * n2][3] *= al1;
-                    o[2 * n2 + 1][0] *= al0; o[2 * n2 + 1][1] *= al0; o[2 * n2 + 1][2] *= al1; o[2 * n2 + 1][3] *= al1;
-                    uint32_t b[4];
-                    ldmatrix_x4_trans(b, sV + (warp * 16 + v_key) * stride + n2 * 16 + v_dim);
-                    mma_bf16(o[2 * n2], a, b[0], b[1]);
-                    mma_bf16(o[2 * n2 + 1], a, b[2], b[3]);
+            for (int kd = 0; kd < KD; ++kd) {
+                if (kd < d16) {
+                    uint32_t a[4];
+                    ldmatrix_x4_trans(a, sV + (warp * 16 + vt_key) * stride + kd * 16 + vt_dim);
+                    mma_bf16(oT[kd], a, pb0, pb1);
                 }
             }
         }
-        __syncthreads();
+        __syncwarp();                                                // this warp's rows of the stage are free again
     }
     cp_async_wait<0>();
-    l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
-    l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
 
     // combine the four warps through shared memory (the K/V stages are free now)
-    float* cO = reinterpret_cast<float*>(sKV);                       // [4 warps][16 rows][d]
-    float* cML = cO + 4 * 16 * d;                                    // [4][16][2]
+    float* cO = reinterpret_cast<float*>(smem_raw);                  // [4 warps][8 heads][d]
+    float* cML = cO + 4 * DEC_HEADS * d;                             // [4][8][2]
     __syncthreads();
 #pragma unroll
-    for (int i = 0; i < ND; ++i) {
-        if (i < d8) {
-            const int col = i * 8 + tq * 2;
-            cO[(warp * 16 + g) * d + col] = o[i][0];
-            cO[(warp * 16 + g) * d + col + 1] = o[i][1];
-            cO[(warp * 16 + g + 8) * d + col] = o[i][2];
-            cO[(warp * 16 + g + 8) * d + col + 1] = o[i][3];
+    for (int kd = 0; kd < KD; ++kd) {
+        if (kd < d16) {
+            const int dim = kd * 16 + g;
+            float* base = cO + (size_t)warp * DEC_HEADS * d;
+            base[(2 * tq) * d + dim] = oT[kd][0];
+            base[(2 * tq + 1) * d + dim] = oT[kd][1];
+            base[(2 * tq) * d + dim + 8] = oT[kd][2];
+            base[(2 * tq + 1) * d + dim + 8] = oT[kd][3];
         }
     }
     if (tq == 0) {
-        cML[((warp * 16 + g) << 1)] = m0;      cML[((warp * 16 + g) << 1) + 1] = l0;
-        cML[((warp * 16 + g + 8) << 1)] = m1;  cML[((warp * 16 + g + 8) << 1) + 1] = l1;
+        cML[(warp * DEC_HEADS + g) * 2] = m_run;
+        cML[(warp * DEC_HEADS + g) * 2 + 1] = l_run;
     }
     __syncthreads();
     for (int idx = threadIdx.x; idx < nheads * d; idx += NTHREADS) {
         const int row = idx / d, col = idx - row * d;
         float M = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) M = fmaxf(M, cML[(w * 16 + row) * 2]);
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, cML[(w * DEC_HEADS + row) * 2]);
         const float Ms = M == -INFINITY ? 0.f : M;
         float acc = 0.f, L = 0.f;
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
-            const float sc = exp2f(cML[(w * 16 + row) * 2] - Ms);
-            acc += sc * cO[(w * 16 + row) * d + col];
-            L += sc * cML[(w * 16 + row) * 2 + 1];
+            const float sc = exp2f(cML[(w * DEC_HEADS + row) * 2] - Ms);
+            acc += sc * cO[((size_t)w * DEC_HEADS + row) * d + col];
+            L += sc * cML[(w * DEC_HEADS + row) * 2 + 1];
         }
         const size_t base = ((size_t)ti * nh + h0 + row) * num_splits + split;
         part_o[base * d + col] = acc;
@@ -468,8 +503,9 @@ __global__ void decode_reduce_kernel(const float* __restrict__ part_o, const flo
 
 static size_t prefill_smem(int d) { return (size_t)(64 + 2 * 2 * BN) * (d + PAD) * sizeof(bf16); }
 static size_t decode_smem(int d) {
-    const size_t stages = (size_t)(16 + DEC_STAGES * 2 * BN) * (d + PAD) * sizeof(bf16);
-    const size_t combine = (size_t)16 * (d + PAD) * sizeof(bf16) + (size_t)(4 * 16 * d + 4 * 16 * 2) * sizeof(float);
+    // stages (+ a separate Q tile for the largest head-size class); the end-of-kernel combine reuses them
+    const size_t stages = (size_t)((d > 128 ? 16 : 0) + DEC_STAGES * 2 * BN) * (d + PAD) * sizeof(bf16);
+    const size_t combine = (size_t)(4 * DEC_HEADS * d + 4 * DEC_HEADS * 2) * sizeof(float);
     return stages > combine ? stages : combine;
 }
 
@@ -508,13 +544,15 @@ extern "C" int rg_decode_attention(const void* q, int q_stride, void* out, const
     const float scale_log2 = scale * 1.4426950408889634f;
     const size_t smem = decode_smem(d);
     const int group = nh / nkv;
-    const int head_tiles = (group + 15) / 16;
+    const int head_tiles = (group + DEC_HEADS - 1) / DEC_HEADS;
+    int page_shift = -1;                                            // log2 of the page size when it is a power of two
+    for (int b = 0; b < 31; ++b) if (page_size == (1 << b)) page_shift = b;
     if (num_splits > 65535 || nkv * head_tiles > 65535) return RG_ERR_UNSUPPORTED;
     dim3 grid(n_tokens, nkv * head_tiles, num_splits);
 #define RG_DECODE(DM) { int e = allow_smem(decode_attention_kernel<DM>, smem); if (e) return e; \
     decode_attention_kernel<DM><<<grid, NTHREADS, smem, s>>>((const bf16*)q, q_stride, (const bf16*)kv_cache, \
-        block_table, max_blocks, rows, req_of_token, positions, part_o, part_ml, nh, nkv, d, page_size, window, \
-        scale_log2, num_splits, head_tiles); }
+        block_table, max_blocks, rows, req_of_token, positions, part_o, part_ml, nh, nkv, d, page_size, page_shift, \
+        window, scale_log2, num_splits, head_tiles); }
     if (d <= 64) RG_DECODE(64) else if (d <= 128) RG_DECODE(128) else RG_DECODE(256)
 #undef RG_DECODE
     int e = (int)cudaGetLastError();

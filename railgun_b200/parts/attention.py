@@ -84,7 +84,7 @@ class PagedAttention(Mixer):
             return ops.paged_attention_general(qkv, qkv.shape[1], cache.kv, table, batch.req_of_token,
                                                batch.positions, nh, nkv, d, self.window, self.scale)
         out = torch.empty((qkv.shape[0], nh * d), dtype=qkv.dtype, device=qkv.device)
-        kv_tiles = nkv * (-(-(nh // nkv) // 16))
+        kv_tiles = nkv * (-(-(nh // nkv) // 8))
         if batch.decode_only:
             n = batch.num_tokens
             ops.decode_attention(qkv, qkv.shape[1], out, cache.kv, table, None, n, batch.req_of_token,
