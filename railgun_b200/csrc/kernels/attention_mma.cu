@@ -51,38 +51,62 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 2^x for x <= 0 (or -inf -> 0): the hardware approximation (2 ulp), in 32-bit
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
 // Gathering BN keys (rows key0 .. key0+BN-1 of a request) of K and V for one kv head into shared memory
-// is done row by row: thread t handles half of row t/2.  The page of a row is looked up one tile ahead
-// (lookup_page) so that the table read is off the critical path when the copies are issued (issue_kv_rows).
-// Rows at or beyond key_end have page -1 and are zero-filled.  sK, sV: [BN][d + PAD].
-__device__ __forceinline__ int lookup_page(const int* __restrict__ bt, int key0, int key_end, int page_size) {
-    const int key = key0 + (threadIdx.x >> 1);
-    return key < key_end ? bt[key / page_size] : -1;
-}
-__device__ __forceinline__ void issue_kv_rows(bf16* sK, bf16* sV, const bf16* __restrict__ kv_cache, int page,
-                                              int key0, int kvh, int nkv, int d, int page_size) {
-    const int row = threadIdx.x >> 1, half = threadIdx.x & 1;     // 128 threads: 64 rows x 2
-    const bool valid = page >= 0;
-    const bf16* ksrc = kv_cache;
-    const bf16* vsrc = kv_cache;
-    if (valid) {
-        const int off = (key0 + row) % page_size;
+// is done in 16-byte pieces.  The page of a piece's row is looked up one tile ahead so that the table read
+// is off the critical path when the copies are issued.  Rows at or beyond key_end have page -1 and are
+// zero-filled.  sK, sV: [BN][d + PAD].
+// The same rule for the 64-row tiles all four warps of the prefill kernel share: piece idx = threadIdx.x +
+// 128 j over 64 rows x d/8 pieces, consecutive threads on consecutive 16-byte pieces of a row.
+template <int KD>
+struct TileGather {
+    int row[KD], col[KD];
+    __device__ __forceinline__ void init(int d) {
+        const int d8 = d >> 3;
+#pragma unroll
+        for (int j = 0; j < KD; ++j) {
+            const int idx = threadIdx.x + NTHREADS * j;            // 64 d/8 = 8 d pieces
+            row[j] = idx < 8 * d ? idx / d8 : -1;
+            col[j] = (idx % d8) * 8;
+        }
+    }
+    __device__ __forceinline__ void pages(const int* __restrict__ bt, int key0, int key_end, int page_size,
+                                          int (&pg)[KD]) const {
+#pragma unroll
+        for (int j = 0; j < KD; ++j) {
+            const int key = key0 + row[j];
+            pg[j] = (row[j] >= 0 && key < key_end) ? bt[key / page_size] : -1;
+        }
+    }
+    __device__ __forceinline__ void issue(bf16* sK, bf16* sV, const bf16* __restrict__ kv_cache, const int (&pg)[KD],
+                                          int key0, int kvh, int nkv, int d, int page_size) const {
+        const int stride = d + PAD;
         const size_t page_elems = (size_t)2 * nkv * page_size * d;
-        ksrc = kv_cache + (size_t)page * page_elems + ((size_t)kvh * page_size + off) * d;
-        vsrc = ksrc + (size_t)nkv * page_size * d;
+        const size_t v_off = (size_t)nkv * page_size * d;
+#pragma unroll
+        for (int j = 0; j < KD; ++j) {
+            if (row[j] >= 0) {
+                const bool valid = pg[j] >= 0;
+                const bf16* ksrc = kv_cache;
+                if (valid)
+                    ksrc = kv_cache + (size_t)pg[j] * page_elems +
+                           ((size_t)kvh * page_size + (key0 + row[j]) % page_size) * d + col[j];
+                cp_async16(sK + row[j] * stride + col[j], ksrc, valid);
+                cp_async16(sV + row[j] * stride + col[j], ksrc + (valid ? v_off : 0), valid);
+            }
+        }
     }
-    const int stride = d + PAD;
-    const int chunks = d >> 3;
-    for (int c = half; c < chunks; c += 2) {
-        cp_async16(sK + row * stride + c * 8, ksrc + c * 8, valid);
-        cp_async16(sV + row * stride + c * 8, vsrc + c * 8, valid);
-    }
-}
+};
 
 // ---------------------------------------------------------------------------------------------------
 // Prefill: one CTA per (query tile of up to 64 consecutive positions of one request, head).
@@ -124,10 +148,13 @@ prefill_attention_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
             cp_async16(sQ + row * stride + c * 8, src, valid);
         }
     }
-    issue_kv_rows(sKV, sKV + BN * stride, kv_cache, lookup_page(bt, kt0 * BN, hi + 1, page_size), kt0 * BN, kvh, nkv,
-                  d, page_size);
+    TileGather<KD> tg;
+    tg.init(d);
+    int page_next[KD];
+    tg.pages(bt, kt0 * BN, hi + 1, page_size, page_next);
+    tg.issue(sKV, sKV + BN * stride, kv_cache, page_next, kt0 * BN, kvh, nkv, d, page_size);
     cp_async_commit();
-    int page_next = kt0 + 1 <= kt1 ? lookup_page(bt, (kt0 + 1) * BN, hi + 1, page_size) : -1;
+    tg.pages(bt, (kt0 + 1) * BN, hi + 1, page_size, page_next);    // beyond the last key: all -1
 
     uint32_t qf[Q_IN_REGS ? KD : 1][4];
     float o[ND][4];
@@ -147,9 +174,9 @@ prefill_attention_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
         bf16* sV = sK + BN * stride;
         if (kt + 1 <= kt1) {
             bf16* nK = sKV + (stage ^ 1) * stage_elems;
-            issue_kv_rows(nK, nK + BN * stride, kv_cache, page_next, (kt + 1) * BN, kvh, nkv, d, page_size);
+            tg.issue(nK, nK + BN * stride, kv_cache, page_next, (kt + 1) * BN, kvh, nkv, d, page_size);
             cp_async_commit();
-            page_next = kt + 2 <= kt1 ? lookup_page(bt, (kt + 2) * BN, hi + 1, page_size) : -1;
+            tg.pages(bt, (kt + 2) * BN, hi + 1, page_size, page_next);
             cp_async_wait<1>();
         } else {
             cp_async_wait<0>();
@@ -266,7 +293,9 @@ prefill_attention_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
 // accumulated transposed, O^T[dim, head] += V^T[dim, key] P^T[key, head], so that the softmax and the
 // rescaling only cost work for 8 head columns and P feeds the second product straight from registers.
 // ---------------------------------------------------------------------------------------------------
+#ifndef DEC_STAGES
 #define DEC_STAGES 3
+#endif
 #define DEC_HEADS 8        // query heads per CTA
 
 template <int DMAX>
@@ -317,30 +346,69 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
     }
     const int n_tiles = (k_end - k_begin + BN - 1) / BN;
 
-    // this thread's part of the gathering: half of row (threadIdx.x / 2) of every tile
-    const int my_row = threadIdx.x >> 1, my_half = threadIdx.x & 1;
+    // This warp gathers its own 16 rows of every tile.  Consecutive lanes take consecutive 16-byte pieces
+    // of a row, so one instruction covers whole 128-byte lines (few, wide requests to L2).
     const size_t page_elems = (size_t)2 * nkv * page_size * d;
     const size_t v_off = (size_t)nkv * page_size * d;
-    const int chunks = d8;
-    auto page_of = [&](int key0) -> int {
-        const int key = key0 + my_row;
-        if (key >= k_end) return -1;
-        return bt[page_shift >= 0 ? key >> page_shift : key / page_size];
-    };
-    auto gather = [&](int stage, int page, int key0) {
-        bf16* sK = sKV + stage * stage_elems + my_row * stride;
-        bf16* sV = sK + BN * stride;
-        const bool valid = page >= 0;
-        const bf16* ksrc = kv_cache;
-        if (valid) {
-            const int key = key0 + my_row;
-            const int off = page_shift >= 0 ? key & (page_size - 1) : key % page_size;
-            ksrc = kv_cache + (size_t)page * page_elems + ((size_t)kvh * page_size + off) * d;
+    int g_row[KD], g_col[KD];                                      // piece j of this lane: row in the warp's 16, column
+#pragma unroll
+    for (int j = 0; j < KD; ++j) {
+        const int idx = lane + 32 * j;                             // over 16 rows x d/8 pieces = 2 d pieces
+        g_row[j] = idx < 2 * d ? idx / d8 : -1;
+        g_col[j] = (idx % d8) * 8;
+    }
+    // When a page holds a multiple of 16 tokens, the warp's 16 rows of a tile are one contiguous run of the
+    // cache (tiles start at multiples of 16): one table entry, pieces at consecutive addresses.
+    const bool one_page = page_shift >= 4;
+    int g_dst[KD];                                                 // shared-memory offset of piece j within the warp's rows
+#pragma unroll
+    for (int j = 0; j < KD; ++j) g_dst[j] = g_row[j] * stride + g_col[j];
+    auto pages_of = [&](int key0, int (&pg)[KD]) {                 // page of every piece's row (-1: no such key)
+        if (one_page) {
+            const int key = key0 + warp * 16;                      // the same page for the whole warp
+            pg[0] = key < k_end ? bt[key >> page_shift] : -1;
+            return;
         }
-        const bf16* vsrc = ksrc + (valid ? v_off : 0);
-        for (int c = my_half; c < chunks; c += 2) {
-            cp_async16(sK + c * 8, ksrc + c * 8, valid);
-            cp_async16(sV + c * 8, vsrc + c * 8, valid);
+#pragma unroll
+        for (int j = 0; j < KD; ++j) {
+            const int key = key0 + warp * 16 + g_row[j];
+            pg[j] = (g_row[j] >= 0 && key < k_end) ? bt[page_shift >= 0 ? key >> page_shift : key / page_size] : -1;
+        }
+    };
+    auto gather = [&](int stage, const int (&pg)[KD], int key0) {
+        bf16* sK = sKV + stage * stage_elems + warp * 16 * stride;
+        bf16* sV = sK + BN * stride;
+        if (one_page) {
+            const int key = key0 + warp * 16;
+            const bool page_ok = pg[0] >= 0;
+            const bf16* base = kv_cache;
+            if (page_ok)
+                base = kv_cache + (size_t)pg[0] * page_elems + ((size_t)kvh * page_size + (key & (page_size - 1))) * d;
+            const int rows_ok = k_end - key;                        // rows at or beyond it are zero-filled
+#pragma unroll
+            for (int j = 0; j < KD; ++j) {
+                if (g_row[j] >= 0) {
+                    const bool valid = page_ok && g_row[j] < rows_ok;
+                    const bf16* ksrc = valid ? base + (lane + 32 * j) * 8 : kv_cache;
+                    cp_async16(sK + g_dst[j], ksrc, valid);
+                    cp_async16(sV + g_dst[j], ksrc + (valid ? v_off : 0), valid);
+                }
+            }
+            return;
+        }
+#pragma unroll
+        for (int j = 0; j < KD; ++j) {
+            if (g_row[j] >= 0) {
+                const bool valid = pg[j] >= 0;
+                const bf16* ksrc = kv_cache;
+                if (valid) {
+                    const int key = key0 + warp * 16 + g_row[j];
+                    const int off = page_shift >= 0 ? key & (page_size - 1) : key % page_size;
+                    ksrc = kv_cache + (size_t)pg[j] * page_elems + ((size_t)kvh * page_size + off) * d + g_col[j];
+                }
+                cp_async16(sK + g_dst[j], ksrc, valid);
+                cp_async16(sV + g_dst[j], ksrc + (valid ? v_off : 0), valid);
+            }
         }
     };
 
@@ -351,12 +419,16 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
         cp_async16(sQ + row * stride + c * 8, src, valid);
     }
     cp_async_commit();
+    int page_next[KD];
 #pragma unroll
     for (int st = 0; st < DEC_STAGES - 1; ++st) {
-        if (st < n_tiles) gather(st, page_of(k_begin + st * BN), k_begin + st * BN);
+        if (st < n_tiles) {
+            pages_of(k_begin + st * BN, page_next);
+            gather(st, page_next, k_begin + st * BN);
+        }
         cp_async_commit();
     }
-    int page_next = DEC_STAGES - 1 < n_tiles ? page_of(k_begin + (DEC_STAGES - 1) * BN) : -1;
+    pages_of(k_begin + (DEC_STAGES - 1) * BN, page_next);            // beyond the split: all -1
 
     float oT[KD][4];                                                // O^T: dims (16 kd + g, + 8) x heads (2 tq, 2 tq + 1)
 #pragma unroll
@@ -384,7 +456,7 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
             const int nt = it + DEC_STAGES - 1;
             if (nt < n_tiles) gather(nt % DEC_STAGES, page_next, k_begin + nt * BN);
             cp_async_commit();
-            page_next = nt + 1 < n_tiles ? page_of(k_begin + (nt + 1) * BN) : -1;
+            pages_of(k_begin + (nt + 1) * BN, page_next);
             cp_async_wait<DEC_STAGES - 1>();
         }
         __syncwarp();
@@ -403,19 +475,22 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
                 }
             }
             // head g, keys key_base + 2 tq + {0, 1} (s0) and + 8 (s1); rows 8..15 of the tile are padding
-            const int k0 = key_base + tq * 2;
-            const float v00 = (k0 < k_end && k0 >= lo) ? s0[0] * scale_log2 : -INFINITY;
-            const float v01 = (k0 + 1 < k_end && k0 + 1 >= lo) ? s0[1] * scale_log2 : -INFINITY;
-            const float v10 = (k0 + 8 < k_end && k0 + 8 >= lo) ? s1[0] * scale_log2 : -INFINITY;
-            const float v11 = (k0 + 9 < k_end && k0 + 9 >= lo) ? s1[1] * scale_log2 : -INFINITY;
+            float v00 = s0[0] * scale_log2, v01 = s0[1] * scale_log2, v10 = s1[0] * scale_log2, v11 = s1[1] * scale_log2;
+            if (key_base + 16 > k_end || key_base < lo) {            // an edge tile: some of its keys are not attended
+                const int k0 = key_base + tq * 2;
+                if (!(k0 < k_end && k0 >= lo)) v00 = -INFINITY;
+                if (!(k0 + 1 < k_end && k0 + 1 >= lo)) v01 = -INFINITY;
+                if (!(k0 + 8 < k_end && k0 + 8 >= lo)) v10 = -INFINITY;
+                if (!(k0 + 9 < k_end && k0 + 9 >= lo)) v11 = -INFINITY;
+            }
             float mx = fmaxf(fmaxf(v00, v01), fmaxf(v10, v11));
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
             const float mn = fmaxf(m_run, mx);
             const float ms = mn == -INFINITY ? 0.f : mn;
-            const float alpha = exp2f(m_run - ms);
+            const float alpha = ex2(m_run - ms);
             m_run = mn;
-            const float p00 = exp2f(v00 - ms), p01 = exp2f(v01 - ms), p10 = exp2f(v10 - ms), p11 = exp2f(v11 - ms);
+            const float p00 = ex2(v00 - ms), p01 = ex2(v01 - ms), p10 = ex2(v10 - ms), p11 = ex2(v11 - ms);
             l_run = l_run * alpha + (p00 + p01) + (p10 + p11);       // per-thread partial; summed over tq at the end
             const uint32_t pb0 = pack_bf16(p00, p01), pb1 = pack_bf16(p10, p11);
             if (__any_sync(0xffffffffu, alpha != 1.f)) {             // some head's max moved: rescale

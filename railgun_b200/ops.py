@@ -265,10 +265,13 @@ def prefill_attention(q, q_stride: int, out, kv_cache, block_table, tiles, posit
 
 
 def decode_splits(n_tokens: int, kv_tiles: int, max_context: int) -> int:
-    """How many parts each context is cut into: enough thread blocks to fill
-    the GPU (about 592 of this kernel are resident), at least 64 keys each."""
-    want = -(-592 // max(1, n_tokens * kv_tiles))
-    return max(1, min(want, -(-max_context // 64), 256))
+    """How many parts each context is cut into.  Measured on B200: the split
+    kernel runs best when all its thread blocks are resident at once (4 per SM,
+    592 in all) and each part has at least 256 keys; more parts only add
+    partial results to reduce."""
+    by_residency = 592 // max(1, n_tokens * kv_tiles)
+    by_length = -(-max_context // 256)
+    return max(1, min(by_residency, by_length, 256))
 
 
 def decode_attention(q, q_stride: int, out, kv_cache, block_table, rows, n_tokens: int, req_of_token, positions,
