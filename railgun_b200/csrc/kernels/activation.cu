@@ -6,6 +6,8 @@
 
 template <typename A>
 __global__ void silu_mul_kernel(const A* __restrict__ gu, A* __restrict__ out, int I, size_t total) {
+    pdl_wait();
+    pdl_trigger();
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
     const size_t t = idx / I;
@@ -19,6 +21,8 @@ __global__ void silu_mul_kernel(const A* __restrict__ gu, A* __restrict__ out, i
 // rows), as the decode GEMM's fused epilogue reads it: out[t, 8b + j] = silu(gu[t, 16b + j]) * gu[t, 16b + 8 + j].
 template <typename A>
 __global__ void silu_mul_interleaved_kernel(const A* __restrict__ gu, A* __restrict__ out, int I, size_t total) {
+    pdl_wait();
+    pdl_trigger();
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
     const size_t t = idx / I;
@@ -37,11 +41,12 @@ extern "C" int rg_silu_mul_interleaved(const void* gu, void* out, int dtype, int
     const int threads = 256;
     const unsigned blocks = (unsigned)((total + threads - 1) / threads);
     if (dtype == RG_DTYPE_BF16)
-        silu_mul_interleaved_kernel<bf16><<<blocks, threads, 0, s>>>((const bf16*)gu, (bf16*)out, I, total);
-    else if (dtype == RG_DTYPE_F32)
-        silu_mul_interleaved_kernel<float><<<blocks, threads, 0, s>>>((const float*)gu, (float*)out, I, total);
-    else return RG_ERR_UNSUPPORTED;
-    return RG_LAUNCH_RESULT();
+        return rg_launch(silu_mul_interleaved_kernel<bf16>, dim3(blocks), dim3(threads), 0, s, 1, (const bf16*)gu,
+                         (bf16*)out, I, total);
+    if (dtype == RG_DTYPE_F32)
+        return rg_launch(silu_mul_interleaved_kernel<float>, dim3(blocks), dim3(threads), 0, s, 1, (const float*)gu,
+                         (float*)out, I, total);
+    return RG_ERR_UNSUPPORTED;
 }
 
 extern "C" int rg_silu_mul(const void* gu, void* out, int dtype, int T, int I, void* stream) {
@@ -51,9 +56,10 @@ extern "C" int rg_silu_mul(const void* gu, void* out, int dtype, int T, int I, v
     const int threads = 256;
     const unsigned blocks = (unsigned)((total + threads - 1) / threads);
     if (dtype == RG_DTYPE_BF16)
-        silu_mul_kernel<bf16><<<blocks, threads, 0, s>>>((const bf16*)gu, (bf16*)out, I, total);
-    else if (dtype == RG_DTYPE_F32)
-        silu_mul_kernel<float><<<blocks, threads, 0, s>>>((const float*)gu, (float*)out, I, total);
-    else return RG_ERR_UNSUPPORTED;
-    return RG_LAUNCH_RESULT();
+        return rg_launch(silu_mul_kernel<bf16>, dim3(blocks), dim3(threads), 0, s, 1, (const bf16*)gu, (bf16*)out, I,
+                         total);
+    if (dtype == RG_DTYPE_F32)
+        return rg_launch(silu_mul_kernel<float>, dim3(blocks), dim3(threads), 0, s, 1, (const float*)gu, (float*)out, I,
+                         total);
+    return RG_ERR_UNSUPPORTED;
 }

@@ -26,6 +26,8 @@ __global__ void paged_attention_general_kernel(
     float* qs = smem;                    // [d]
     float* ps = qs + d;                  // [ATT_THREADS]
     float* scratch = ps + ATT_THREADS;   // [33]
+    pdl_wait();
+    pdl_trigger();
     const int t = blockIdx.x, h = blockIdx.y;
     const int kvh = h / (nh / nkv);
     const int r = req_of_token[t];
@@ -88,13 +90,12 @@ extern "C" int rg_paged_attention_general(
     dim3 grid(T, nh);
     const size_t smem = (size_t)(d + ATT_THREADS + 33) * sizeof(float);
     if (dtype == RG_DTYPE_BF16)
-        paged_attention_general_kernel<bf16><<<grid, ATT_THREADS, smem, s>>>(
-            (const bf16*)q, q_stride, (bf16*)out, (const bf16*)kv_cache, block_table, max_blocks,
-            req_of_token, positions, nh, nkv, d, page_size, window, scale);
-    else if (dtype == RG_DTYPE_F32)
-        paged_attention_general_kernel<float><<<grid, ATT_THREADS, smem, s>>>(
-            (const float*)q, q_stride, (float*)out, (const float*)kv_cache, block_table, max_blocks,
-            req_of_token, positions, nh, nkv, d, page_size, window, scale);
-    else return RG_ERR_UNSUPPORTED;
-    return RG_LAUNCH_RESULT();
+        return rg_launch(paged_attention_general_kernel<bf16>, grid, dim3(ATT_THREADS), smem, s, 1,
+                         (const bf16*)q, q_stride, (bf16*)out, (const bf16*)kv_cache, block_table, max_blocks,
+                         req_of_token, positions, nh, nkv, d, page_size, window, scale);
+    if (dtype == RG_DTYPE_F32)
+        return rg_launch(paged_attention_general_kernel<float>, grid, dim3(ATT_THREADS), smem, s, 1,
+                         (const float*)q, q_stride, (float*)out, (const float*)kv_cache, block_table, max_blocks,
+                         req_of_token, positions, nh, nkv, d, page_size, window, scale);
+    return RG_ERR_UNSUPPORTED;
 }

@@ -127,6 +127,8 @@ prefill_attention_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
     bf16* sKV = sQ + 64 * stride;                                 // 2 stages x (K [BN][stride], V [BN][stride])
     const int stage_elems = 2 * BN * stride;
 
+    pdl_wait();
+    pdl_trigger();
     const int tile = blockIdx.x, h = blockIdx.y;
     const int row0 = tiles[tile * 3 + 0], nrows = tiles[tile * 3 + 1], r = tiles[tile * 3 + 2];
     const int kvh = h / (nh / nkv);
@@ -316,6 +318,8 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
     // last stage, which is first filled inside the loop
     bf16* sQ = Q_IN_REGS ? sKV + (DEC_STAGES - 1) * stage_elems : sKV + DEC_STAGES * stage_elems;
 
+    pdl_wait();
+    pdl_trigger();
     const int split = blockIdx.z;
     const int kvh = blockIdx.y / head_tiles, ht = blockIdx.y - kvh * head_tiles;
     const int ti = blockIdx.x;
@@ -557,6 +561,8 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
 __global__ void decode_reduce_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                      bf16* __restrict__ out, const int* __restrict__ rows, int nh, int d,
                                      int num_splits) {
+    pdl_wait();
+    pdl_trigger();
     const int ti = blockIdx.x, h = blockIdx.y;
     const int t = rows ? rows[ti] : ti;
     const size_t base = ((size_t)ti * nh + h) * num_splits;
@@ -600,11 +606,11 @@ extern "C" int rg_prefill_attention(const void* q, int q_stride, void* out, cons
     const size_t smem = prefill_smem(d);
     dim3 grid(n_tiles, nh);
 #define RG_PREFILL(DM) { int e = allow_smem(prefill_attention_kernel<DM>, smem); if (e) return e; \
-    prefill_attention_kernel<DM><<<grid, NTHREADS, smem, s>>>((const bf16*)q, q_stride, (bf16*)out, \
-        (const bf16*)kv_cache, block_table, max_blocks, tiles, positions, nh, nkv, d, page_size, window, scale_log2); }
+    return rg_launch(prefill_attention_kernel<DM>, grid, dim3(NTHREADS), smem, s, 1, (const bf16*)q, q_stride, \
+        (bf16*)out, (const bf16*)kv_cache, block_table, max_blocks, tiles, positions, nh, nkv, d, page_size, window, \
+        scale_log2); }
     if (d <= 64) RG_PREFILL(64) else if (d <= 128) RG_PREFILL(128) else RG_PREFILL(256)
 #undef RG_PREFILL
-    return RG_LAUNCH_RESULT();
 }
 
 // Scratch the caller provides: part_o floats = n_tokens * nh * num_splits * d; part_ml = n_tokens * nh * num_splits * 2.
@@ -624,17 +630,17 @@ extern "C" int rg_decode_attention(const void* q, int q_stride, void* out, const
     for (int b = 0; b < 31; ++b) if (page_size == (1 << b)) page_shift = b;
     if (num_splits > 65535 || nkv * head_tiles > 65535) return RG_ERR_UNSUPPORTED;
     dim3 grid(n_tokens, nkv * head_tiles, num_splits);
-#define RG_DECODE(DM) { int e = allow_smem(decode_attention_kernel<DM>, smem); if (e) return e; \
-    decode_attention_kernel<DM><<<grid, NTHREADS, smem, s>>>((const bf16*)q, q_stride, (const bf16*)kv_cache, \
-        block_table, max_blocks, rows, req_of_token, positions, part_o, part_ml, nh, nkv, d, page_size, page_shift, \
-        window, scale_log2, num_splits, head_tiles); }
+    int e = 0;
+#define RG_DECODE(DM) { e = allow_smem(decode_attention_kernel<DM>, smem); if (e) return e; \
+    e = rg_launch(decode_attention_kernel<DM>, grid, dim3(NTHREADS), smem, s, 1, (const bf16*)q, q_stride, \
+        (const bf16*)kv_cache, block_table, max_blocks, rows, req_of_token, positions, part_o, part_ml, nh, nkv, d, \
+        page_size, page_shift, window, scale_log2, num_splits, head_tiles); }
     if (d <= 64) RG_DECODE(64) else if (d <= 128) RG_DECODE(128) else RG_DECODE(256)
 #undef RG_DECODE
-    int e = (int)cudaGetLastError();
     if (e) return e;
     dim3 rgrid(n_tokens, nh);
-    decode_reduce_kernel<<<rgrid, d >= 128 ? 128 : 64, 0, s>>>(part_o, part_ml, (bf16*)out, rows, nh, d, num_splits);
-    return RG_LAUNCH_RESULT();
+    return rg_launch(decode_reduce_kernel, rgrid, dim3(d >= 128 ? 128 : 64), 0, s, 1, (const float*)part_o,
+                     (const float*)part_ml, (bf16*)out, rows, nh, d, num_splits);
 }
 
 // ---------------------------------------------------------------------------------------------------

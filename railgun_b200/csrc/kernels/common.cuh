@@ -62,3 +62,44 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 }
 
 #define RG_LAUNCH_RESULT() ((int)cudaGetLastError())
+
+// Programmatic dependent launch.  A kernel launched with the attribute may start while the kernel before it
+// in the stream is still running; it must not touch anything that kernel (or an earlier one) reads or writes
+// before pdl_wait(), which returns once the previous kernel has completed and its writes are visible.  Only
+// constants (weights) may be read earlier.  pdl_trigger() lets the next kernel start launching.  Without the
+// attribute both are no-ops.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+static int rg_pdl_enabled = 0;
+extern "C" void rg_set_pdl(int on) { rg_pdl_enabled = on; }
+
+// Launch through cudaLaunchKernelEx so that the launch can carry attributes (dependent launch, clusters).
+template <typename... KArgs, typename... Args>
+static int rg_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, int cluster_x,
+                     Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (rg_pdl_enabled) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    if (cluster_x > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = cluster_x;
+        attr[n].val.clusterDim.y = 1;
+        attr[n].val.clusterDim.z = 1;
+        ++n;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+    if (e != cudaSuccess) return (int)e;
+    return (int)cudaGetLastError();
+}

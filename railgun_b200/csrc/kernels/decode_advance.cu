@@ -11,6 +11,8 @@ __global__ void decode_advance_kernel(int* __restrict__ token_ids, const int* __
                                       int* __restrict__ start_pos, int* __restrict__ slots,
                                       const int* __restrict__ block_table, int max_blocks, int page_size, int B,
                                       int* __restrict__ out_tokens, int* __restrict__ step_counter, int max_steps) {
+    pdl_wait();
+    pdl_trigger();
     const int b = blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= B) return;
     const int step = *step_counter;
@@ -26,7 +28,11 @@ __global__ void decode_advance_kernel(int* __restrict__ token_ids, const int* __
     slots[b] = blk < max_blocks ? block_table[(size_t)b * max_blocks + blk] * page_size + pos % page_size : -1;
 }
 
-__global__ void bump_counter_kernel(int* c) { *c += 1; }
+__global__ void bump_counter_kernel(int* c) {
+    pdl_wait();
+    pdl_trigger();
+    *c += 1;
+}
 
 extern "C" int rg_decode_advance(int* token_ids, const int* sampled, int* positions, int* context_lens,
                                  int* start_pos, int* slots, const int* block_table, int max_blocks,
@@ -34,9 +40,9 @@ extern "C" int rg_decode_advance(int* token_ids, const int* sampled, int* positi
                                  void* stream) {
     if (B <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
-    decode_advance_kernel<<<(B + 127) / 128, 128, 0, s>>>(token_ids, sampled, positions, context_lens, start_pos,
-                                                          slots, block_table, max_blocks, page_size, B, out_tokens,
-                                                          step_counter, max_steps);
-    bump_counter_kernel<<<1, 1, 0, s>>>(step_counter);
-    return RG_LAUNCH_RESULT();
+    int e = rg_launch(decode_advance_kernel, dim3((B + 127) / 128), dim3(128), 0, s, 1, token_ids, sampled, positions,
+                      context_lens, start_pos, slots, block_table, max_blocks, page_size, B, out_tokens, step_counter,
+                      max_steps);
+    if (e) return e;
+    return rg_launch(bump_counter_kernel, dim3(1), dim3(1), 0, s, 1, step_counter);
 }

@@ -6,6 +6,8 @@
 template <typename W>
 __global__ void embed_kernel(const int* __restrict__ ids, const W* __restrict__ table,
                              float* __restrict__ out, int H, int V) {
+    pdl_wait();
+    pdl_trigger();
     const int t = blockIdx.x;
     const int id = ids[t];
     float* o = out + (size_t)t * H;
@@ -23,10 +25,8 @@ extern "C" int rg_embedding(const int* ids, const void* table, int table_dtype, 
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = H >= 1024 ? 256 : 128;
     if (table_dtype == RG_DTYPE_BF16)
-        embed_kernel<bf16><<<T, threads, 0, s>>>(ids, (const bf16*)table, out, H, V);
-    else if (table_dtype == RG_DTYPE_F32)
-        embed_kernel<float><<<T, threads, 0, s>>>(ids, (const float*)table, out, H, V);
-    else
-        return RG_ERR_UNSUPPORTED;
-    return RG_LAUNCH_RESULT();
+        return rg_launch(embed_kernel<bf16>, dim3(T), dim3(threads), 0, s, 1, ids, (const bf16*)table, out, H, V);
+    if (table_dtype == RG_DTYPE_F32)
+        return rg_launch(embed_kernel<float>, dim3(T), dim3(threads), 0, s, 1, ids, (const float*)table, out, H, V);
+    return RG_ERR_UNSUPPORTED;
 }

@@ -16,6 +16,8 @@
 // (crates/vllm-models/src/llama/architecture.rs:81-85).  The reference runs
 // these products through cuBLAS (crates/vllm-models/src/llama/attention.rs:94-96,133).
 #include "common.cuh"
+#include <cooperative_groups.h>
+namespace cg = cooperative_groups;
 
 #define EPI_NONE 0
 #define EPI_SILU_MUL 1
@@ -36,16 +38,22 @@ __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// One block: 16 rows of W (n0 .. n0+15), all of K split over NW warps in interleaved 128-wide pieces.
+// One block: 16 rows of W (n0 .. n0+15) and one slice of K, split over NW warps in interleaved 128-wide
+// pieces.  CS blocks of a cluster share the 16 rows and take one K slice each; block 0 of the cluster adds
+// the slices' sums, read from the other blocks' shared memory, in rank order (the same order every time).
 // MT: batch rows / 8 (rounded up).  x rows are ldx elements apart.  K % 8 == 0.
-template <int MT, int NW, int EPI, typename OUT>
+template <int MT, int NW, int CS, int EPI, typename OUT>
 __global__ void __launch_bounds__(NW * 32)
 skinny_gemm_kernel(const bf16* __restrict__ W, const bf16* __restrict__ x, int ldx, OUT* __restrict__ out, int ldo,
                    int M, int N, int K) {
-    extern __shared__ float red[];                     // [NW][16][8 * MT]
+    extern __shared__ float red[];                     // [NW][16][8 * MT], then the block's sum [16][8 * MT]
+    constexpr int COLS = 8 * MT;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, tq = lane & 3;
-    const int n0 = blockIdx.x * 16;
+    const int rank = CS > 1 ? (int)(blockIdx.x % CS) : 0;
+    const int n0 = (int)(blockIdx.x / CS) * 16;
+    const int slice = ((K + CS * 128 - 1) / (CS * 128)) * 128;     // K slice of one block, a multiple of 128
+    const int k_lo = rank * slice, k_hi = min(K, k_lo + slice);
     const int r0 = n0 + g, r1 = n0 + g + 8;
     const bool v0 = r0 < N, v1 = r1 < N;
     const bf16* w0 = W + (size_t)(v0 ? r0 : 0) * K + tq * 8;
@@ -63,29 +71,48 @@ skinny_gemm_kernel(const bf16* __restrict__ W, const bf16* __restrict__ x, int l
     for (int j = 0; j < MT; ++j) { acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f; }
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
 
-    for (int kb = warp * 128; kb < K; kb += NW * 128) {
-        uint4 a[4], b[4];
+    // W does not depend on the kernel before this one: its first piece is requested before the wait, and
+    // every later piece one iteration ahead of its use.
+    uint4 a[4], b[4];
+    int kb = k_lo + warp * 128;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {                  // 8 loads of W in flight per thread
-            const int k = kb + c * 32;
-            const bool kin = k + tq * 8 < K;
-            a[c] = (kin && v0) ? ld_stream16(w0 + k) : zero;
-            b[c] = (kin && v1) ? ld_stream16(w1 + k) : zero;
-        }
+    for (int c = 0; c < 4; ++c) {
+        const int k = kb + c * 32;
+        const bool kin = k + tq * 8 < k_hi;
+        a[c] = (kin && v0) ? ld_stream16(w0 + k) : zero;
+        b[c] = (kin && v1) ? ld_stream16(w1 + k) : zero;
+    }
+    pdl_wait();
+    pdl_trigger();
+    for (; kb < k_hi; kb += NW * 128) {
+        uint4 xq[MT][4], an[4], bn[4];
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
             const int k = kb + c * 32;
-            const bool kin = k + tq * 8 < K;
+            const bool kin = k + tq * 8 < k_hi;
+#pragma unroll
+            for (int j = 0; j < MT; ++j) xq[j][c] = (kin && xv[j]) ? ld_cached16(xr[j] + k) : zero;
+        }
+        const int kn = kb + NW * 128;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const int k = kn + c * 32;
+            const bool kin = k + tq * 8 < k_hi;
+            an[c] = (kin && v0) ? ld_stream16(w0 + k) : zero;
+            bn[c] = (kin && v1) ? ld_stream16(w1 + k) : zero;
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
 #pragma unroll
             for (int j = 0; j < MT; ++j) {
-                const uint4 xq = (kin && xv[j]) ? ld_cached16(xr[j] + k) : zero;
-                mma16816(acc[j], a[c].x, b[c].x, a[c].y, b[c].y, xq.x, xq.y);
-                mma16816(acc[j], a[c].z, b[c].z, a[c].w, b[c].w, xq.z, xq.w);
+                mma16816(acc[j], a[c].x, b[c].x, a[c].y, b[c].y, xq[j][c].x, xq[j][c].y);
+                mma16816(acc[j], a[c].z, b[c].z, a[c].w, b[c].w, xq[j][c].z, xq[j][c].w);
             }
         }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) { a[c] = an[c]; b[c] = bn[c]; }
     }
     // the warps' partial sums -> shared memory, summed in warp order
-    constexpr int COLS = 8 * MT;
     float* mine = red + (size_t)warp * 16 * COLS;
 #pragma unroll
     for (int j = 0; j < MT; ++j) {
@@ -96,53 +123,69 @@ skinny_gemm_kernel(const bf16* __restrict__ W, const bf16* __restrict__ x, int l
         mine[(g + 8) * COLS + col + 1] = acc[j][3];
     }
     __syncthreads();
+    float* fin = red + (size_t)NW * 16 * COLS;          // [16][COLS]
+    for (int idx = threadIdx.x; idx < 16 * COLS; idx += NW * 32) {
+        float s = 0.f;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) s += red[(size_t)w * 16 * COLS + idx];
+        fin[idx] = s;
+    }
+    if (CS > 1) {
+        cg::cluster_group cluster = cg::this_cluster();
+        cluster.sync();                                 // every block's sum is in its shared memory
+        if (rank == 0) {
+            for (int idx = threadIdx.x; idx < 16 * COLS; idx += NW * 32) {
+                float s = fin[idx];
+#pragma unroll
+                for (int r = 1; r < CS; ++r) s += cluster.map_shared_rank(fin, r)[idx];
+                fin[idx] = s;
+            }
+        }
+        cluster.sync();                                 // nobody leaves while its shared memory is being read
+        if (rank != 0) return;
+    }
+    __syncthreads();
     if (EPI == EPI_NONE) {
         for (int idx = threadIdx.x; idx < 16 * COLS; idx += NW * 32) {
             const int m = idx >> 4, row = idx & 15;    // consecutive threads -> consecutive n: coalesced stores
-            if (m < M && n0 + row < N) {
-                float s = 0.f;
-#pragma unroll
-                for (int w = 0; w < NW; ++w) s += red[((size_t)w * 16 + row) * COLS + m];
-                out[(size_t)m * ldo + n0 + row] = from_f32<OUT>(s);
-            }
+            if (m < M && n0 + row < N) out[(size_t)m * ldo + n0 + row] = from_f32<OUT>(fin[row * COLS + m]);
         }
     } else {
         for (int idx = threadIdx.x; idx < 8 * COLS; idx += NW * 32) {
             const int m = idx >> 3, j = idx & 7;
             if (m < M && n0 + j + 8 < N) {
-                float gate = 0.f, up = 0.f;
-#pragma unroll
-                for (int w = 0; w < NW; ++w) {
-                    gate += red[((size_t)w * 16 + j) * COLS + m];
-                    up += red[((size_t)w * 16 + j + 8) * COLS + m];
-                }
+                const float gate = fin[j * COLS + m], up = fin[(j + 8) * COLS + m];
                 out[(size_t)m * ldo + (n0 >> 1) + j] = from_f32<OUT>(gate / (1.f + expf(-gate)) * up);
             }
         }
     }
 }
 
-template <int MT, int NW, int EPI, typename OUT>
+template <int MT, int NW, int CS, int EPI, typename OUT>
 static int launch_skinny(const bf16* W, const bf16* x, int ldx, OUT* out, int ldo, int M, int N, int K,
                          cudaStream_t s) {
-    const size_t smem = (size_t)NW * 16 * 8 * MT * sizeof(float);
+    const size_t smem = (size_t)(NW + 1) * 16 * 8 * MT * sizeof(float);
+    auto kernel = skinny_gemm_kernel<MT, NW, CS, EPI, OUT>;
     if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(skinny_gemm_kernel<MT, NW, EPI, OUT>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
-    skinny_gemm_kernel<MT, NW, EPI, OUT><<<(N + 15) / 16, NW * 32, smem, s>>>(W, x, ldx, out, ldo, M, N, K);
-    return RG_LAUNCH_RESULT();
+    return rg_launch(kernel, dim3((unsigned)(((N + 15) / 16) * CS)), dim3(NW * 32), smem, s, CS, W, x, ldx, out, ldo, M,
+                     N, K);
 }
 
 template <int EPI, typename OUT>
 static int dispatch_skinny(const bf16* W, const bf16* x, int ldx, OUT* out, int ldo, int M, int N, int K,
                            cudaStream_t s) {
-    // more warps per block when a block's 16 rows are long or the blocks are few, so that enough loads are in flight
-    const long long blocks = (N + 15) / 16;
-    const bool wide = K >= 4096 || blocks < 2 * 148;
-#define RG_SK(MT_) (wide ? launch_skinny<MT_, 16, EPI, OUT>(W, x, ldx, out, ldo, M, N, K, s) \
-                         : launch_skinny<MT_, 4, EPI, OUT>(W, x, ldx, out, ldo, M, N, K, s))
+    // Every warp should have one or two 128-wide pieces of K and all blocks should be resident at once:
+    // many row tiles -> few warps per block; few row tiles -> 16 warps; few row tiles and a long K -> K is
+    // also cut over a cluster of 4 blocks.
+    const long long tiles = (N + 15) / 16;
+    const int shape = tiles >= 16 * 148 ? 0 : (tiles >= 4 * 148 ? 1 : ((K >= 4096 && tiles < 2 * 148) ? 3 : 2));
+#define RG_SK(MT_) (shape == 0 ? launch_skinny<MT_, 4, 1, EPI, OUT>(W, x, ldx, out, ldo, M, N, K, s) \
+                  : shape == 1 ? launch_skinny<MT_, 8, 1, EPI, OUT>(W, x, ldx, out, ldo, M, N, K, s) \
+                  : shape == 2 ? launch_skinny<MT_, 16, 1, EPI, OUT>(W, x, ldx, out, ldo, M, N, K, s) \
+                               : launch_skinny<MT_, 8, 4, EPI, OUT>(W, x, ldx, out, ldo, M, N, K, s))
     if (M <= 8) return RG_SK(1);
     if (M <= 16) return RG_SK(2);
     if (M <= 32) return RG_SK(4);

@@ -15,6 +15,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const P* __restric
                                    const float* __restrict__ w, float eps, O* __restrict__ out,
                                    const int* __restrict__ rows, int H) {
     __shared__ float scratch[33];
+    pdl_wait();
+    pdl_trigger();
     const int orow = blockIdx.x;
     const int srow = rows ? rows[orow] : orow;
     float* r = resid + (size_t)srow * H;
@@ -40,6 +42,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const P* __restric
 // residual[row] += pending[row] only (a block arrangement that ends without a norm).
 template <typename P>
 __global__ void residual_add_kernel(float* __restrict__ resid, const P* __restrict__ pending, size_t n) {
+    pdl_wait();
+    pdl_trigger();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) resid[i] += to_f32(pending[i]);
 }
@@ -50,16 +54,15 @@ extern "C" int rg_add_rmsnorm(float* resid, const void* pending, int pending_dty
     if (n_out_rows <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
-#define RG_NORM(P, O) add_rmsnorm_kernel<P, O><<<n_out_rows, threads, 0, s>>>( \
+#define RG_NORM(P, O) return rg_launch(add_rmsnorm_kernel<P, O>, dim3(n_out_rows), dim3(threads), 0, s, 1, \
         resid, (const P*)pending, w, eps, (O*)out, rows, H)
     if (pending == nullptr) pending_dtype = out_dtype;
     if (pending_dtype == RG_DTYPE_BF16 && out_dtype == RG_DTYPE_BF16) RG_NORM(bf16, bf16);
-    else if (pending_dtype == RG_DTYPE_F32 && out_dtype == RG_DTYPE_F32) RG_NORM(float, float);
-    else if (pending_dtype == RG_DTYPE_F32 && out_dtype == RG_DTYPE_BF16) RG_NORM(float, bf16);
-    else if (pending_dtype == RG_DTYPE_BF16 && out_dtype == RG_DTYPE_F32) RG_NORM(bf16, float);
-    else return RG_ERR_UNSUPPORTED;
+    if (pending_dtype == RG_DTYPE_F32 && out_dtype == RG_DTYPE_F32) RG_NORM(float, float);
+    if (pending_dtype == RG_DTYPE_F32 && out_dtype == RG_DTYPE_BF16) RG_NORM(float, bf16);
+    if (pending_dtype == RG_DTYPE_BF16 && out_dtype == RG_DTYPE_F32) RG_NORM(bf16, float);
 #undef RG_NORM
-    return RG_LAUNCH_RESULT();
+    return RG_ERR_UNSUPPORTED;
 }
 
 extern "C" int rg_residual_add(float* resid, const void* pending, int pending_dtype, long long n, void* stream) {
@@ -68,9 +71,10 @@ extern "C" int rg_residual_add(float* resid, const void* pending, int pending_dt
     const int threads = 256;
     const unsigned blocks = (unsigned)((n + threads - 1) / threads);
     if (pending_dtype == RG_DTYPE_BF16)
-        residual_add_kernel<bf16><<<blocks, threads, 0, s>>>(resid, (const bf16*)pending, (size_t)n);
-    else if (pending_dtype == RG_DTYPE_F32)
-        residual_add_kernel<float><<<blocks, threads, 0, s>>>(resid, (const float*)pending, (size_t)n);
-    else return RG_ERR_UNSUPPORTED;
-    return RG_LAUNCH_RESULT();
+        return rg_launch(residual_add_kernel<bf16>, dim3(blocks), dim3(threads), 0, s, 1, resid, (const bf16*)pending,
+                         (size_t)n);
+    if (pending_dtype == RG_DTYPE_F32)
+        return rg_launch(residual_add_kernel<float>, dim3(blocks), dim3(threads), 0, s, 1, resid, (const float*)pending,
+                         (size_t)n);
+    return RG_ERR_UNSUPPORTED;
 }

@@ -17,6 +17,8 @@ __global__ void rope_cache_kernel(A* __restrict__ qkv, const float* __restrict__
                                   const int* __restrict__ positions, const int* __restrict__ slots,
                                   A* __restrict__ kv_cache, int nh, int nkv, int d, int page_size,
                                   int max_pos, int* __restrict__ err) {
+    pdl_wait();
+    pdl_trigger();
     const int t = blockIdx.x;
     const int half = d >> 1;
     int pos = positions[t];
@@ -73,11 +75,10 @@ extern "C" int rg_rope_cache(void* qkv, int dtype, const float* table, const int
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = 256;
     if (dtype == RG_DTYPE_BF16)
-        rope_cache_kernel<bf16><<<T, threads, 0, s>>>((bf16*)qkv, table, positions, slots, (bf16*)kv_cache,
-                                                      nh, nkv, d, page_size, max_pos, err);
-    else if (dtype == RG_DTYPE_F32)
-        rope_cache_kernel<float><<<T, threads, 0, s>>>((float*)qkv, table, positions, slots, (float*)kv_cache,
-                                                       nh, nkv, d, page_size, max_pos, err);
-    else return RG_ERR_UNSUPPORTED;
-    return RG_LAUNCH_RESULT();
+        return rg_launch(rope_cache_kernel<bf16>, dim3(T), dim3(threads), 0, s, 1, (bf16*)qkv, table, positions, slots,
+                         (bf16*)kv_cache, nh, nkv, d, page_size, max_pos, err);
+    if (dtype == RG_DTYPE_F32)
+        return rg_launch(rope_cache_kernel<float>, dim3(T), dim3(threads), 0, s, 1, (float*)qkv, table, positions,
+                         slots, (float*)kv_cache, nh, nkv, d, page_size, max_pos, err);
+    return RG_ERR_UNSUPPORTED;
 }

@@ -60,6 +60,8 @@ __device__ __forceinline__ void block_argmax(float& v, int& idx, float* sv, int*
 __global__ void argmax_kernel(const float* __restrict__ logits, int V, int* __restrict__ out) {
     __shared__ float sv[32];
     __shared__ int si[32];
+    pdl_wait();
+    pdl_trigger();
     const float* row = logits + (size_t)blockIdx.x * V;
     float best = -INFINITY;
     int bi = 0x7fffffff;
@@ -79,6 +81,8 @@ __global__ void sample_kernel(const float* __restrict__ logits, int V,
     __shared__ float sv[33];
     __shared__ int si[32];
     __shared__ float seg[SAMPLE_THREADS];
+    pdl_wait();
+    pdl_trigger();
     const int row_i = blockIdx.x;
     const float* row = logits + (size_t)row_i * V;
     const float T = temperature[row_i];
@@ -206,6 +210,8 @@ __global__ void argmax_partial_kernel(const float* __restrict__ logits, int V, i
                                       float* __restrict__ pv, int* __restrict__ pi) {
     __shared__ float sv[32];
     __shared__ int si[32];
+    pdl_wait();
+    pdl_trigger();
     const float* row = logits + (size_t)blockIdx.y * V;
     const int b = blockIdx.x * chunk, e = min(V, b + chunk);
     float best = -INFINITY;
@@ -224,6 +230,8 @@ __global__ void argmax_final_kernel(const float* __restrict__ pv, const int* __r
                                     int* __restrict__ out) {
     __shared__ float sv[32];
     __shared__ int si[32];
+    pdl_wait();
+    pdl_trigger();
     float best = -INFINITY;
     int bi = 0x7fffffff;
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
@@ -241,21 +249,19 @@ extern "C" int rg_argmax(const float* logits, int rows, int V, int* out, float* 
     if (rows <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     if (pieces <= 1 || pv == nullptr || pi == nullptr) {
-        argmax_kernel<<<rows, SAMPLE_THREADS, 0, s>>>(logits, V, out);
-        return RG_LAUNCH_RESULT();
+        return rg_launch(argmax_kernel, dim3(rows), dim3(SAMPLE_THREADS), 0, s, 1, logits, V, out);
     }
     const int chunk = (V + pieces - 1) / pieces;
     dim3 grid(pieces, rows);
-    argmax_partial_kernel<<<grid, 256, 0, s>>>(logits, V, chunk, pv, pi);
-    argmax_final_kernel<<<rows, 64, 0, s>>>(pv, pi, pieces, out);
-    return RG_LAUNCH_RESULT();
+    int e = rg_launch(argmax_partial_kernel, grid, dim3(256), 0, s, 1, logits, V, chunk, pv, pi);
+    if (e) return e;
+    return rg_launch(argmax_final_kernel, dim3(rows), dim3(64), 0, s, 1, (const float*)pv, (const int*)pi, pieces, out);
 }
 
 extern "C" int rg_sample(const float* logits, int rows, int V, const float* temperature, const int* top_k,
                          const float* top_p, const unsigned long long* seed,
                          const unsigned long long* counter, int* out, void* stream) {
     if (rows <= 0) return 0;
-    sample_kernel<<<rows, SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(
-        logits, V, temperature, top_k, top_p, seed, counter, out);
-    return RG_LAUNCH_RESULT();
+    return rg_launch(sample_kernel, dim3(rows), dim3(SAMPLE_THREADS), 0, (cudaStream_t)stream, 1, logits, V, temperature,
+                     top_k, top_p, seed, counter, out);
 }

@@ -8,6 +8,7 @@ or if a library fails to build, these raise.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_int, c_float, c_void_p, c_longlong
 
 import torch
@@ -71,10 +72,21 @@ def launch_counter() -> LaunchCounter:
     return _COUNTER
 
 
+# Programmatic dependent launch: a kernel may start (and fetch weights) while the kernel before it drains.
+# RAILGUN_B200_PDL=0 switches it off.
+PDL_ENABLED = os.environ.get("RAILGUN_B200_PDL", "1") != "0"
+_pdl_set: set = set()
+
+
 def _fn(lib_name: str, fn_name: str):
     fn = _fn_cache.get(fn_name)
     if fn is None:
-        fn = getattr(native.load(lib_name), fn_name)
+        lib = native.load(lib_name)
+        if lib_name not in _pdl_set:
+            lib.rg_set_pdl.restype = None
+            lib.rg_set_pdl(c_int(1 if PDL_ENABLED else 0))
+            _pdl_set.add(lib_name)
+        fn = getattr(lib, fn_name)
         fn.restype = c_int
         _fn_cache[fn_name] = fn
     _COUNTER.value += _LAUNCHES_PER_CALL.get(fn_name, 1)
@@ -151,7 +163,8 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     return torch.stack([gate.view(I // 8, 8, K), up.view(I // 8, 8, K)], dim=1).reshape(2 * I, K).contiguous()
 
 
-SKINNY_MAX_ROWS = 64
+SKINNY_MAX_ROWS = 64           # what the kernel takes
+SKINNY_AUTO_ROWS = 8           # up to here it beats the library product on B200 (measured), so linear() uses it
 
 
 def skinny_gemm_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
@@ -367,8 +380,8 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype=None) -> torch.Tenso
         raise KernelError("linear: CUDA tensors only (there is no CPU path)")
     if x.dtype == torch.float32 and torch.backends.cuda.matmul.allow_tf32:
         raise KernelError("linear: TF32 is enabled; the 32-bit path must be true 32-bit")
-    if skinny_gemm_ok(x, weight):
-        return skinny_gemm(x, weight, out_dtype)             # decode: stream the weights once
+    if x.shape[0] <= SKINNY_AUTO_ROWS and skinny_gemm_ok(x, weight):
+        return skinny_gemm(x, weight, out_dtype)             # small decode batches: stream the weights once
     if out_dtype is not None and out_dtype != x.dtype:
         return torch.mm(x, weight.t(), out_dtype=out_dtype)
     return torch.mm(x, weight.t())

@@ -37,7 +37,7 @@ class SwiGLU(FeedForward):
         self.w_down = tensors.get(m + "down_proj.weight", env.dtype)
 
     def forward(self, x, batch):
-        if self.interleaved and ops.skinny_gemm_ok(x, self.w_gate_up):
+        if self.interleaved and x.shape[0] <= ops.SKINNY_AUTO_ROWS and ops.skinny_gemm_ok(x, self.w_gate_up):
             act = ops.skinny_gemm(x, self.w_gate_up, silu_mul=True)
         else:
             act = ops.silu_mul(ops.linear(x, self.w_gate_up), interleaved=self.interleaved)
