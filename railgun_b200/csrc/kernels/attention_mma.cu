@@ -70,39 +70,41 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // 128 j over 64 rows x d/8 pieces, consecutive threads on consecutive 16-byte pieces of a row.
 template <int KD>
 struct TileGather {
-    int row[KD], col[KD];
-    __device__ __forceinline__ void init(int d) {
-        const int d8 = d >> 3;
+    int row[KD], dst[KD], src[KD];       // row in the tile; shared-memory offset; offset inside a page's K block
+    int page_shift, page_size, d;
+    __device__ __forceinline__ void init(int d_, int page_size_, int page_shift_, int kvh) {
+        d = d_; page_size = page_size_; page_shift = page_shift_;
+        const int d8 = d >> 3, stride = d + PAD;
 #pragma unroll
         for (int j = 0; j < KD; ++j) {
             const int idx = threadIdx.x + NTHREADS * j;            // 64 d/8 = 8 d pieces
             row[j] = idx < 8 * d ? idx / d8 : -1;
-            col[j] = (idx % d8) * 8;
+            const int col = (idx % d8) * 8;
+            dst[j] = row[j] * stride + col;
+            src[j] = kvh * page_size * d + col;
         }
     }
-    __device__ __forceinline__ void pages(const int* __restrict__ bt, int key0, int key_end, int page_size,
-                                          int (&pg)[KD]) const {
+    __device__ __forceinline__ void pages(const int* __restrict__ bt, int key0, int key_end, int (&pg)[KD]) const {
 #pragma unroll
         for (int j = 0; j < KD; ++j) {
             const int key = key0 + row[j];
-            pg[j] = (row[j] >= 0 && key < key_end) ? bt[key / page_size] : -1;
+            pg[j] = (row[j] >= 0 && key < key_end) ? bt[page_shift >= 0 ? key >> page_shift : key / page_size] : -1;
         }
     }
     __device__ __forceinline__ void issue(bf16* sK, bf16* sV, const bf16* __restrict__ kv_cache, const int (&pg)[KD],
-                                          int key0, int kvh, int nkv, int d, int page_size) const {
-        const int stride = d + PAD;
-        const size_t page_elems = (size_t)2 * nkv * page_size * d;
-        const size_t v_off = (size_t)nkv * page_size * d;
+                                          int key0, size_t page_elems, int v_off) const {
 #pragma unroll
         for (int j = 0; j < KD; ++j) {
             if (row[j] >= 0) {
                 const bool valid = pg[j] >= 0;
                 const bf16* ksrc = kv_cache;
-                if (valid)
-                    ksrc = kv_cache + (size_t)pg[j] * page_elems +
-                           ((size_t)kvh * page_size + (key0 + row[j]) % page_size) * d + col[j];
-                cp_async16(sK + row[j] * stride + col[j], ksrc, valid);
-                cp_async16(sV + row[j] * stride + col[j], ksrc + (valid ? v_off : 0), valid);
+                if (valid) {
+                    const int key = key0 + row[j];
+                    const int off = page_shift >= 0 ? key & (page_size - 1) : key % page_size;
+                    ksrc = kv_cache + (size_t)pg[j] * page_elems + (src[j] + off * d);
+                }
+                cp_async16(sK + dst[j], ksrc, valid);
+                cp_async16(sV + dst[j], ksrc + (valid ? v_off : 0), valid);
             }
         }
     }
@@ -112,12 +114,15 @@ struct TileGather {
 // Prefill: one CTA per (query tile of up to 64 consecutive positions of one request, head).
 // tiles: [NT][3] = first token row, number of rows, request index.
 // ---------------------------------------------------------------------------------------------------
-template <int DMAX>
-__global__ void __launch_bounds__(NTHREADS)
+// EXACT: the head size is DMAX itself, known at compile time (loops unroll without guards and shared-memory
+// addresses fold into the instructions); otherwise any multiple of 16 up to DMAX, passed at run time.
+template <int DMAX, bool EXACT>
+__global__ void __launch_bounds__(NTHREADS, DMAX <= 64 ? 4 : (DMAX <= 128 ? 2 : 1))
 prefill_attention_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
                          const bf16* __restrict__ kv_cache, const int* __restrict__ block_table, int max_blocks,
-                         const int* __restrict__ tiles, const int* __restrict__ positions, int nh, int nkv, int d,
-                         int page_size, int window, float scale_log2) {
+                         const int* __restrict__ tiles, const int* __restrict__ positions, int nh, int nkv, int d_arg,
+                         int page_size, int page_shift, int window, float scale_log2) {
+    const int d = EXACT ? DMAX : d_arg;
     constexpr int KD = DMAX / 16;          // k-steps over the head dimension
     constexpr int ND = DMAX / 8;           // n-tiles of the output
     constexpr bool Q_IN_REGS = DMAX <= 128;
@@ -129,7 +134,8 @@ prefill_attention_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
 
     pdl_wait();
     pdl_trigger();
-    const int tile = blockIdx.x, h = blockIdx.y;
+    // later tiles of a prompt attend more keys: they are started first so that the short ones fill the tail
+    const int tile = gridDim.x - 1 - blockIdx.x, h = blockIdx.y;
     const int row0 = tiles[tile * 3 + 0], nrows = tiles[tile * 3 + 1], r = tiles[tile * 3 + 2];
     const int kvh = h / (nh / nkv);
     const int* bt = block_table + (size_t)r * max_blocks;
@@ -151,12 +157,14 @@ prefill_attention_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
         }
     }
     TileGather<KD> tg;
-    tg.init(d);
+    tg.init(d, page_size, page_shift, kvh);
+    const size_t page_elems = (size_t)2 * nkv * page_size * d;
+    const int v_off = nkv * page_size * d;
     int page_next[KD];
-    tg.pages(bt, kt0 * BN, hi + 1, page_size, page_next);
-    tg.issue(sKV, sKV + BN * stride, kv_cache, page_next, kt0 * BN, kvh, nkv, d, page_size);
+    tg.pages(bt, kt0 * BN, hi + 1, page_next);
+    tg.issue(sKV, sKV + BN * stride, kv_cache, page_next, kt0 * BN, page_elems, v_off);
     cp_async_commit();
-    tg.pages(bt, (kt0 + 1) * BN, hi + 1, page_size, page_next);    // beyond the last key: all -1
+    tg.pages(bt, (kt0 + 1) * BN, hi + 1, page_next);               // beyond the last key: all -1
 
     uint32_t qf[Q_IN_REGS ? KD : 1][4];
     float o[ND][4];
@@ -176,9 +184,9 @@ prefill_attention_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
         bf16* sV = sK + BN * stride;
         if (kt + 1 <= kt1) {
             bf16* nK = sKV + (stage ^ 1) * stage_elems;
-            tg.issue(nK, nK + BN * stride, kv_cache, page_next, (kt + 1) * BN, kvh, nkv, d, page_size);
+            tg.issue(nK, nK + BN * stride, kv_cache, page_next, (kt + 1) * BN, page_elems, v_off);
             cp_async_commit();
-            tg.pages(bt, (kt + 2) * BN, hi + 1, page_size, page_next);
+            tg.pages(bt, (kt + 2) * BN, hi + 1, page_next);
             cp_async_wait<1>();
         } else {
             cp_async_wait<0>();
@@ -212,16 +220,19 @@ prefill_attention_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
                     }
                 }
             }
-            // mask by absolute position, scale into the log2 domain
+            // scale into the log2 domain; mask by absolute position where the tile is not wholly attended
+            const bool edge = key_base + BN - 1 > wfirst || (window > 0 && key_base < wlast - window + 1);
             float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
             for (int j = 0; j < BN / 8; ++j) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    const int key = key_base + j * 8 + tq * 2 + (e & 1);
-                    const int prow = (e < 2) ? prow0 : prow1;
-                    const bool ok = key <= prow && (window <= 0 || key > prow - window);
-                    const float v = ok ? s[j][e] * scale_log2 : -INFINITY;
+                    float v = s[j][e] * scale_log2;
+                    if (edge) {
+                        const int key = key_base + j * 8 + tq * 2 + (e & 1);
+                        const int prow = (e < 2) ? prow0 : prow1;
+                        if (!(key <= prow && (window <= 0 || key > prow - window))) v = -INFINITY;
+                    }
                     s[j][e] = v;
                     if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
                 }
@@ -232,20 +243,22 @@ prefill_attention_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
             mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
             const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
             const float ms0 = mn0 == -INFINITY ? 0.f : mn0, ms1 = mn1 == -INFINITY ? 0.f : mn1;
-            const float al0 = exp2f(m0 - ms0), al1 = exp2f(m1 - ms1);
+            const float al0 = ex2(m0 - ms0), al1 = ex2(m1 - ms1);
             m0 = mn0; m1 = mn1;
             float rs0 = 0.f, rs1 = 0.f;
 #pragma unroll
             for (int j = 0; j < BN / 8; ++j) {
-                s[j][0] = exp2f(s[j][0] - ms0); s[j][1] = exp2f(s[j][1] - ms0);
-                s[j][2] = exp2f(s[j][2] - ms1); s[j][3] = exp2f(s[j][3] - ms1);
+                s[j][0] = ex2(s[j][0] - ms0); s[j][1] = ex2(s[j][1] - ms0);
+                s[j][2] = ex2(s[j][2] - ms1); s[j][3] = ex2(s[j][3] - ms1);
                 rs0 += s[j][0] + s[j][1];
                 rs1 += s[j][2] + s[j][3];
             }
             l0 = l0 * al0 + rs0;                                   // per-thread partial sums; reduced at the end
             l1 = l1 * al1 + rs1;
+            if (__any_sync(0xffffffffu, al0 != 1.f || al1 != 1.f)) {   // some row's max moved: rescale
 #pragma unroll
-            for (int i = 0; i < ND; ++i) { o[i][0] *= al0; o[i][1] *= al0; o[i][2] *= al1; o[i][3] *= al1; }
+                for (int i = 0; i < ND; ++i) { o[i][0] *= al0; o[i][1] *= al0; o[i][2] *= al1; o[i][3] *= al1; }
+            }
             // O += P V
 #pragma unroll
             for (int kk = 0; kk < BN / 16; ++kk) {
@@ -300,14 +313,15 @@ prefill_attention_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
 #endif
 #define DEC_HEADS 8        // query heads per CTA
 
-template <int DMAX>
+template <int DMAX, bool EXACT>
 __global__ void __launch_bounds__(NTHREADS)
 decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ kv_cache,
                         const int* __restrict__ block_table, int max_blocks, const int* __restrict__ rows,
                         const int* __restrict__ req_of_token, const int* __restrict__ positions,
-                        float* __restrict__ part_o, float* __restrict__ part_ml, int nh, int nkv, int d,
+                        float* __restrict__ part_o, float* __restrict__ part_ml, int nh, int nkv, int d_arg,
                         int page_size, int page_shift, int window, float scale_log2, int num_splits,
                         int head_tiles) {
+    const int d = EXACT ? DMAX : d_arg;
     constexpr int KD = DMAX / 16;
     constexpr bool Q_IN_REGS = DMAX <= 128;
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -604,12 +618,15 @@ extern "C" int rg_prefill_attention(const void* q, int q_stride, void* out, cons
     cudaStream_t s = (cudaStream_t)stream;
     const float scale_log2 = scale * 1.4426950408889634f;
     const size_t smem = prefill_smem(d);
+    int page_shift = -1;                                            // log2 of the page size when it is a power of two
+    for (int b = 0; b < 31; ++b) if (page_size == (1 << b)) page_shift = b;
     dim3 grid(n_tiles, nh);
-#define RG_PREFILL(DM) { int e = allow_smem(prefill_attention_kernel<DM>, smem); if (e) return e; \
-    return rg_launch(prefill_attention_kernel<DM>, grid, dim3(NTHREADS), smem, s, 1, (const bf16*)q, q_stride, \
-        (bf16*)out, (const bf16*)kv_cache, block_table, max_blocks, tiles, positions, nh, nkv, d, page_size, window, \
-        scale_log2); }
-    if (d <= 64) RG_PREFILL(64) else if (d <= 128) RG_PREFILL(128) else RG_PREFILL(256)
+#define RG_PREFILL(DM, EX) { int e = allow_smem(prefill_attention_kernel<DM, EX>, smem); if (e) return e; \
+    return rg_launch(prefill_attention_kernel<DM, EX>, grid, dim3(NTHREADS), smem, s, 1, (const bf16*)q, q_stride, \
+        (bf16*)out, (const bf16*)kv_cache, block_table, max_blocks, tiles, positions, nh, nkv, d, page_size, page_shift, \
+        window, scale_log2); }
+    if (d == 64) RG_PREFILL(64, true) else if (d == 128) RG_PREFILL(128, true)
+    else if (d < 64) RG_PREFILL(64, false) else if (d < 128) RG_PREFILL(128, false) else RG_PREFILL(256, false)
 #undef RG_PREFILL
 }
 
@@ -631,11 +648,12 @@ extern "C" int rg_decode_attention(const void* q, int q_stride, void* out, const
     if (num_splits > 65535 || nkv * head_tiles > 65535) return RG_ERR_UNSUPPORTED;
     dim3 grid(n_tokens, nkv * head_tiles, num_splits);
     int e = 0;
-#define RG_DECODE(DM) { e = allow_smem(decode_attention_kernel<DM>, smem); if (e) return e; \
-    e = rg_launch(decode_attention_kernel<DM>, grid, dim3(NTHREADS), smem, s, 1, (const bf16*)q, q_stride, \
+#define RG_DECODE(DM, EX) { e = allow_smem(decode_attention_kernel<DM, EX>, smem); if (e) return e; \
+    e = rg_launch(decode_attention_kernel<DM, EX>, grid, dim3(NTHREADS), smem, s, 1, (const bf16*)q, q_stride, \
         (const bf16*)kv_cache, block_table, max_blocks, rows, req_of_token, positions, part_o, part_ml, nh, nkv, d, \
         page_size, page_shift, window, scale_log2, num_splits, head_tiles); }
-    if (d <= 64) RG_DECODE(64) else if (d <= 128) RG_DECODE(128) else RG_DECODE(256)
+    if (d == 64) RG_DECODE(64, true) else if (d == 128) RG_DECODE(128, true)
+    else if (d < 64) RG_DECODE(64, false) else if (d < 128) RG_DECODE(128, false) else RG_DECODE(256, false)
 #undef RG_DECODE
     if (e) return e;
     dim3 rgrid(n_tokens, nh);

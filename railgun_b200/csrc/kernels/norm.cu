@@ -39,6 +39,59 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const P* __restric
     }
 }
 
+// The same with 4 elements per access for H % 4 == 0 (16-byte residual accesses).  The order of the sum of
+// squares inside a thread differs from the scalar kernel's, the block reduction is the same.
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const bf16* p) {
+    const uint2 v = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(bf16* p, float4 v) {
+    uint2 o;
+    *reinterpret_cast<__nv_bfloat162*>(&o.x) = __floats2bfloat162_rn(v.x, v.y);
+    *reinterpret_cast<__nv_bfloat162*>(&o.y) = __floats2bfloat162_rn(v.z, v.w);
+    *reinterpret_cast<uint2*>(p) = o;
+}
+
+template <typename P, typename O>
+__global__ void add_rmsnorm_vec4_kernel(float* __restrict__ resid, const P* __restrict__ pending,
+                                        const float* __restrict__ w, float eps, O* __restrict__ out,
+                                        const int* __restrict__ rows, int H) {
+    __shared__ float scratch[33];
+    pdl_wait();
+    pdl_trigger();
+    const int orow = blockIdx.x;
+    const int srow = rows ? rows[orow] : orow;
+    float* r = resid + (size_t)srow * H;
+    const P* p = pending ? pending + (size_t)srow * H : nullptr;
+    const bool write_back = (rows == nullptr) && (p != nullptr);
+    float ss = 0.f;
+    for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+        float4 v = load4(r + i);
+        if (p) {
+            const float4 q = load4(p + i);
+            v.x += q.x; v.y += q.y; v.z += q.z; v.w += q.w;
+            if (write_back) store4(r + i, v);
+        }
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / (float)H + eps);
+    O* o = out + (size_t)orow * H;
+    for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+        float4 v = load4(r + i);
+        if (p && !write_back) {
+            const float4 q = load4(p + i);
+            v.x += q.x; v.y += q.y; v.z += q.z; v.w += q.w;
+        }
+        const float4 g = load4(w + i);
+        store4(o + i, make_float4(v.x * inv * g.x, v.y * inv * g.y, v.z * inv * g.z, v.w * inv * g.w));
+    }
+}
+
 // residual[row] += pending[row] only (a block arrangement that ends without a norm).
 template <typename P>
 __global__ void residual_add_kernel(float* __restrict__ resid, const P* __restrict__ pending, size_t n) {
@@ -53,8 +106,12 @@ extern "C" int rg_add_rmsnorm(float* resid, const void* pending, int pending_dty
                               int H, void* stream) {
     if (n_out_rows <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
-    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
-#define RG_NORM(P, O) return rg_launch(add_rmsnorm_kernel<P, O>, dim3(n_out_rows), dim3(threads), 0, s, 1, \
+    const bool vec = H % 4 == 0 && (uintptr_t)resid % 16 == 0 && (uintptr_t)out % 16 == 0 &&
+                     (uintptr_t)pending % 16 == 0 && (uintptr_t)w % 16 == 0;
+    const int threads = vec ? (H >= 4096 ? 512 : (H >= 1024 ? 256 : 128)) : (H >= 2048 ? 512 : (H >= 512 ? 256 : 128));
+#define RG_NORM(P, O) return vec ? rg_launch(add_rmsnorm_vec4_kernel<P, O>, dim3(n_out_rows), dim3(threads), 0, s, 1, \
+        resid, (const P*)pending, w, eps, (O*)out, rows, H) \
+      : rg_launch(add_rmsnorm_kernel<P, O>, dim3(n_out_rows), dim3(threads), 0, s, 1, \
         resid, (const P*)pending, w, eps, (O*)out, rows, H)
     if (pending == nullptr) pending_dtype = out_dtype;
     if (pending_dtype == RG_DTYPE_BF16 && out_dtype == RG_DTYPE_BF16) RG_NORM(bf16, bf16);

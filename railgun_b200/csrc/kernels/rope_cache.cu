@@ -67,6 +67,73 @@ __global__ void rope_cache_kernel(A* __restrict__ qkv, const float* __restrict__
     }
 }
 
+// Two neighbouring pairs per thread (4-byte accesses for bfloat16): d % 4 == 0.
+template <typename A> struct Pair;
+template <> struct Pair<bf16> {
+    typedef __nv_bfloat162 T;
+    static __device__ __forceinline__ float2 load(const bf16* p) { return __bfloat1622float2(*reinterpret_cast<const T*>(p)); }
+    static __device__ __forceinline__ void store(bf16* p, float2 v) { *reinterpret_cast<T*>(p) = __floats2bfloat162_rn(v.x, v.y); }
+};
+template <> struct Pair<float> {
+    typedef float2 T;
+    static __device__ __forceinline__ float2 load(const float* p) { return *reinterpret_cast<const float2*>(p); }
+    static __device__ __forceinline__ void store(float* p, float2 v) { *reinterpret_cast<float2*>(p) = v; }
+};
+
+template <typename A>
+__global__ void rope_cache_vec2_kernel(A* __restrict__ qkv, const float* __restrict__ table,
+                                       const int* __restrict__ positions, const int* __restrict__ slots,
+                                       A* __restrict__ kv_cache, int nh, int nkv, int d, int page_size,
+                                       int max_pos, int* __restrict__ err) {
+    pdl_wait();
+    pdl_trigger();
+    const int t = blockIdx.x;
+    const int half = d >> 1, hq = half >> 1;          // hq: element pairs per half head
+    int pos = positions[t];
+    if (pos < 0 || pos >= max_pos) {
+        if (threadIdx.x == 0 && err) atomicExch(err, 1);
+        pos = 0;
+    }
+    A* row = qkv + (size_t)t * (nh + 2 * nkv) * d;
+    const float* cs = table ? table + (size_t)pos * d : nullptr;
+    const int slot = slots ? slots[t] : -1;
+    A* kdst = nullptr;
+    A* vdst = nullptr;
+    if (slot >= 0) {
+        const int page = slot / page_size, off = slot - page * page_size;
+        kdst = kv_cache + (((size_t)page * 2 + 0) * nkv * page_size + off) * d;
+        vdst = kv_cache + (((size_t)page * 2 + 1) * nkv * page_size + off) * d;
+    }
+    const size_t head_stride = (size_t)page_size * d;
+    const int n_rot = (nh + nkv) * hq;
+    for (int w = threadIdx.x; w < n_rot; w += blockDim.x) {
+        const int h = w / hq, i = (w - h * hq) * 2;
+        A* x = row + (size_t)h * d;
+        const float2 lo = Pair<A>::load(x + i), hi = Pair<A>::load(x + i + half);
+        float2 nlo = lo, nhi = hi;
+        if (cs) {
+            const float2 c = *reinterpret_cast<const float2*>(cs + i), s = *reinterpret_cast<const float2*>(cs + half + i);
+            nlo = make_float2(lo.x * c.x - hi.x * s.x, lo.y * c.y - hi.y * s.y);
+            nhi = make_float2(hi.x * c.x + lo.x * s.x, hi.y * c.y + lo.y * s.y);
+        }
+        Pair<A>::store(x + i, nlo);
+        Pair<A>::store(x + i + half, nhi);
+        if (h >= nh && kdst) {
+            A* kd = kdst + (size_t)(h - nh) * head_stride;
+            Pair<A>::store(kd + i, nlo);
+            Pair<A>::store(kd + i + half, nhi);
+        }
+    }
+    if (vdst) {
+        const A* v = row + (size_t)(nh + nkv) * d;
+        const int n_v = nkv * (d >> 1);
+        for (int w = threadIdx.x; w < n_v; w += blockDim.x) {
+            const int h = (w * 2) / d, i = w * 2 - h * d;
+            Pair<A>::store(vdst + (size_t)h * head_stride + i, Pair<A>::load(v + w * 2));
+        }
+    }
+}
+
 extern "C" int rg_rope_cache(void* qkv, int dtype, const float* table, const int* positions,
                              const int* slots, void* kv_cache, int T, int nh, int nkv, int d,
                              int page_size, int max_pos, int* err, void* stream) {
@@ -74,6 +141,15 @@ extern "C" int rg_rope_cache(void* qkv, int dtype, const float* table, const int
     if (d % 2) return RG_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = 256;
+    if (d % 4 == 0 && (uintptr_t)qkv % 8 == 0 && (uintptr_t)kv_cache % 8 == 0 && (uintptr_t)table % 8 == 0) {
+        if (dtype == RG_DTYPE_BF16)
+            return rg_launch(rope_cache_vec2_kernel<bf16>, dim3(T), dim3(threads), 0, s, 1, (bf16*)qkv, table, positions,
+                             slots, (bf16*)kv_cache, nh, nkv, d, page_size, max_pos, err);
+        if (dtype == RG_DTYPE_F32)
+            return rg_launch(rope_cache_vec2_kernel<float>, dim3(T), dim3(threads), 0, s, 1, (float*)qkv, table,
+                             positions, slots, (float*)kv_cache, nh, nkv, d, page_size, max_pos, err);
+        return RG_ERR_UNSUPPORTED;
+    }
     if (dtype == RG_DTYPE_BF16)
         return rg_launch(rope_cache_kernel<bf16>, dim3(T), dim3(threads), 0, s, 1, (bf16*)qkv, table, positions, slots,
                          (bf16*)kv_cache, nh, nkv, d, page_size, max_pos, err);
