@@ -12,6 +12,7 @@ from __future__ import annotations
 
 import numpy as np
 
+from .. import ops
 from ..sampling.sampler import Sampler
 from .batch import StepEntry
 from .request import RequestOutput, SamplingParams
@@ -65,6 +66,7 @@ class Engine:
             tokens = self.runner.last_greedy.cpu().numpy()      # the decode graph already took the argmax
         else:
             tokens = self.sampler.sample(logits, params, [self.scheduler.num_generated(r) for r in wanted])
+        ops.tc_gemm_check()                 # the tokens are on the host: the step has finished
         self.scheduler.update(wanted, tokens)
         return list(zip(wanted, tokens.tolist()))
 

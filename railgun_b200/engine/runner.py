@@ -188,6 +188,7 @@ class ModelRunner:
                 self.alloc.release(rid)
 
     def check_device_errors(self) -> None:
+        ops.tc_gemm_check()
         if int(self.err_flag.item()):
             self.err_flag.zero_()
             raise RuntimeError("a kernel met a position outside its table")

@@ -315,6 +315,69 @@ def decode_attention(q, q_stride: int, out, kv_cache, block_table, rows, n_token
         c_int(num_splits), _stream()), "decode_attention")
 
 
+_tc_err: dict = {}
+TC_GEMM_MIN_ROWS = 1024        # from here the fused tcgen05 gate|up product beats cuBLAS + SiLU-mul (measured)
+
+
+def tc_gemm_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    """Can the tcgen05 product take these operands?"""
+    return (x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dim() == 2
+            and x.shape[1] % 8 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
+            and weight.is_contiguous() and weight.data_ptr() % 16 == 0)
+
+
+def tc_gemm(x: torch.Tensor, weight: torch.Tensor, out_dtype=None, silu_mul: bool = False, wide: bool = True,
+            check: bool = False) -> torch.Tensor:
+    """y = x W^T on the tcgen05 tensor cores (TMA-fed, accumulators in tensor
+    memory).  ``silu_mul``: W is interleaved gate|up storage and y = silu(gate)
+    * up.  ``wide``: 128 x 256 tiles instead of 128 x 128.  The kernel's waits
+    are bounded; ``tc_gemm_check()`` (or ``check=True``, which synchronises)
+    raises if one gave up."""
+    if not tc_gemm_ok(x, weight):
+        raise KernelError(f"tc_gemm refuses x {tuple(x.shape)} {x.dtype} stride {x.stride()}, "
+                          f"W {tuple(weight.shape)} {weight.dtype}: bfloat16, K a multiple of 8, 16-byte aligned")
+    M, K = x.shape
+    N = weight.shape[0]
+    if weight.shape[1] != K:
+        raise KernelError(f"tc_gemm: x has {K} columns, W has {weight.shape[1]}")
+    out_dtype = out_dtype or torch.bfloat16
+    if silu_mul and (N % 16 or out_dtype != torch.bfloat16):
+        raise KernelError("tc_gemm: the SiLU-mul epilogue needs N % 16 == 0 and bfloat16 output")
+    err = _tc_err.get(x.device)
+    if err is None:
+        err = _tc_err[x.device] = torch.zeros(1, dtype=torch.int32, device=x.device)
+    global _tc_unchecked
+    _tc_unchecked = True
+    out = torch.empty((M, N // 2 if silu_mul else N), dtype=out_dtype, device=x.device)
+    _ok(_fn("gemm_tcgen05", "rg_tc_gemm")(
+        _ptr(x), c_int(x.stride(0)), _ptr(weight), _ptr(out), c_int(out.shape[1]), c_int(_dtype_code(out)),
+        c_int(1 if silu_mul else 0), c_int(M), c_int(N), c_int(K), c_int(1 if wide else 0), _ptr(err), _stream()),
+        "tc_gemm")
+    if check:
+        tc_gemm_check(x.device)
+    return out
+
+
+_tc_unchecked = False
+
+
+def tc_gemm_check(device=None) -> None:
+    """Raise if a wait inside a tcgen05 product gave up since the last check
+    (synchronises; free when no such product ran since)."""
+    global _tc_unchecked
+    if not _tc_unchecked:
+        return
+    _tc_unchecked = False
+    for dev, err in _tc_err.items():
+        if device is not None and dev != device:
+            continue
+        code = int(err.item())
+        if code:
+            err.zero_()
+            who = {1: "the TMA producer", 2: "the MMA issuer", 3: "the epilogue"}.get(code, f"role {code}")
+            raise KernelError(f"tc_gemm: {who} gave up waiting on a barrier; the result is invalid")
+
+
 def argmax(logits: torch.Tensor) -> torch.Tensor:
     """Index of the largest logit of every row, ties to the lowest index."""
     _check(logits, "logits", torch.float32)

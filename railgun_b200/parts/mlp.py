@@ -38,7 +38,9 @@ class SwiGLU(FeedForward):
 
     def forward(self, x, batch):
         if self.interleaved and x.shape[0] <= ops.SKINNY_AUTO_ROWS and ops.skinny_gemm_ok(x, self.w_gate_up):
-            act = ops.skinny_gemm(x, self.w_gate_up, silu_mul=True)
+            act = ops.skinny_gemm(x, self.w_gate_up, silu_mul=True)              # decode: weights streamed once
+        elif self.interleaved and x.shape[0] >= ops.TC_GEMM_MIN_ROWS and ops.tc_gemm_ok(x, self.w_gate_up):
+            act = ops.tc_gemm(x, self.w_gate_up, silu_mul=True)                  # prefill: tcgen05, SiLU-mul in the epilogue
         else:
             act = ops.silu_mul(ops.linear(x, self.w_gate_up), interleaved=self.interleaved)
         return ops.linear(act, self.w_down)
