@@ -71,8 +71,8 @@ skinny_gemm_kernel(const bf16* __restrict__ W, const bf16* __restrict__ x, int l
     for (int j = 0; j < MT; ++j) { acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f; }
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
 
-    // W does not depend on the kernel before this one: its first piece is requested before the wait, and
-    // every later piece one iteration ahead of its use.
+    // W does not depend on the kernel before this one: its first piece is requested before the wait.
+    // (Requesting every piece one iteration ahead was measured slower: the extra registers cost residency.)
     uint4 a[4], b[4];
     int kb = k_lo + warp * 128;
 #pragma unroll
@@ -84,22 +84,25 @@ skinny_gemm_kernel(const bf16* __restrict__ W, const bf16* __restrict__ x, int l
     }
     pdl_wait();
     pdl_trigger();
+    bool first = true;
     for (; kb < k_hi; kb += NW * 128) {
-        uint4 xq[MT][4], an[4], bn[4];
+        uint4 xq[MT][4];
+        if (!first) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {              // 8 loads of W in flight per thread
+                const int k = kb + c * 32;
+                const bool kin = k + tq * 8 < k_hi;
+                a[c] = (kin && v0) ? ld_stream16(w0 + k) : zero;
+                b[c] = (kin && v1) ? ld_stream16(w1 + k) : zero;
+            }
+        }
+        first = false;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
             const int k = kb + c * 32;
             const bool kin = k + tq * 8 < k_hi;
 #pragma unroll
             for (int j = 0; j < MT; ++j) xq[j][c] = (kin && xv[j]) ? ld_cached16(xr[j] + k) : zero;
-        }
-        const int kn = kb + NW * 128;
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            const int k = kn + c * 32;
-            const bool kin = k + tq * 8 < k_hi;
-            an[c] = (kin && v0) ? ld_stream16(w0 + k) : zero;
-            bn[c] = (kin && v1) ? ld_stream16(w1 + k) : zero;
         }
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
@@ -109,8 +112,6 @@ skinny_gemm_kernel(const bf16* __restrict__ W, const bf16* __restrict__ x, int l
                 mma16816(acc[j], a[c].z, b[c].z, a[c].w, b[c].w, xq[j][c].z, xq[j][c].w);
             }
         }
-#pragma unroll
-        for (int c = 0; c < 4; ++c) { a[c] = an[c]; b[c] = bn[c]; }
     }
     // the warps' partial sums -> shared memory, summed in warp order
     float* mine = red + (size_t)warp * 16 * COLS;
