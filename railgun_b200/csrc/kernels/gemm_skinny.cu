@@ -38,26 +38,33 @@ __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// One block: 16 rows of W (n0 .. n0+15) and one slice of K, split over NW warps in interleaved 128-wide
-// pieces.  CS blocks of a cluster share the 16 rows and take one K slice each; block 0 of the cluster adds
-// the slices' sums, read from the other blocks' shared memory, in rank order (the same order every time).
+// One block: RT x 16 rows of W (from n0) and one slice of K, split over NW warps in interleaved 128-wide
+// pieces; every warp multiplies all RT row tiles by the same fragments of x.  CS blocks of a cluster share the
+// rows and take one K slice each; block 0 of the cluster adds the slices' sums, read from the other blocks'
+// shared memory, in rank order (the same order every time).
 // MT: batch rows / 8 (rounded up).  x rows are ldx elements apart.  K % 8 == 0.
-template <int MT, int NW, int CS, int EPI, typename OUT>
+template <int MT, int NW, int CS, int RT, int EPI, typename OUT>
 __global__ void __launch_bounds__(NW * 32)
 skinny_gemm_kernel(const bf16* __restrict__ W, const bf16* __restrict__ x, int ldx, OUT* __restrict__ out, int ldo,
                    int M, int N, int K) {
-    extern __shared__ float red[];                     // [NW][16][8 * MT], then the block's sum [16][8 * MT]
-    constexpr int COLS = 8 * MT;
+    extern __shared__ float red[];                     // [NW][RT * 16][8 * MT], then the block's sum [RT * 16][8 * MT]
+    constexpr int COLS = 8 * MT, ROWS = RT * 16;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, tq = lane & 3;
     const int rank = CS > 1 ? (int)(blockIdx.x % CS) : 0;
-    const int n0 = (int)(blockIdx.x / CS) * 16;
+    const int n0 = (int)(blockIdx.x / CS) * ROWS;
     const int slice = ((K + CS * 128 - 1) / (CS * 128)) * 128;     // K slice of one block, a multiple of 128
     const int k_lo = rank * slice, k_hi = min(K, k_lo + slice);
-    const int r0 = n0 + g, r1 = n0 + g + 8;
-    const bool v0 = r0 < N, v1 = r1 < N;
-    const bf16* w0 = W + (size_t)(v0 ? r0 : 0) * K + tq * 8;
-    const bf16* w1 = W + (size_t)(v1 ? r1 : 0) * K + tq * 8;
+    const bf16* w0[RT];
+    const bf16* w1[RT];
+    bool v0[RT], v1[RT];
+#pragma unroll
+    for (int t = 0; t < RT; ++t) {
+        const int r0 = n0 + t * 16 + g, r1 = r0 + 8;
+        v0[t] = r0 < N; v1[t] = r1 < N;
+        w0[t] = W + (size_t)(v0[t] ? r0 : 0) * K + tq * 8;
+        w1[t] = W + (size_t)(v1[t] ? r1 : 0) * K + tq * 8;
+    }
     const bf16* xr[MT];
     bool xv[MT];
 #pragma unroll
@@ -66,36 +73,35 @@ skinny_gemm_kernel(const bf16* __restrict__ W, const bf16* __restrict__ x, int l
         xv[j] = m < M;
         xr[j] = x + (size_t)(xv[j] ? m : 0) * ldx + tq * 8;
     }
-    float acc[MT][4];
+    float acc[RT][MT][4];
 #pragma unroll
-    for (int j = 0; j < MT; ++j) { acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f; }
+    for (int t = 0; t < RT; ++t)
+#pragma unroll
+        for (int j = 0; j < MT; ++j) { acc[t][j][0] = acc[t][j][1] = acc[t][j][2] = acc[t][j][3] = 0.f; }
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
 
     // W does not depend on the kernel before this one: its first piece is requested before the wait.
     // (Requesting every piece one iteration ahead was measured slower: the extra registers cost residency.)
-    uint4 a[4], b[4];
+    uint4 a[RT][4], b[RT][4];
     int kb = k_lo + warp * 128;
+    auto load_w = [&]() {
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-        const int k = kb + c * 32;
-        const bool kin = k + tq * 8 < k_hi;
-        a[c] = (kin && v0) ? ld_stream16(w0 + k) : zero;
-        b[c] = (kin && v1) ? ld_stream16(w1 + k) : zero;
-    }
+        for (int t = 0; t < RT; ++t)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {              // 8 RT loads of W in flight per thread
+                const int k = kb + c * 32;
+                const bool kin = k + tq * 8 < k_hi;
+                a[t][c] = (kin && v0[t]) ? ld_stream16(w0[t] + k) : zero;
+                b[t][c] = (kin && v1[t]) ? ld_stream16(w1[t] + k) : zero;
+            }
+    };
+    load_w();
     pdl_wait();
     pdl_trigger();
     bool first = true;
     for (; kb < k_hi; kb += NW * 128) {
         uint4 xq[MT][4];
-        if (!first) {
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {              // 8 loads of W in flight per thread
-                const int k = kb + c * 32;
-                const bool kin = k + tq * 8 < k_hi;
-                a[c] = (kin && v0) ? ld_stream16(w0 + k) : zero;
-                b[c] = (kin && v1) ? ld_stream16(w1 + k) : zero;
-            }
-        }
+        if (!first) load_w();
         first = false;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
@@ -105,37 +111,41 @@ skinny_gemm_kernel(const bf16* __restrict__ W, const bf16* __restrict__ x, int l
             for (int j = 0; j < MT; ++j) xq[j][c] = (kin && xv[j]) ? ld_cached16(xr[j] + k) : zero;
         }
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int t = 0; t < RT; ++t)
 #pragma unroll
-            for (int j = 0; j < MT; ++j) {
-                mma16816(acc[j], a[c].x, b[c].x, a[c].y, b[c].y, xq[j][c].x, xq[j][c].y);
-                mma16816(acc[j], a[c].z, b[c].z, a[c].w, b[c].w, xq[j][c].z, xq[j][c].w);
+            for (int c = 0; c < 4; ++c) {
+#pragma unroll
+                for (int j = 0; j < MT; ++j) {
+                    mma16816(acc[t][j], a[t][c].x, b[t][c].x, a[t][c].y, b[t][c].y, xq[j][c].x, xq[j][c].y);
+                    mma16816(acc[t][j], a[t][c].z, b[t][c].z, a[t][c].w, b[t][c].w, xq[j][c].z, xq[j][c].w);
+                }
             }
-        }
     }
     // the warps' partial sums -> shared memory, summed in warp order
-    float* mine = red + (size_t)warp * 16 * COLS;
+    float* mine = red + (size_t)warp * ROWS * COLS;
 #pragma unroll
-    for (int j = 0; j < MT; ++j) {
-        const int col = j * 8 + tq * 2;
-        mine[g * COLS + col] = acc[j][0];
-        mine[g * COLS + col + 1] = acc[j][1];
-        mine[(g + 8) * COLS + col] = acc[j][2];
-        mine[(g + 8) * COLS + col + 1] = acc[j][3];
-    }
+    for (int t = 0; t < RT; ++t)
+#pragma unroll
+        for (int j = 0; j < MT; ++j) {
+            const int col = j * 8 + tq * 2, row = t * 16 + g;
+            mine[row * COLS + col] = acc[t][j][0];
+            mine[row * COLS + col + 1] = acc[t][j][1];
+            mine[(row + 8) * COLS + col] = acc[t][j][2];
+            mine[(row + 8) * COLS + col + 1] = acc[t][j][3];
+        }
     __syncthreads();
-    float* fin = red + (size_t)NW * 16 * COLS;          // [16][COLS]
-    for (int idx = threadIdx.x; idx < 16 * COLS; idx += NW * 32) {
+    float* fin = red + (size_t)NW * ROWS * COLS;        // [ROWS][COLS]
+    for (int idx = threadIdx.x; idx < ROWS * COLS; idx += NW * 32) {
         float s = 0.f;
 #pragma unroll
-        for (int w = 0; w < NW; ++w) s += red[(size_t)w * 16 * COLS + idx];
+        for (int w = 0; w < NW; ++w) s += red[(size_t)w * ROWS * COLS + idx];
         fin[idx] = s;
     }
     if (CS > 1) {
         cg::cluster_group cluster = cg::this_cluster();
         cluster.sync();                                 // every block's sum is in its shared memory
         if (rank == 0) {
-            for (int idx = threadIdx.x; idx < 16 * COLS; idx += NW * 32) {
+            for (int idx = threadIdx.x; idx < ROWS * COLS; idx += NW * 32) {
                 float s = fin[idx];
 #pragma unroll
                 for (int r = 1; r < CS; ++r) s += cluster.map_shared_rank(fin, r)[idx];
@@ -147,46 +157,53 @@ skinny_gemm_kernel(const bf16* __restrict__ W, const bf16* __restrict__ x, int l
     }
     __syncthreads();
     if (EPI == EPI_NONE) {
-        for (int idx = threadIdx.x; idx < 16 * COLS; idx += NW * 32) {
-            const int m = idx >> 4, row = idx & 15;    // consecutive threads -> consecutive n: coalesced stores
+        for (int idx = threadIdx.x; idx < ROWS * COLS; idx += NW * 32) {
+            const int m = idx / ROWS, row = idx - m * ROWS;   // consecutive threads -> consecutive n: coalesced stores
             if (m < M && n0 + row < N) out[(size_t)m * ldo + n0 + row] = from_f32<OUT>(fin[row * COLS + m]);
         }
     } else {
-        for (int idx = threadIdx.x; idx < 8 * COLS; idx += NW * 32) {
-            const int m = idx >> 3, j = idx & 7;
-            if (m < M && n0 + j + 8 < N) {
-                const float gate = fin[j * COLS + m], up = fin[(j + 8) * COLS + m];
-                out[(size_t)m * ldo + (n0 >> 1) + j] = from_f32<OUT>(gate / (1.f + expf(-gate)) * up);
+        for (int idx = threadIdx.x; idx < (ROWS / 2) * COLS; idx += NW * 32) {
+            const int m = idx / (ROWS / 2), o = idx - m * (ROWS / 2);  // output o of this block: tile o / 8, element o % 8
+            const int row = (o >> 3) * 16 + (o & 7);
+            if (m < M && n0 + row + 8 < N) {
+                const float gate = fin[row * COLS + m], up = fin[(row + 8) * COLS + m];
+                out[(size_t)m * ldo + (n0 >> 1) + o] = from_f32<OUT>(gate / (1.f + expf(-gate)) * up);
             }
         }
     }
 }
 
-template <int MT, int NW, int CS, int EPI, typename OUT>
+template <int MT, int NW, int CS, int RT, int EPI, typename OUT>
 static int launch_skinny(const bf16* W, const bf16* x, int ldx, OUT* out, int ldo, int M, int N, int K,
                          cudaStream_t s) {
-    const size_t smem = (size_t)(NW + 1) * 16 * 8 * MT * sizeof(float);
-    auto kernel = skinny_gemm_kernel<MT, NW, CS, EPI, OUT>;
+    const size_t smem = (size_t)(NW + 1) * RT * 16 * 8 * MT * sizeof(float);
+    auto kernel = skinny_gemm_kernel<MT, NW, CS, RT, EPI, OUT>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
-    return rg_launch(kernel, dim3((unsigned)(((N + 15) / 16) * CS)), dim3(NW * 32), smem, s, CS, W, x, ldx, out, ldo, M,
-                     N, K);
+    const unsigned blocks = (unsigned)(((N + RT * 16 - 1) / (RT * 16)) * CS);
+    return rg_launch(kernel, dim3(blocks), dim3(NW * 32), smem, s, CS, W, x, ldx, out, ldo, M, N, K);
 }
 
 template <int EPI, typename OUT>
 static int dispatch_skinny(const bf16* W, const bf16* x, int ldx, OUT* out, int ldo, int M, int N, int K,
                            cudaStream_t s) {
-    // Every warp should have one or two 128-wide pieces of K and all blocks should be resident at once:
-    // many row tiles -> few warps per block; few row tiles -> 16 warps; few row tiles and a long K -> K is
-    // also cut over a cluster of 4 blocks.
+    // Shapes from measurements on B200 at M = 8 (Llama 1B sizes): a block should stream enough of W to pay
+    // for its start and its reduction (two row tiles per warp wherever there are enough rows), every warp should
+    // have one or two 128-wide pieces of K, and all blocks should be resident at once.
+    //   very many rows (head: 128256)            8 warps, 2 row tiles          6.75 TB/s
+    //   many rows (gate|up: 16384)                4 warps, 2 row tiles          5.3 TB/s with SiLU-mul
+    //   few rows, long K (down: 2048 x 8192)      8 warps, 2 row tiles, K over a cluster of 4
+    //   few rows (QKV: 3072 / O: 2048)            16 warps, 2 / 1 row tiles
     const long long tiles = (N + 15) / 16;
-    const int shape = tiles >= 16 * 148 ? 0 : (tiles >= 4 * 148 ? 1 : ((K >= 4096 && tiles < 2 * 148) ? 3 : 2));
-#define RG_SK(MT_) (shape == 0 ? launch_skinny<MT_, 4, 1, EPI, OUT>(W, x, ldx, out, ldo, M, N, K, s) \
-                  : shape == 1 ? launch_skinny<MT_, 8, 1, EPI, OUT>(W, x, ldx, out, ldo, M, N, K, s) \
-                  : shape == 2 ? launch_skinny<MT_, 16, 1, EPI, OUT>(W, x, ldx, out, ldo, M, N, K, s) \
-                               : launch_skinny<MT_, 8, 4, EPI, OUT>(W, x, ldx, out, ldo, M, N, K, s))
+    const int shape = tiles >= 16 * 148 ? 0 : tiles >= 4 * 148 ? 1 : (K >= 4096 && tiles < 2 * 148) ? 2
+                    : tiles >= 160 ? 3 : 4;
+#define RG_SK(MT_) (shape == 0 ? launch_skinny<MT_, 8, 1, 2, EPI, OUT>(W, x, ldx, out, ldo, M, N, K, s) \
+                  : shape == 1 ? launch_skinny<MT_, 4, 1, 2, EPI, OUT>(W, x, ldx, out, ldo, M, N, K, s) \
+                  : shape == 2 ? launch_skinny<MT_, 8, 4, 2, EPI, OUT>(W, x, ldx, out, ldo, M, N, K, s) \
+                  : shape == 3 ? launch_skinny<MT_, 16, 1, 2, EPI, OUT>(W, x, ldx, out, ldo, M, N, K, s) \
+                               : launch_skinny<MT_, 16, 1, 1, EPI, OUT>(W, x, ldx, out, ldo, M, N, K, s))
     if (M <= 8) return RG_SK(1);
     if (M <= 16) return RG_SK(2);
     if (M <= 32) return RG_SK(4);
