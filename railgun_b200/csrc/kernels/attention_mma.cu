@@ -318,10 +318,12 @@ __global__ void __launch_bounds__(NTHREADS)
 decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ kv_cache,
                         const int* __restrict__ block_table, int max_blocks, const int* __restrict__ rows,
                         const int* __restrict__ req_of_token, const int* __restrict__ positions,
-                        float* __restrict__ part_o, float* __restrict__ part_ml, int nh, int nkv, int d_arg,
+                        float* __restrict__ part_o, float* __restrict__ part_ml, bf16* __restrict__ out,
+                        int* __restrict__ counters, int nh, int nkv, int d_arg,
                         int page_size, int page_shift, int window, float scale_log2, int num_splits,
                         int head_tiles) {
     const int d = EXACT ? DMAX : d_arg;
+    __shared__ int is_last;
     constexpr int KD = DMAX / 16;
     constexpr bool Q_IN_REGS = DMAX <= 128;
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -354,12 +356,44 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, tq = lane & 3;
 
+    // With `counters` the block that finishes last for its (token, head tile) adds the splits' partial
+    // results, always in split order, and writes the output; the counter is left at zero for the next launch.
+    auto reduce_if_last = [&]() {
+        if (counters == nullptr) return;                            // a separate kernel reduces
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int* c = counters + (size_t)ti * gridDim.y + blockIdx.y;
+            const int prev = atomicAdd(c, 1);
+            is_last = prev == num_splits - 1;
+            if (is_last) *c = 0;
+        }
+        __syncthreads();
+        if (!is_last) return;
+        __threadfence();
+        for (int idx = threadIdx.x; idx < nheads * d; idx += NTHREADS) {
+            const int row = idx / d, col = idx - row * d;
+            const size_t base = ((size_t)ti * nh + h0 + row) * num_splits;
+            float M = -INFINITY;
+            for (int s2 = 0; s2 < num_splits; ++s2) M = fmaxf(M, __ldcg(part_ml + (base + s2) * 2));
+            const float Ms = M == -INFINITY ? 0.f : M;
+            float L = 0.f, acc = 0.f;
+            for (int s2 = 0; s2 < num_splits; ++s2) {
+                const float w = exp2f(__ldcg(part_ml + (base + s2) * 2) - Ms);
+                L += w * __ldcg(part_ml + (base + s2) * 2 + 1);
+                if (w > 0.f) acc += w * __ldcg(part_o + (base + s2) * d + col);
+            }
+            const float inv = L > 0.f ? 1.f / L : 0.f;
+            out[((size_t)t * nh + h0 + row) * d + col] = __float2bfloat16_rn(acc * inv);
+        }
+    };
     if (k_begin >= k_end) {                                         // an empty split: zero weight in the reduction
         for (int i = threadIdx.x; i < nheads; i += NTHREADS) {
             float* ml = part_ml + (((size_t)ti * nh + h0 + i) * num_splits + split) * 2;
             ml[0] = -INFINITY;
             ml[1] = 0.f;
         }
+        reduce_if_last();
         return;
     }
     const int n_tiles = (k_end - k_begin + BN - 1) / BN;
@@ -565,10 +599,16 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
             acc += sc * cO[((size_t)w * DEC_HEADS + row) * d + col];
             L += sc * cML[(w * DEC_HEADS + row) * 2 + 1];
         }
-        const size_t base = ((size_t)ti * nh + h0 + row) * num_splits + split;
-        part_o[base * d + col] = acc;
-        if (col == 0) { part_ml[base * 2] = M; part_ml[base * 2 + 1] = L; }
+        if (num_splits == 1 && counters != nullptr) {               // the only split: this is the result
+            const float inv = L > 0.f ? 1.f / L : 0.f;
+            out[((size_t)t * nh + h0 + row) * d + col] = __float2bfloat16_rn(acc * inv);
+        } else {
+            const size_t base = ((size_t)ti * nh + h0 + row) * num_splits + split;
+            part_o[base * d + col] = acc;
+            if (col == 0) { part_ml[base * 2] = M; part_ml[base * 2 + 1] = L; }
+        }
     }
+    if (num_splits > 1) reduce_if_last();
 }
 
 // out[t, h, :] = sum_s 2^{m_s - M} o_s / sum_s 2^{m_s - M} l_s
@@ -631,11 +671,13 @@ extern "C" int rg_prefill_attention(const void* q, int q_stride, void* out, cons
 }
 
 // Scratch the caller provides: part_o floats = n_tokens * nh * num_splits * d; part_ml = n_tokens * nh * num_splits * 2.
+// counters: NULL (a second kernel reduces the splits), or n_tokens * nkv * ceil(group / 8) ints that are zero on
+// entry and are left zero (the last block of each token and head tile reduces and resets its counter).
 extern "C" int rg_decode_attention(const void* q, int q_stride, void* out, const void* kv_cache,
                                    const int* block_table, int max_blocks, const int* rows, int n_tokens,
                                    const int* req_of_token, const int* positions, float* part_o, float* part_ml,
-                                   int nh, int nkv, int d, int page_size, int window, float scale, int num_splits,
-                                   void* stream) {
+                                   int* counters, int nh, int nkv, int d, int page_size, int window, float scale,
+                                   int num_splits, void* stream) {
     if (n_tokens <= 0) return 0;
     if (d % 16 || d < 16 || d > 256 || nh % nkv || num_splits < 1) return RG_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
@@ -650,12 +692,12 @@ extern "C" int rg_decode_attention(const void* q, int q_stride, void* out, const
     int e = 0;
 #define RG_DECODE(DM, EX) { e = allow_smem(decode_attention_kernel<DM, EX>, smem); if (e) return e; \
     e = rg_launch(decode_attention_kernel<DM, EX>, grid, dim3(NTHREADS), smem, s, 1, (const bf16*)q, q_stride, \
-        (const bf16*)kv_cache, block_table, max_blocks, rows, req_of_token, positions, part_o, part_ml, nh, nkv, d, \
-        page_size, page_shift, window, scale_log2, num_splits, head_tiles); }
+        (const bf16*)kv_cache, block_table, max_blocks, rows, req_of_token, positions, part_o, part_ml, (bf16*)out, \
+        counters, nh, nkv, d, page_size, page_shift, window, scale_log2, num_splits, head_tiles); }
     if (d == 64) RG_DECODE(64, true) else if (d == 128) RG_DECODE(128, true)
     else if (d < 64) RG_DECODE(64, false) else if (d < 128) RG_DECODE(128, false) else RG_DECODE(256, false)
 #undef RG_DECODE
-    if (e) return e;
+    if (e || counters != nullptr) return e;
     dim3 rgrid(n_tokens, nh);
     return rg_launch(decode_reduce_kernel, rgrid, dim3(d >= 128 ? 128 : 64), 0, s, 1, (const float*)part_o,
                      (const float*)part_ml, (bf16*)out, rows, nh, d, num_splits);
@@ -694,7 +736,10 @@ extern "C" int rg_decode_attention_static_scratch(
     // part_o floats, rounded up to 64 floats (256 bytes), then part_ml
     const unsigned long long slots = (unsigned long long)n_tokens * num_heads * num_splits;
     const unsigned long long o_floats = (slots * head_dim + 63ull) / 64ull * 64ull;
-    const unsigned long long need = (o_floats + slots * 2ull) * sizeof(float);
+    const unsigned long long ml_floats = (slots * 2ull + 63ull) / 64ull * 64ull;
+    const unsigned long long n_counters = (unsigned long long)n_tokens * num_kv_heads *
+                                          ((num_heads / (num_kv_heads > 0 ? num_kv_heads : 1) + 7) / 8);
+    const unsigned long long need = (o_floats + ml_floats + n_counters) * sizeof(float);
     if (need > RG_STATIC_SCRATCH_BYTES) {
         char msg[256];
         snprintf(msg, sizeof msg,
@@ -724,9 +769,19 @@ extern "C" int rg_decode_attention_static_scratch(
         }
         base = rg_static_scratch_ptr[dev];
     }
+    // The counters start at zero (a __device__ array is zeroed when the library is loaded) and every launch
+    // leaves them at zero; they sit behind this call's partial results, which is why a call must not overlap
+    // another one.  The counters' place depends on the sizes, so they are cleared when the sizes change.
+    static unsigned long long last_counter_offset[RG_MAX_DEVICES];
+    int* counters = reinterpret_cast<int*>(base + o_floats + ml_floats);
+    if (last_counter_offset[dev] != o_floats + ml_floats + 1) {
+        cudaError_t ce = cudaMemsetAsync(counters, 0, n_counters * sizeof(int), (cudaStream_t)stream);
+        if (ce != cudaSuccess) { rg_set_error(error_text, error_cap, cudaGetErrorString(ce)); return (int)ce; }
+        last_counter_offset[dev] = o_floats + ml_floats + 1;
+    }
     const int code = rg_decode_attention(q, q_stride, out, kv_cache, block_table, max_blocks, rows, n_tokens,
-                                         req_of_token, positions, base, base + o_floats, num_heads, num_kv_heads,
-                                         head_dim, page_size, window, scale, num_splits, stream);
+                                         req_of_token, positions, base, base + o_floats, counters, num_heads,
+                                         num_kv_heads, head_dim, page_size, window, scale, num_splits, stream);
     if (code == RG_ERR_UNSUPPORTED)
         rg_set_error(error_text, error_cap, "the kernels refuse these sizes (head_dim 16..256 in steps of 16, "
                                             "num_heads a multiple of num_kv_heads)");

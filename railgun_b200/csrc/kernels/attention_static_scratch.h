@@ -25,9 +25,13 @@
 // capture begins.  Later calls do no set-up.
 //
 // All calls share the one array and it keeps the last call's contents.  The
-// kernels write every slot they later read, so nothing has to be cleared
-// between calls; but two calls whose kernels overlap on the GPU (different
-// streams, no ordering between them) race on it.  Order them.
+// kernels write every partial result they later read; the per-token counters
+// that tell the last block to reduce must be zero on entry, are left at zero by
+// every launch, and are cleared by the call itself (cudaMemsetAsync on the
+// caller's stream, no allocation) whenever the sizes, and with them the
+// counters' place in the array, change.  Two calls whose kernels overlap on the
+// GPU (different streams, no ordering between them) race on the array.  Order
+// them.
 //
 // It calls no cudaMalloc, cudaFree or allocating library routine.
 #pragma once

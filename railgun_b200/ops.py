@@ -287,13 +287,22 @@ def decode_splits(n_tokens: int, kv_tiles: int, max_context: int) -> int:
     return max(1, min(by_residency, by_length, 256))
 
 
+_decode_counters: dict = {}
+
+
 def decode_attention(q, q_stride: int, out, kv_cache, block_table, rows, n_tokens: int, req_of_token, positions,
                      nh: int, nkv: int, d: int, window: int, scale: float, num_splits: int,
-                     scratch=None) -> None:
+                     scratch=None, fused_reduce=None) -> None:
     """Split attention for single tokens: token rows ``rows`` (None: rows
     0..n_tokens-1) each attend their request's context.  Partial results go
     through scratch memory (allocated here unless given) and are reduced into
-    ``out`` [T, nh*d]."""
+    ``out`` [T, nh*d]: by the block that finishes last for each token and head
+    tile (``fused_reduce``, always in split order) or by a second kernel.
+    Default: fused when there is a single split (the kernel then writes the
+    result itself), a second kernel otherwise (measured faster: the last block
+    would reduce alone at the end of the launch)."""
+    if fused_reduce is None:
+        fused_reduce = num_splits == 1
     page_size = _check_paged(q, kv_cache, block_table, nkv, d)
     _check(req_of_token, "req_of_token", torch.int32)
     _check(positions, "positions", torch.int32)
@@ -307,11 +316,19 @@ def decode_attention(q, q_stride: int, out, kv_cache, block_table, rows, n_token
         part_o, part_ml = scratch
         if part_o.numel() < n_tokens * nh * num_splits * d or part_ml.numel() < n_tokens * nh * num_splits * 2:
             raise KernelError("decode_attention: the scratch buffers are too small")
-    _COUNTER.value += 1                      # the launcher runs two kernels: partial results, then the reduction
+    counters = None
+    if fused_reduce:
+        # one counter per (token, kv head, tile of 8 query heads): zero on entry, left zero by the kernel
+        need = n_tokens * nkv * (-(-(nh // nkv) // 8))
+        counters = _decode_counters.get(q.device)
+        if counters is None or counters.numel() < need:
+            counters = _decode_counters[q.device] = torch.zeros(max(need, 4096), dtype=torch.int32, device=q.device)
+    else:
+        _COUNTER.value += 1                  # the launcher runs two kernels: partial results, then the reduction
     _ok(_fn("attention_mma", "rg_decode_attention")(
         _ptr(q), c_int(q_stride), _ptr(out), _ptr(kv_cache), _ptr(block_table), c_int(block_table.shape[1]),
         _ptr(rows), c_int(n_tokens), _ptr(req_of_token), _ptr(positions), _ptr(part_o), _ptr(part_ml),
-        c_int(nh), c_int(nkv), c_int(d), c_int(page_size), c_int(window or 0), c_float(scale),
+        _ptr(counters), c_int(nh), c_int(nkv), c_int(d), c_int(page_size), c_int(window or 0), c_float(scale),
         c_int(num_splits), _stream()), "decode_attention")
 
 

@@ -349,8 +349,18 @@ def test_decode_attention_mma(case_id, splits):
     req = torch.tensor(c["req"], dtype=torch.int32, device=DEV)
     pos = torch.tensor(c["positions"], dtype=torch.int32, device=DEV)
     ops.decode_attention(q, nh * d, out, c["kv"].to(DEV), c["bt"].to(DEV), None, T, req, pos, nh, nkv, d, window,
-                         scale, splits)
+                         scale, splits, fused_reduce=True)
     assert rel_err(out, ref) < 1e-2
+    # the reduction as a second kernel gives the same numbers as the one fused into the last block
+    two = torch.full((T, nh * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.decode_attention(q, nh * d, two, c["kv"].to(DEV), c["bt"].to(DEV), None, T, req, pos, nh, nkv, d, window,
+                         scale, splits, fused_reduce=False)
+    assert torch.equal(two, out)
+    # and again: the counters were left at zero
+    again = torch.full((T, nh * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.decode_attention(q, nh * d, again, c["kv"].to(DEV), c["bt"].to(DEV), None, T, req, pos, nh, nkv, d, window,
+                         scale, splits, fused_reduce=True)
+    assert torch.equal(again, out)
     # a subset of rows, in another order, through the row list: the other rows stay untouched
     if T >= 3:
         rows = torch.tensor([T - 1, 0, T // 2], dtype=torch.int32, device=DEV)
