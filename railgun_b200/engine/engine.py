@@ -51,24 +51,36 @@ class Engine:
     def step(self) -> list:
         """One scheduler decision and one model step.  Returns the (request id,
         sampled token) pairs of this step, or None if nothing could be scheduled."""
-        entries = self.scheduler.schedule()
-        if not entries:
+        ids, starts, counts, wants, tokens = self.scheduler.schedule_flat()
+        n = len(ids)
+        if n == 0:
             return None
-        batch = [StepEntry(e.request_id, e.tokens, [len(e.tokens) - 1] if e.want_last else []) for e in entries]
-        logits = self.runner.step(batch)
         self.steps_run += 1
-        wanted = [e.request_id for e in entries if e.want_last]
+        if self.runner.use_graphs and len(tokens) == n and wants.all():
+            # every request brings one token and wants its logits: straight to the decode graph
+            wanted = ids.tolist()
+            logits = self.runner.decode_step_flat(ids, tokens)
+        else:
+            batch, off, wanted = [], 0, []
+            for i in range(n):
+                c = int(counts[i])
+                rid = int(ids[i])
+                batch.append(StepEntry(rid, tokens[off:off + c], [c - 1] if wants[i] else []))
+                if wants[i]:
+                    wanted.append(rid)
+                off += c
+            logits = self.runner.step(batch)
         if logits is None:
             self.scheduler.update([], [])
             return []
         params = [self._params[r] for r in wanted]
         if self.runner.last_greedy is not None and all(p.temperature == 0.0 for p in params):
-            tokens = self.runner.last_greedy.cpu().numpy()      # the decode graph already took the argmax
+            sampled = self.runner.last_greedy.cpu().numpy()     # the decode graph already took the argmax
         else:
-            tokens = self.sampler.sample(logits, params, [self.scheduler.num_generated(r) for r in wanted])
+            sampled = self.sampler.sample(logits, params, [self.scheduler.num_generated(r) for r in wanted])
         ops.tc_gemm_check()                 # the tokens are on the host: the step has finished
-        self.scheduler.update(wanted, tokens)
-        return list(zip(wanted, tokens.tolist()))
+        self.scheduler.update(wanted, sampled)
+        return list(zip(wanted, sampled.tolist()))
 
     def abort(self, request_id: int) -> None:
         self.scheduler.abort(request_id)

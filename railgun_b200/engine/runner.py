@@ -243,6 +243,15 @@ class ModelRunner:
         tokens = np.fromiter((e.tokens[0] for e in entries), dtype=np.int32, count=R)
         if len(set(ids.tolist())) != R:
             raise BatchError("a request appears twice in one step")
+        return self.decode_step_flat(ids, tokens)
+
+    def decode_step_flat(self, ids: np.ndarray, tokens: np.ndarray) -> torch.Tensor:
+        """One decode step for requests already in the cache: ``ids`` int64
+        (distinct), ``tokens`` int32, one token each, logits wanted for all.
+        Returns the logits [R, V] (a view of a static buffer); the greedy tokens
+        are in ``last_greedy``."""
+        R = len(ids)
+        self.last_greedy = None
         if tokens.min() < 0 or tokens.max() >= self.model.vocab_size:
             raise BatchError(f"token ids must be in [0, {self.model.vocab_size})")
         ctx = max(self._ctx_hint + 1, 1)

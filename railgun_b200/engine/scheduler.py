@@ -70,8 +70,26 @@ class Scheduler:
         if code:
             raise SchedulerError(f"request {request_id}: {_ADD_ERRORS.get(code, code)}")
 
+    def schedule_flat(self):
+        """Decide the next step and return it as arrays (views, valid until the
+        next call): request ids [n], start positions [n], token counts [n],
+        wants-logits flags [n], and all tokens one after the other."""
+        n = self._schedule_raw()
+        total = int(self._count[:n].sum()) if n else 0
+        return self._ids[:n], self._start[:n], self._count[:n], self._want[:n], self._tokens[:total]
+
     def schedule(self) -> list:
         """Decide the next step: a list of ScheduledEntry (maybe empty)."""
+        n = self._schedule_raw()
+        out, off = [], 0
+        for i in range(n):
+            c = int(self._count[i])
+            out.append(ScheduledEntry(int(self._ids[i]), int(self._start[i]), self._tokens[off:off + c].copy(),
+                                      bool(self._want[i])))
+            off += c
+        return out
+
+    def _schedule_raw(self) -> int:
         n = self._lib.rg_sched_schedule(self._h, self._ids.ctypes.data, self._start.ctypes.data,
                                         self._count.ctypes.data, self._want.ctypes.data, self._ids.size,
                                         self._tokens.ctypes.data, self._tokens.size)
@@ -86,13 +104,7 @@ class Scheduler:
                                          self._tokens.ctypes.data, self._tokens.size)
         if n < 0:
             raise SchedulerError(f"schedule failed with status {n}")
-        out, off = [], 0
-        for i in range(n):
-            c = int(self._count[i])
-            out.append(ScheduledEntry(int(self._ids[i]), int(self._start[i]), self._tokens[off:off + c].copy(),
-                                      bool(self._want[i])))
-            off += c
-        return out
+        return n
 
     def preempted(self) -> list:
         n = self._lib.rg_sched_preempted(self._h, self._scratch.ctypes.data, self._scratch.size)
