@@ -63,6 +63,8 @@ class StepBatch:
     num_prefill_tiles: int = 0
     decode_rows: torch.Tensor | None = None
     num_decode_rows: int = 0
+    prefill_tiles128: torch.Tensor | None = None     # the same requests in tiles of up to 128 positions
+    num_prefill_tiles128: int = 0
 
 
 def build_step_batch(entries, alloc, page_sizes, vocab_size: int, max_position: int, device,
@@ -115,7 +117,7 @@ def build_step_batch(entries, alloc, page_sizes, vocab_size: int, max_position: 
     tables = [[alloc.block_table(e.request_id, g) for e in entries] for g in range(G)]
     max_blocks = [max(1, max(len(t) for t in tables[g])) for g in range(G)]
 
-    tiles, dec_rows = [], []
+    tiles, tiles128, dec_rows = [], [], []
     off = 0
     for i, c in enumerate(counts):
         c = int(c)
@@ -123,11 +125,12 @@ def build_step_batch(entries, alloc, page_sizes, vocab_size: int, max_position: 
             dec_rows.append(off)
         else:
             tiles += [(off + k, min(ATTENTION_TILE_ROWS, c - k), i) for k in range(0, c, ATTENTION_TILE_ROWS)]
+            tiles128 += [(off + k, min(128, c - k), i) for k in range(0, c, 128)]
         off += c
     sizes = [T, T, T, W, R + 1, R, R, R]
     for g in range(G):
         sizes += [T, R * max_blocks[g]]
-    sizes += [3 * len(tiles), len(dec_rows)]
+    sizes += [3 * len(tiles), len(dec_rows), 3 * len(tiles128)]
     offs = np.concatenate([[0], np.cumsum(sizes)])
     buf = torch.empty(int(offs[-1]), dtype=torch.int32, pin_memory=torch.cuda.is_available())
     host = buf.numpy()
@@ -159,6 +162,8 @@ def build_step_batch(entries, alloc, page_sizes, vocab_size: int, max_position: 
         seg(8 + 2 * G)[:] = np.asarray(tiles, dtype=np.int32).reshape(-1)
     if dec_rows:
         seg(9 + 2 * G)[:] = np.asarray(dec_rows, dtype=np.int32)
+    if tiles128:
+        seg(10 + 2 * G)[:] = np.asarray(tiles128, dtype=np.int32).reshape(-1)
     dev = buf.to(device, non_blocking=True)
     d = lambda i: dev[int(offs[i]):int(offs[i + 1])]
     return StepBatch(
@@ -173,4 +178,5 @@ def build_step_batch(entries, alloc, page_sizes, vocab_size: int, max_position: 
         decode_only=bool(counts.max() == 1),
         prefill_tiles=d(8 + 2 * G).view(-1, 3) if tiles else None, num_prefill_tiles=len(tiles),
         decode_rows=d(9 + 2 * G) if dec_rows else None, num_decode_rows=len(dec_rows),
+        prefill_tiles128=d(10 + 2 * G).view(-1, 3) if tiles128 else None, num_prefill_tiles128=len(tiles128),
     )

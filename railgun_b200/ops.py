@@ -378,6 +378,42 @@ def tc_gemm(x: torch.Tensor, weight: torch.Tensor, out_dtype=None, silu_mul: boo
 _tc_unchecked = False
 
 
+def prefill_attention_tc_ok(q, kv_cache, d: int, page_size: int) -> bool:
+    """Can the tcgen05 flash kernel take this?  bfloat16, head size 64, pages of 8, 16, 32, 64 or 128 tokens."""
+    return (q.is_cuda and q.dtype == torch.bfloat16 and d == 64 and page_size in (8, 16, 32, 64, 128)
+            and q.dim() == 2 and q.stride(1) == 1 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0
+            and kv_cache.is_contiguous())
+
+
+def prefill_attention_tc(q, out, kv_cache, block_table, tiles, positions, nh: int, nkv: int, d: int,
+                         window: int, scale: float) -> None:
+    """Flash attention on the tcgen05 tensor cores for requests that bring
+    several tokens: ``q`` is the fused qkv buffer [T, (nh + 2 nkv) d], ``tiles``
+    [n, 3] = (first row, rows <= 128, request index).  Writes the tiles' rows
+    of ``out`` [T, nh*d].  Its waits are bounded; ``tc_gemm_check()`` raises if
+    one gave up."""
+    page_size = kv_cache.shape[3]
+    if not prefill_attention_tc_ok(q, kv_cache, d, page_size):
+        raise KernelError("prefill_attention_tc: bfloat16, head size 64, page size 8..128 dividing 128")
+    _check(kv_cache, "kv_cache", q.dtype)
+    _check(block_table, "block_table", torch.int32)
+    _check(tiles, "tiles", torch.int32)
+    _check(positions, "positions", torch.int32)
+    _check(out, "out", q.dtype)
+    if tuple(kv_cache.shape[1:]) != (2, nkv, page_size, d):
+        raise KernelError(f"kv cache shape {tuple(kv_cache.shape)} does not match heads {nkv} x {d}")
+    err = _tc_err.get(q.device)
+    if err is None:
+        err = _tc_err[q.device] = torch.zeros(1, dtype=torch.int32, device=q.device)
+    global _tc_unchecked
+    _tc_unchecked = True
+    _ok(_fn("attention_tcgen05", "rg_prefill_attention_tc")(
+        _ptr(q), c_int(q.stride(0)), c_int(q.shape[0]), _ptr(out), _ptr(kv_cache), c_int(kv_cache.shape[0]),
+        _ptr(block_table), c_int(block_table.shape[1]), _ptr(tiles), c_int(tiles.shape[0]), _ptr(positions),
+        c_int(nh), c_int(nkv), c_int(d), c_int(page_size), c_int(window or 0), c_float(scale), _ptr(err),
+        _stream()), "prefill_attention_tc")
+
+
 def tc_gemm_check(device=None) -> None:
     """Raise if a wait inside a tcgen05 product gave up since the last check
     (synchronises; free when no such product ran since)."""
@@ -391,8 +427,9 @@ def tc_gemm_check(device=None) -> None:
         code = int(err.item())
         if code:
             err.zero_()
-            who = {1: "the TMA producer", 2: "the MMA issuer", 3: "the epilogue"}.get(code, f"role {code}")
-            raise KernelError(f"tc_gemm: {who} gave up waiting on a barrier; the result is invalid")
+            who = {1: "the TMA producer", 2: "the MMA issuer", 3: "the epilogue", 4: "the MMA issuer"}.get(
+                code, f"role {code} of the attention kernel")
+            raise KernelError(f"a tcgen05 kernel: {who} gave up waiting on a barrier; the result is invalid")
 
 
 def argmax(logits: torch.Tensor) -> torch.Tensor:

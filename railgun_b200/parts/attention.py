@@ -9,6 +9,8 @@ the same numbers as three products.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from .. import ops
@@ -16,6 +18,11 @@ from ..cache.manager import PagedKVNeed
 from ..weights.loader import TensorSpec
 from .base import Mixer
 from .registry import register_mixer, POSITION_ENCODINGS
+
+
+# The tcgen05 flash kernel takes portions of prompts when the head size is 64 and pages hold 8..128 tokens;
+# RAILGUN_B200_TC_ATTENTION=0 sends them to the mma.sync kernel instead.
+USE_TC_ATTENTION = os.environ.get("RAILGUN_B200_TC_ATTENTION", "1") != "0"
 
 
 class PagedAttention(Mixer):
@@ -92,8 +99,13 @@ class PagedAttention(Mixer):
                                  ops.decode_splits(n, kv_tiles, batch.max_context_len))
             return out
         if batch.num_prefill_tiles:
-            ops.prefill_attention(qkv, qkv.shape[1], out, cache.kv, table, batch.prefill_tiles, batch.positions,
-                                  nh, nkv, d, self.window, self.scale)
+            if USE_TC_ATTENTION and batch.num_prefill_tiles128 and ops.prefill_attention_tc_ok(
+                    qkv, cache.kv, d, cache.page_size):
+                ops.prefill_attention_tc(qkv, out, cache.kv, table, batch.prefill_tiles128, batch.positions,
+                                         nh, nkv, d, self.window, self.scale)
+            else:
+                ops.prefill_attention(qkv, qkv.shape[1], out, cache.kv, table, batch.prefill_tiles, batch.positions,
+                                      nh, nkv, d, self.window, self.scale)
         if batch.num_decode_rows:
             n = batch.num_decode_rows
             ops.decode_attention(qkv, qkv.shape[1], out, cache.kv, table, batch.decode_rows, n, batch.req_of_token,

@@ -506,3 +506,72 @@ def test_tc_gemm_refusals():
     assert not ops.tc_gemm_ok(torch.zeros(2, 24, device=DEV), torch.zeros(32, 24, device=DEV))  # 32-bit
     with pytest.raises(ops.KernelError):
         ops.tc_gemm(torch.zeros(2, 20, dtype=torch.bfloat16, device=DEV), w)
+
+
+# ---- the tcgen05 flash attention kernel (head size 64) ----------------------------------------------------
+
+TC_ATT_CASES = [
+    # nh, nkv, page, ctx_lens, q_lens, window
+    (1, 1, 16, [128], [128], 0),
+    (2, 1, 16, [70], [70], 0),
+    (4, 2, 16, [300, 41], [300, 41], 0),
+    (8, 2, 8, [1000, 130, 64, 65], [500, 130, 64, 3], 0),          # portions that start inside a context
+    (4, 4, 32, [700], [260], 100),                                 # a window
+    (5, 5, 64, [129, 257], [2, 129], 0),
+    (3, 1, 128, [400], [400], 37),
+    (32, 8, 16, [1500], [1500], 0),                                # the 1B model's shape
+]
+
+
+@pytest.mark.parametrize("case_id", range(len(TC_ATT_CASES)))
+def test_prefill_attention_tcgen05(case_id):
+    from railgun_b200 import ops
+    nh, nkv, page, ctx, ql, window = TC_ATT_CASES[case_id]
+    d = 64
+    c = make_paged_case(len(ctx), ctx, ql, nh, nkv, d, page, torch.bfloat16, seed=300 + case_id)
+    ref = attention_reference(c, nh, nkv, d, page, window, d ** -0.5)
+    wide = torch.zeros(c["T"], (nh + 2 * nkv) * d, dtype=torch.bfloat16)
+    wide[:, :nh * d] = c["q"].reshape(c["T"], nh * d)
+    tiles, off = [], 0
+    for r, n in enumerate(ql):
+        tiles += [(off + k, min(128, n - k), r) for k in range(0, n, 128)]
+        off += n
+    out = torch.full((c["T"], nh * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.prefill_attention_tc(wide.to(DEV), out, c["kv"].to(DEV), c["bt"].to(DEV),
+                             torch.tensor(tiles, dtype=torch.int32, device=DEV),
+                             torch.tensor(c["positions"], dtype=torch.int32, device=DEV), nh, nkv, d, window, d ** -0.5)
+    ops.tc_gemm_check()
+    assert rel_err(out, ref) < 1e-2
+
+
+def test_prefill_attention_tcgen05_finds_a_far_key():
+    from railgun_b200 import ops
+    nh, nkv, d, page = 4, 2, 64, 16
+    for needle in (0, 15, 16, 127, 128, 351, 698):
+        c = make_paged_case(1, [700], [1], nh, nkv, d, page, torch.bfloat16, seed=needle)
+        pg, off = c["tables"][0][needle // page], needle % page
+        c["kv"][pg, 0] *= 0.05
+        c["kv"][pg, 0, :, off, :] = (c["q"][0, ::2, :] * 4).to(torch.bfloat16)
+        ref = attention_reference(c, nh, nkv, d, page, 0, d ** -0.5)
+        q = torch.zeros(1, (nh + 2 * nkv) * d, dtype=torch.bfloat16)
+        q[:, :nh * d] = c["q"].reshape(1, nh * d)
+        out = torch.zeros(1, nh * d, dtype=torch.bfloat16, device=DEV)
+        ops.prefill_attention_tc(q.to(DEV), out, c["kv"].to(DEV), c["bt"].to(DEV),
+                                 torch.tensor([[0, 1, 0]], dtype=torch.int32, device=DEV),
+                                 torch.tensor([699], dtype=torch.int32, device=DEV), nh, nkv, d, 0, d ** -0.5)
+        ops.tc_gemm_check()
+        assert rel_err(out, ref) < 1e-2
+
+
+def test_prefill_attention_tcgen05_refuses_other_shapes():
+    from railgun_b200 import ops
+    q = torch.zeros(4, 3 * 128, dtype=torch.bfloat16, device=DEV)
+    kv128 = torch.zeros(2, 2, 1, 16, 128, dtype=torch.bfloat16, device=DEV)
+    assert not ops.prefill_attention_tc_ok(q, kv128, 128, 16)                       # head size
+    kv = torch.zeros(2, 2, 1, 12, 64, dtype=torch.bfloat16, device=DEV)
+    assert not ops.prefill_attention_tc_ok(q, kv, 64, 12)                           # page size
+    with pytest.raises(ops.KernelError):
+        ops.prefill_attention_tc(q, torch.zeros(4, 64, dtype=torch.bfloat16, device=DEV), kv,
+                                 torch.zeros(1, 1, dtype=torch.int32, device=DEV),
+                                 torch.tensor([[0, 4, 0]], dtype=torch.int32, device=DEV),
+                                 torch.zeros(4, dtype=torch.int32, device=DEV), 1, 1, 64, 0, 1.0)
