@@ -73,6 +73,17 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&v)[32]) {
                  : "r"(taddr) : "memory");
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void tc_ld32_nowait(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                   "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+                   "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+                   "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                 : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
@@ -245,30 +256,37 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ 
             const bool edge = key_base + FA_BN - 1 > p0 || (window > 0 && key_base < p0 + FA_BM - window);
             const int k_hi = prow - key_base;                                 // columns <= k_hi are not in the future
             const int k_lo = window > 0 ? prow - window + 1 - key_base : -1;  // columns >= k_lo are inside the window
-            // pass 1: the row's maximum, on the raw scores (scale > 0, so the maximum commutes with it)
-            float mx = -INFINITY;
+            // pass 1: the row's maximum, on the raw scores (scale > 0, so the maximum commutes with it); two
+            // chunks of 32 columns in flight per wait, four independent running maxima
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll 1
-            for (int c = 0; c < FA_BN / 32; ++c) {
-                uint32_t v[32];
-                tc_ld32(tmem_s + lane_off + (uint32_t)(c * 32), v);
+            for (int c = 0; c < FA_BN / 32; c += 2) {
+                uint32_t v[32], w[32];
+                tc_ld32_nowait(tmem_s + lane_off + (uint32_t)(c * 32), v);
+                tc_ld32_nowait(tmem_s + lane_off + (uint32_t)(c * 32 + 32), w);
+                tc_ld_wait();
                 if (!edge) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
+                    for (int i = 0; i < 32; ++i) {
+                        mx4[i & 3] = fmaxf(mx4[i & 3], fmaxf(__uint_as_float(v[i]), __uint_as_float(w[i])));
+                    }
                 } else {
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
                         const int col = c * 32 + i;
-                        if (col <= k_hi && col >= k_lo) mx = fmaxf(mx, __uint_as_float(v[i]));
+                        if (col <= k_hi && col >= k_lo) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(v[i]));
+                        if (col + 32 <= k_hi && col + 32 >= k_lo) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(w[i]));
                     }
                 }
             }
+            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             mx *= scale_log2;
             const float mn = fmaxf(m_run, mx);
             const float ms = mn == -INFINITY ? 0.f : mn;
             const float alpha = ex2(m_run - ms);
             m_run = mn;
             // pass 2: p = 2^(s scale - m), row sum, P -> shared memory (bfloat16, 16-byte pieces XOR-swizzled by row)
-            float rs = 0.f;
+            float rs4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 1
             for (int c = 0; c < FA_BN / 32; ++c) {
                 uint32_t v[32];
@@ -279,7 +297,7 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ 
                     for (int i = 0; i < 32; i += 2) {
                         const float p0v = ex2(fmaf(__uint_as_float(v[i]), scale_log2, -ms));
                         const float p1v = ex2(fmaf(__uint_as_float(v[i + 1]), scale_log2, -ms));
-                        rs += p0v + p1v;
+                        rs4[(i >> 1) & 3] += p0v + p1v;
                         __nv_bfloat162 hh = __floats2bfloat162_rn(p0v, p1v);
                         pk[i >> 1] = *reinterpret_cast<uint32_t*>(&hh);
                     }
@@ -291,7 +309,7 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ 
                                               ? ex2(fmaf(__uint_as_float(v[i]), scale_log2, -ms)) : 0.f;
                         const float p1v = (col + 1 <= k_hi && col + 1 >= k_lo)
                                               ? ex2(fmaf(__uint_as_float(v[i + 1]), scale_log2, -ms)) : 0.f;
-                        rs += p0v + p1v;
+                        rs4[(i >> 1) & 3] += p0v + p1v;
                         __nv_bfloat162 hh = __floats2bfloat162_rn(p0v, p1v);
                         pk[i >> 1] = *reinterpret_cast<uint32_t*>(&hh);
                     }
@@ -305,7 +323,7 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ 
                                  "r"(pk[q4 * 4]), "r"(pk[q4 * 4 + 1]), "r"(pk[q4 * 4 + 2]), "r"(pk[q4 * 4 + 3]) : "memory");
                 }
             }
-            l_run = l_run * alpha + rs;
+            l_run = l_run * alpha + ((rs4[0] + rs4[1]) + (rs4[2] + rs4[3]));
             tc_fence_before();
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // P must be visible to the tensor core
             __syncwarp();
