@@ -7,6 +7,13 @@ where these tests run, and its forward pass leaves out the rotary embedding
 formulas below are the architecture's own, with the reference cited for the
 order of operations, tensor names and conventions.
 
+Three of the reference's CUDA kernels do compile as host C++ through a small
+stand-in header; ``tests/golden/make_reference_kernel_golden.py`` ran them once
+and ``tests/test_golden.py`` holds ``attention`` and ``rope`` below against
+their stored outputs (cache layout, head grouping, softmax-weighted values for
+a single query, rotation of pairs (i, i + d/2)).  Everything else rests on the
+formulas.
+
 Whole sequences, no cache, float64 arithmetic, one function per part.  It
 shares no code with ``railgun_b200``: it reads config.json and
 model.safetensors itself.
