@@ -14,95 +14,17 @@
 // Same formulas and masks as attention_mma.cu's prefill kernel (s = scale q.k, keys [max(0, p - w + 1), p],
 // crates/vllm-cuda/src/kernels/paged_attention.cu:40,66-69,103-107); the reference has no prefill attention.
 // Every mbarrier wait is bounded and reports through *err (see gemm_tcgen05.cu).
-#include "common.cuh"
-#include <cuda.h>
+#include "tcgen05.cuh"
 
 #define FA_BM 128
 #define FA_BN 128
 #define FA_D 64
 #define FA_THREADS 192            // warps 0-3: softmax / output rows; warp 4: TMA producer; warp 5: MMA issue, TMEM owner
-#define FA_SPIN_LIMIT 1000000u
 
-__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* err, int code, volatile int* abort_flag) {
-    for (uint32_t i = 0; i < FA_SPIN_LIMIT; ++i) {
-        uint32_t ok;
-        asm volatile("{\n\t.reg .pred p;\n\t"
-                     "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-                     "selp.u32 %0, 1, 0, p;\n\t}"
-                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-        if (ok) return true;
-        if ((i & 1023u) == 1023u && *abort_flag) return false;
-    }
-    atomicCAS(err, 0, code);
-    *abort_flag = 1;
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\t"
-                 "setp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
-}
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&v)[32]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-                   "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
-                   "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
-                   "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-                 : "r"(taddr) : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tc_ld32_nowait(uint32_t taddr, uint32_t (&v)[32]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-                   "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
-                   "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
-                   "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-                 : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
     return y;
-}
-
-// Operand descriptors for tiles whose rows are 128 bytes with the 128-byte swizzle (what TMA writes), groups of
-// 8 rows 1024 bytes apart: start address >> 4 in bits [0,14), leading byte offset >> 4 in [16,30), stride byte
-// offset >> 4 in [32,46), version 1 in [46,48), SWIZZLE_128B = 2 in [61,64).
-//  - K-major (Q, K, P: the contraction runs along a row): LBO unused (1), SBO = 1024.
-//  - MN-major (V as [key][dim]: the contraction runs down the rows, 8 rows per 1024-byte group): SBO = 1024
-//    between groups of 8 keys; LBO = distance between 64-element blocks along dim (one block here).
-__device__ __forceinline__ uint64_t desc_k_major(uint32_t saddr) {
-    return (uint64_t)((saddr >> 4) & 0x3FFFu) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
-           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
-}
-__device__ __forceinline__ uint64_t desc_mn_major(uint32_t saddr) {
-    return (uint64_t)((saddr >> 4) & 0x3FFFu) | ((uint64_t)(16384 >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
-           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
 }
 
 // tiles: [NT][3] = first token row, rows (<= 128), request.  q_map: the fused qkv buffer [T, (nh + 2 nkv) d];
@@ -136,14 +58,9 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ 
         mbar_init(k_empty0, 1); mbar_init(k_empty0 + 8, 1);
         mbar_init(v_full, 1); mbar_init(v_empty, 1);
         mbar_init(s_full, 1); mbar_init(p_full, 4); mbar_init(o_full, 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        fence_barrier_init();
     }
-    if (warp == 5) {                                                         // S: columns [0,128), O_tile: [128,192)
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(smem_addr(&tmem_base_slot)), "r"(256u) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
+    if (warp == 5) tmem_alloc(&tmem_base_slot, 256u);                        // S: columns [0,128), O_tile: [128,192)
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -195,8 +112,8 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ 
     } else if (warp == 5 && lane == 0) {
         // ---- MMA issue
         // S: D F32, A/B BF16 K-major, N 128, M 128.  PV: the same with B MN-major (bit 16) and N 64.
-        constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(FA_BN >> 3) << 17) | ((uint32_t)(FA_BM >> 4) << 24);
-        constexpr uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(FA_D >> 3) << 17) | ((uint32_t)(FA_BM >> 4) << 24);
+        constexpr uint32_t idesc_s = make_idesc(FA_BM, FA_BN, false);
+        constexpr uint32_t idesc_o = make_idesc(FA_BM, FA_D, true);
         bool ok = mbar_wait(q_full, 0, err, 21, &abort_flag);
         if (ok) ok = mbar_wait(k_full0, 0, err, 22, &abort_flag);
         if (ok) {
@@ -218,7 +135,7 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ 
                 // P: two 64-key halves of [128 rows x 128 bytes]; inside a half, 16 keys = 32 bytes
                 const uint64_t pd = desc_k_major(sP + (uint32_t)(k >> 2) * TILE_BYTES) + 2u * (k & 3);
                 // V: 16 keys further down = 16 rows of 128 bytes
-                const uint64_t vd = desc_mn_major(sV + (uint32_t)k * 2048u);
+                const uint64_t vd = desc_mn_major(sV + (uint32_t)k * 2048u, 16384u);
                 tc_mma(tmem_o, pd, vd, idesc_o, k > 0 ? 1u : 0u);
             }
             tc_commit(o_full);
@@ -364,37 +281,8 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ 
     }
     if (warp == 5) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base_slot), "r"(256u) : "memory");
+        tmem_free(tmem_base_slot, 256u);
     }
-}
-
-// ---- host side ----
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-static EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)p;
-    }
-    return fn;
-}
-static int make_map(CUtensorMap* map, const void* ptr, unsigned long long rows, int cols, unsigned long long ld,
-                    int box_rows) {
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) return RG_ERR_UNSUPPORTED;
-    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? 0 : 20000 + (int)r;
 }
 
 // q: the fused qkv buffer [n_rows_total, q_stride] (head h of q at column h * 64); out [n_rows_total, nh * 64];
@@ -409,9 +297,9 @@ extern "C" int rg_prefill_attention_tc(const void* q, int q_stride, int n_rows_t
         ((uintptr_t)q & 15) || ((uintptr_t)kv_cache & 15) || nh > 65535)
         return RG_ERR_UNSUPPORTED;
     CUtensorMap qm, kvm;
-    int e = make_map(&qm, q, (unsigned long long)n_rows_total, q_stride, (unsigned long long)q_stride, FA_BM);
+    int e = rg_make_map(&qm, q, (unsigned long long)n_rows_total, (unsigned long long)q_stride, (unsigned long long)q_stride, FA_BM);
     if (e) return e;
-    e = make_map(&kvm, kv_cache, (unsigned long long)num_pages * 2ull * nkv * page_size, FA_D, FA_D, page_size);
+    e = rg_make_map(&kvm, kv_cache, (unsigned long long)num_pages * 2ull * nkv * page_size, FA_D, FA_D, page_size);
     if (e) return e;
     const size_t smem = 6 * 128 * 128 + 128 + 1024;
     cudaError_t ce = cudaFuncSetAttribute(fa_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -12,78 +12,13 @@
 // Every wait on an mbarrier is bounded: after RG_SPIN_LIMIT tries the waiter records where it gave up in *err,
 // every role stops, the CTA waits for copies that may still be in flight, frees its TMEM and returns; the
 // host reads *err and raises.
-#include "common.cuh"
-#include <cuda.h>
+#include "tcgen05.cuh"
 
 #define TC_BM 128
 #define TC_BK 64
 #define TC_THREADS 192            // warps 0-3: epilogue; warp 4: TMA producer; warp 5: MMA issue and TMEM owner
-#define RG_SPIN_LIMIT 1000000u
 #define EPI_NONE 0
 #define EPI_SILU_MUL 1
-
-__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-// Bounded wait for the phase with this parity.  false: gave up (the code is left in *err).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* err, int code, volatile int* abort_flag) {
-    for (uint32_t i = 0; i < RG_SPIN_LIMIT; ++i) {
-        uint32_t ok;
-        asm volatile("{\n\t.reg .pred p;\n\t"
-                     "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-                     "selp.u32 %0, 1, 0, p;\n\t}"
-                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-        if (ok) return true;
-        if ((i & 1023u) == 1023u && *abort_flag) return false;
-    }
-    atomicCAS(err, 0, code);
-    *abort_flag = 1;
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\t"
-                 "setp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
-}
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&v)[32]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-                   "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
-                   "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
-                   "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-                 : "r"(taddr) : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-// Shared-memory operand descriptor: K-major tile whose rows are 128 bytes (64 bfloat16), 128-byte swizzle,
-// groups of 8 rows 1024 bytes apart.  Fields: start address >> 4 in bits [0,14), leading byte offset >> 4 in
-// [16,30) (1: unused for swizzled K-major), stride byte offset >> 4 in [32,46) (1024 >> 4), version 1 in
-// [46,48), layout type SWIZZLE_128B = 2 in [61,64).
-__device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
-    return (uint64_t)((saddr >> 4) & 0x3FFFu) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
-           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
-}
-
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
 
 // Persistent: CTA b works on tiles b, b + gridDim.x, ... (rows of C fastest, so that CTAs running at the same
 // time share a tile of B in L2).  Two accumulators in TMEM: while the epilogue warps drain one, the MMA warp
@@ -113,14 +48,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         abort_flag = 0;
         for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(acc_full(b), 1); mbar_init(acc_empty(b), 4); }
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        fence_barrier_init();
     }
-    if (warp == 5) {                                                        // this warp owns the tensor memory
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(smem_addr(&tmem_base_slot)), "r"(TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
+    if (warp == 5) tmem_alloc(&tmem_base_slot, TMEM_COLS);                  // this warp owns the tensor memory
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -145,10 +75,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
     } else if (warp == 5 && lane == 0) {
         // ---- MMA issue: D[128 x BN] (+)= A[128 x 16] B[BN x 16]^T, four K steps per stage
-        // instruction descriptor: D F32 (bits 4-5 = 1), A and B BF16 (bits 7-9, 10-12 = 1), both K-major,
-        // N >> 3 in bits 17-22, M >> 4 in bits 24-28
-        constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
-                                   ((uint32_t)(TC_BM >> 4) << 24);
+        constexpr uint32_t idesc = make_idesc(TC_BM, BN, false);
         int it = 0, local = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
@@ -161,7 +88,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 if (!mbar_wait(full_bar(s), r & 1, err, 2, &abort_flag)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t sa = base + s * STAGE_BYTES;
-                const uint64_t adesc = make_desc(sa), bdesc = make_desc(sa + A_BYTES);
+                const uint64_t adesc = desc_k_major(sa), bdesc = desc_k_major(sa + A_BYTES);
 #pragma unroll
                 for (int k = 0; k < TC_BK / 16; ++k)                        // 16 elements = 32 bytes = 2 descriptor units
                     tc_mma(tmem_d, adesc + 2u * k, bdesc + 2u * k, idesc, (kt > 0 || k > 0) ? 1u : 0u);
@@ -250,39 +177,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
     if (warp == 5) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+        tmem_free(tmem_base, TMEM_COLS);
     }
-}
-
-// ---- host side: tensor maps through the driver entry point (no link-time dependency on libcuda) ----
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)p;
-    }
-    return fn;
-}
-
-// rows x cols bfloat16, row pitch ld elements; box = box_rows x 64 columns, 128-byte swizzle, zeros out of bounds
-static int make_map(CUtensorMap* map, const void* ptr, int rows, int cols, int ld, int box_rows) {
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) return RG_ERR_UNSUPPORTED;
-    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? 0 : 20000 + (int)r;
 }
 
 template <int BN, int STAGES, int EPI, typename OUT>
@@ -315,9 +211,9 @@ extern "C" int rg_tc_gemm(const void* A, int lda, const void* B, void* out, int 
     cudaStream_t s = (cudaStream_t)stream;
     const int BN = wide ? 256 : 128;
     CUtensorMap ma, mb;
-    int e = make_map(&ma, A, M, K, lda, TC_BM);
+    int e = rg_make_map(&ma, A, M, K, lda, TC_BM);
     if (e) return e;
-    e = make_map(&mb, B, N, K, K, BN);
+    e = rg_make_map(&mb, B, N, K, K, BN);
     if (e) return e;
     if (epilogue == EPI_SILU_MUL)
         return wide ? launch_tc<256, 4, EPI_SILU_MUL, bf16>(ma, mb, (bf16*)out, ldo, M, N, K, err, s)
