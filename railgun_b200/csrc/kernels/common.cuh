@@ -74,6 +74,13 @@ __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.lau
 static int rg_pdl_enabled = 0;
 extern "C" void rg_set_pdl(int on) { rg_pdl_enabled = on; }
 
+// While one of these lives (constructed with true), launches are in plain stream order.
+struct RgStreamOrder {
+    int saved;
+    explicit RgStreamOrder(bool on) : saved(rg_pdl_enabled) { if (on) rg_pdl_enabled = 0; }
+    ~RgStreamOrder() { rg_pdl_enabled = saved; }
+};
+
 // Launch through cudaLaunchKernelEx so that the launch can carry attributes (dependent launch, clusters).
 template <typename... KArgs, typename... Args>
 static int rg_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, int cluster_x,

@@ -1,215 +1,5 @@
-// Weight-streaming matrix product for decode: y[M, N] = x[M, K] W[N, K]^T with M <= 64.
-//
-// At these sizes the product is bound by reading W once from HBM, so the
-// kernel is built around keeping many 16-byte loads of W in flight and nothing
-// else: the weight rows take the tensor core's M side (swap-AB: 16 rows of W
-// per mma, the batch on the 8-wide N side), both operand fragments come
-// straight from 16-byte global loads (the k index is permuted the same way in
-// both operands, which a dot product does not notice), W never touches shared
-// memory and bypasses L1.  The warps of a block split K and are summed through
-// shared memory in a fixed order, so a row's result depends neither on the
-// batch it is in nor on anything but its own inputs.
-//
-// Epilogues: plain (bf16 or fp32 out), and SiLU-mul for the gate|up
-// projection stored interleaved (rows 16t..16t+7 gate, 16t+8..16t+15 the
-// matching up rows), out[m, 8t + j] = silu(gate) * up in 32-bit
-// (crates/vllm-models/src/llama/architecture.rs:81-85).  The reference runs
-// these products through cuBLAS (crates/vllm-models/src/llama/attention.rs:94-96,133).
-#include "common.cuh"
-#include <cooperative_groups.h>
-namespace cg = cooperative_groups;
-
-#define EPI_NONE 0
-#define EPI_SILU_MUL 1
-
-__device__ __forceinline__ uint4 ld_stream16(const void* p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
-}
-__device__ __forceinline__ uint4 ld_cached16(const void* p) {
-    return __ldg(reinterpret_cast<const uint4*>(p));
-}
-__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                         uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-// One block: RT x 16 rows of W (from n0) and one slice of K, split over NW warps in interleaved 128-wide
-// pieces; every warp multiplies all RT row tiles by the same fragments of x.  CS blocks of a cluster share the
-// rows and take one K slice each; block 0 of the cluster adds the slices' sums, read from the other blocks'
-// shared memory, in rank order (the same order every time).
-// MT: batch rows / 8 (rounded up).  x rows are ldx elements apart.  K % 8 == 0.
-template <int MT, int NW, int CS, int RT, int EPI, typename OUT>
-__global__ void __launch_bounds__(NW * 32)
-skinny_gemm_kernel(const bf16* __restrict__ W, const bf16* __restrict__ x, int ldx, OUT* __restrict__ out, int ldo,
-                   int M, int N, int K) {
-    extern __shared__ float red[];                     // [NW][RT * 16][8 * MT], then the block's sum [RT * 16][8 * MT]
-    constexpr int COLS = 8 * MT, ROWS = RT * 16;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int g = lane >> 2, tq = lane & 3;
-    const int rank = CS > 1 ? (int)(blockIdx.x % CS) : 0;
-    const int n0 = (int)(blockIdx.x / CS) * ROWS;
-    const int slice = ((K + CS * 128 - 1) / (CS * 128)) * 128;     // K slice of one block, a multiple of 128
-    const int k_lo = rank * slice, k_hi = min(K, k_lo + slice);
-    const bf16* w0[RT];
-    const bf16* w1[RT];
-    bool v0[RT], v1[RT];
-#pragma unroll
-    for (int t = 0; t < RT; ++t) {
-        const int r0 = n0 + t * 16 + g, r1 = r0 + 8;
-        v0[t] = r0 < N; v1[t] = r1 < N;
-        w0[t] = W + (size_t)(v0[t] ? r0 : 0) * K + tq * 8;
-        w1[t] = W + (size_t)(v1[t] ? r1 : 0) * K + tq * 8;
-    }
-    const bf16* xr[MT];
-    bool xv[MT];
-#pragma unroll
-    for (int j = 0; j < MT; ++j) {
-        const int m = j * 8 + g;
-        xv[j] = m < M;
-        xr[j] = x + (size_t)(xv[j] ? m : 0) * ldx + tq * 8;
-    }
-    float acc[RT][MT][4];
-#pragma unroll
-    for (int t = 0; t < RT; ++t)
-#pragma unroll
-        for (int j = 0; j < MT; ++j) { acc[t][j][0] = acc[t][j][1] = acc[t][j][2] = acc[t][j][3] = 0.f; }
-    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-
-    // W does not depend on the kernel before this one: its first piece is requested before the wait.
-    // (Requesting every piece one iteration ahead was measured slower: the extra registers cost residency.)
-    uint4 a[RT][4], b[RT][4];
-    int kb = k_lo + warp * 128;
-    auto load_w = [&]() {
-#pragma unroll
-        for (int t = 0; t < RT; ++t)
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {              // 8 RT loads of W in flight per thread
-                const int k = kb + c * 32;
-                const bool kin = k + tq * 8 < k_hi;
-                a[t][c] = (kin && v0[t]) ? ld_stream16(w0[t] + k) : zero;
-                b[t][c] = (kin && v1[t]) ? ld_stream16(w1[t] + k) : zero;
-            }
-    };
-    load_w();
-    pdl_wait();
-    pdl_trigger();
-    bool first = true;
-    for (; kb < k_hi; kb += NW * 128) {
-        uint4 xq[MT][4];
-        if (!first) load_w();
-        first = false;
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            const int k = kb + c * 32;
-            const bool kin = k + tq * 8 < k_hi;
-#pragma unroll
-            for (int j = 0; j < MT; ++j) xq[j][c] = (kin && xv[j]) ? ld_cached16(xr[j] + k) : zero;
-        }
-#pragma unroll
-        for (int t = 0; t < RT; ++t)
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-#pragma unroll
-                for (int j = 0; j < MT; ++j) {
-                    mma16816(acc[t][j], a[t][c].x, b[t][c].x, a[t][c].y, b[t][c].y, xq[j][c].x, xq[j][c].y);
-                    mma16816(acc[t][j], a[t][c].z, b[t][c].z, a[t][c].w, b[t][c].w, xq[j][c].z, xq[j][c].w);
-                }
-            }
-    }
-    // the warps' partial sums -> shared memory, summed in warp order
-    float* mine = red + (size_t)warp * ROWS * COLS;
-#pragma unroll
-    for (int t = 0; t < RT; ++t)
-#pragma unroll
-        for (int j = 0; j < MT; ++j) {
-            const int col = j * 8 + tq * 2, row = t * 16 + g;
-            mine[row * COLS + col] = acc[t][j][0];
-            mine[row * COLS + col + 1] = acc[t][j][1];
-            mine[(row + 8) * COLS + col] = acc[t][j][2];
-            mine[(row + 8) * COLS + col + 1] = acc[t][j][3];
-        }
-    __syncthreads();
-    float* fin = red + (size_t)NW * ROWS * COLS;        // [ROWS][COLS]
-    for (int idx = threadIdx.x; idx < ROWS * COLS; idx += NW * 32) {
-        float s = 0.f;
-#pragma unroll
-        for (int w = 0; w < NW; ++w) s += red[(size_t)w * ROWS * COLS + idx];
-        fin[idx] = s;
-    }
-    if (CS > 1) {
-        cg::cluster_group cluster = cg::this_cluster();
-        cluster.sync();                                 // every block's sum is in its shared memory
-        if (rank == 0) {
-            for (int idx = threadIdx.x; idx < ROWS * COLS; idx += NW * 32) {
-                float s = fin[idx];
-#pragma unroll
-                for (int r = 1; r < CS; ++r) s += cluster.map_shared_rank(fin, r)[idx];
-                fin[idx] = s;
-            }
-        }
-        cluster.sync();                                 // nobody leaves while its shared memory is being read
-        if (rank != 0) return;
-    }
-    __syncthreads();
-    if (EPI == EPI_NONE) {
-        for (int idx = threadIdx.x; idx < ROWS * COLS; idx += NW * 32) {
-            const int m = idx / ROWS, row = idx - m * ROWS;   // consecutive threads -> consecutive n: coalesced stores
-            if (m < M && n0 + row < N) out[(size_t)m * ldo + n0 + row] = from_f32<OUT>(fin[row * COLS + m]);
-        }
-    } else {
-        for (int idx = threadIdx.x; idx < (ROWS / 2) * COLS; idx += NW * 32) {
-            const int m = idx / (ROWS / 2), o = idx - m * (ROWS / 2);  // output o of this block: tile o / 8, element o % 8
-            const int row = (o >> 3) * 16 + (o & 7);
-            if (m < M && n0 + row + 8 < N) {
-                const float gate = fin[row * COLS + m], up = fin[(row + 8) * COLS + m];
-                out[(size_t)m * ldo + (n0 >> 1) + o] = from_f32<OUT>(gate / (1.f + expf(-gate)) * up);
-            }
-        }
-    }
-}
-
-template <int MT, int NW, int CS, int RT, int EPI, typename OUT>
-static int launch_skinny(const bf16* W, const bf16* x, int ldx, OUT* out, int ldo, int M, int N, int K,
-                         cudaStream_t s) {
-    const size_t smem = (size_t)(NW + 1) * RT * 16 * 8 * MT * sizeof(float);
-    auto kernel = skinny_gemm_kernel<MT, NW, CS, RT, EPI, OUT>;
-    if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-    }
-    const unsigned blocks = (unsigned)(((N + RT * 16 - 1) / (RT * 16)) * CS);
-    return rg_launch(kernel, dim3(blocks), dim3(NW * 32), smem, s, CS, W, x, ldx, out, ldo, M, N, K);
-}
-
-template <int EPI, typename OUT>
-static int dispatch_skinny(const bf16* W, const bf16* x, int ldx, OUT* out, int ldo, int M, int N, int K,
-                           cudaStream_t s) {
-    // Shapes from measurements on B200 at M = 8 (Llama 1B sizes): a block should stream enough of W to pay
-    // for its start and its reduction (two row tiles per warp wherever there are enough rows), every warp should
-    // have one or two 128-wide pieces of K, and all blocks should be resident at once.
-    //   very many rows (head: 128256)            8 warps, 2 row tiles          6.75 TB/s
-    //   many rows (gate|up: 16384)                4 warps, 2 row tiles          5.3 TB/s with SiLU-mul
-    //   few rows, long K (down: 2048 x 8192)      8 warps, 2 row tiles, K over a cluster of 4
-    //   few rows (QKV: 3072 / O: 2048)            16 warps, 2 / 1 row tiles
-    const long long tiles = (N + 15) / 16;
-    const int shape = tiles >= 16 * 148 ? 0 : tiles >= 4 * 148 ? 1 : (K >= 4096 && tiles < 2 * 148) ? 2
-                    : tiles >= 160 ? 3 : 4;
-#define RG_SK(MT_) (shape == 0 ? launch_skinny<MT_, 8, 1, 2, EPI, OUT>(W, x, ldx, out, ldo, M, N, K, s) \
-                  : shape == 1 ? launch_skinny<MT_, 4, 1, 2, EPI, OUT>(W, x, ldx, out, ldo, M, N, K, s) \
-                  : shape == 2 ? launch_skinny<MT_, 8, 4, 2, EPI, OUT>(W, x, ldx, out, ldo, M, N, K, s) \
-                  : shape == 3 ? launch_skinny<MT_, 16, 1, 2, EPI, OUT>(W, x, ldx, out, ldo, M, N, K, s) \
-                               : launch_skinny<MT_, 16, 1, 1, EPI, OUT>(W, x, ldx, out, ldo, M, N, K, s))
-    if (M <= 8) return RG_SK(1);
-    if (M <= 16) return RG_SK(2);
-    if (M <= 32) return RG_SK(4);
-    return RG_SK(8);
-#undef RG_SK
-}
+// The plain entry point of the weight-streaming decode product (gemm_skinny.cuh has the kernel).
+#include "gemm_skinny.cuh"
 
 // out_dtype: RG_DTYPE_BF16 or RG_DTYPE_F32.  epilogue: 0 plain (out [M, N]); 1 SiLU-mul over interleaved gate|up rows
 // (out [M, N / 2]).  Refuses M > 64, K % 8 != 0 and, for the SiLU-mul epilogue, N % 16 != 0.
@@ -220,12 +10,13 @@ extern "C" int rg_skinny_gemm(const void* W, const void* x, int ldx, void* out, 
     cudaStream_t s = (cudaStream_t)stream;
     const bf16* w = (const bf16*)W;
     const bf16* xx = (const bf16*)x;
+    const SkinnyFusion none = {};
     if (epilogue == EPI_SILU_MUL) {
         if (N % 16 || out_dtype != RG_DTYPE_BF16) return RG_ERR_UNSUPPORTED;
-        return dispatch_skinny<EPI_SILU_MUL, bf16>(w, xx, ldx, (bf16*)out, ldo, M, N, K, s);
+        return dispatch_skinny<EPI_SILU_MUL, PRO_PLAIN, bf16>(w, xx, ldx, (bf16*)out, ldo, M, N, K, none, nullptr, s);
     }
     if (epilogue != EPI_NONE) return RG_ERR_UNSUPPORTED;
-    if (out_dtype == RG_DTYPE_BF16) return dispatch_skinny<EPI_NONE, bf16>(w, xx, ldx, (bf16*)out, ldo, M, N, K, s);
-    if (out_dtype == RG_DTYPE_F32) return dispatch_skinny<EPI_NONE, float>(w, xx, ldx, (float*)out, ldo, M, N, K, s);
+    if (out_dtype == RG_DTYPE_BF16) return dispatch_skinny<EPI_NONE, PRO_PLAIN, bf16>(w, xx, ldx, (bf16*)out, ldo, M, N, K, none, nullptr, s);
+    if (out_dtype == RG_DTYPE_F32) return dispatch_skinny<EPI_NONE, PRO_PLAIN, float>(w, xx, ldx, (float*)out, ldo, M, N, K, none, nullptr, s);
     return RG_ERR_UNSUPPORTED;
 }

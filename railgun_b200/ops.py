@@ -194,6 +194,106 @@ def skinny_gemm(x: torch.Tensor, weight: torch.Tensor, out_dtype=None, silu_mul:
     return out
 
 
+SKINNY_FUSED_MAX_ROWS = 16     # what the fused variants (residual epilogue, norm prologue) are compiled for
+
+
+class NormedRows:
+    """RMSNorm of the residual rows, not finished yet: ``scaled`` holds
+    bf16(residual * norm weight) and ``partials`` [>= blocks, ld] the partial
+    sums of squares of the residual rows, one row per block of the product that
+    last added to the residual.  A product that follows multiplies its sums by
+    1 / rms (``linear`` and ``skinny_gemm_scaled`` take this in place of a
+    tensor); ``materialize()`` runs the norm kernel on the residual."""
+
+    __slots__ = ("resid", "scaled", "partials", "blocks", "weight", "eps", "dtype")
+
+    def __init__(self, resid, scaled, partials, blocks: int, weight, eps: float, dtype):
+        self.resid, self.scaled, self.partials, self.blocks = resid, scaled, partials, blocks
+        self.weight, self.eps, self.dtype = weight, eps, dtype
+
+    @property
+    def shape(self):
+        return self.resid.shape
+
+    def materialize(self) -> torch.Tensor:
+        return add_rmsnorm(self.resid, None, self.weight, self.eps, self.dtype)
+
+
+class PendingLinear:
+    """A part's output x W^T, not computed yet: a norm that follows adds it to
+    the residual inside the product's own kernel; ``materialize()`` runs the
+    product."""
+
+    __slots__ = ("x", "weight")
+
+    def __init__(self, x, weight):
+        self.x, self.weight = x, weight
+
+    @property
+    def shape(self):
+        return (self.x.shape[0], self.weight.shape[0])
+
+    def materialize(self) -> torch.Tensor:
+        return linear(self.x, self.weight)
+
+
+def skinny_fused_ok(x: torch.Tensor, weight: torch.Tensor, resid: torch.Tensor) -> bool:
+    """Can x W^T be added to ``resid`` inside the decode product (which then
+    also prepares the next norm)?  Only where ``linear`` would use that product."""
+    return (x.shape[0] <= min(SKINNY_AUTO_ROWS, SKINNY_FUSED_MAX_ROWS) and skinny_gemm_ok(x, weight)
+            and resid.dtype == torch.float32 and resid.is_contiguous() and resid.shape == (x.shape[0], weight.shape[0])
+            and resid.shape[1] % 8 == 0)
+
+
+def skinny_gemm_residual(x: torch.Tensor, weight: torch.Tensor, resid: torch.Tensor, norm_weight: torch.Tensor,
+                         eps: float) -> NormedRows:
+    """resid += x W^T (32-bit, in place), and the RMSNorm (``norm_weight``,
+    ``eps``) of the new rows but for the factor 1 / rms, which the product that
+    reads the result applies."""
+    if not (x.shape[0] <= SKINNY_FUSED_MAX_ROWS and skinny_gemm_ok(x, weight)):
+        raise KernelError(f"skinny_gemm_residual refuses x {tuple(x.shape)} {x.dtype}, W {tuple(weight.shape)}")
+    _check(resid, "resid", torch.float32)
+    _check(norm_weight, "norm_weight", torch.float32)
+    M, K = x.shape
+    N = weight.shape[0]
+    if weight.shape[1] != K or resid.shape != (M, N) or norm_weight.numel() != N:
+        raise KernelError(f"skinny_gemm_residual: x {tuple(x.shape)}, W {tuple(weight.shape)}, residual "
+                          f"{tuple(resid.shape)}, norm weight {norm_weight.numel()}")
+    ld = 8 * ((M + 7) // 8)
+    partials = torch.empty(((N + 15) // 16, ld), dtype=torch.float32, device=x.device)
+    scaled = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    blocks = c_int(0)
+    _ok(_fn("gemm_skinny_fused", "rg_skinny_gemm_residual")(
+        _ptr(weight), _ptr(x), c_int(x.stride(0)), _ptr(resid), c_int(resid.stride(0)), _ptr(norm_weight), _ptr(scaled),
+        c_int(M), c_int(N), c_int(K), _ptr(partials), c_int(ld), ctypes.byref(blocks), _stream()),
+        "skinny_gemm_residual")
+    return NormedRows(resid, scaled, partials, blocks.value, norm_weight, eps, torch.bfloat16)
+
+
+def skinny_scaled_ok(rows: NormedRows, weight: torch.Tensor) -> bool:
+    return (rows.dtype == torch.bfloat16 and rows.shape[0] <= min(SKINNY_AUTO_ROWS, SKINNY_FUSED_MAX_ROWS)
+            and skinny_gemm_ok(rows.scaled, weight) and rows.shape[1] == weight.shape[1])
+
+
+def skinny_gemm_scaled(rows: NormedRows, weight: torch.Tensor, silu_mul: bool = False) -> torch.Tensor:
+    """y = rmsnorm(residual rows) W^T from the unfinished norm ``rows``: the
+    product over the scaled rows, its 32-bit sums multiplied by 1 / rms before
+    the epilogue; ``silu_mul`` as in ``skinny_gemm``.  bfloat16 out."""
+    if not skinny_scaled_ok(rows, weight):
+        raise KernelError(f"skinny_gemm_scaled refuses rows {tuple(rows.shape)}, W {tuple(weight.shape)} {weight.dtype}")
+    x = rows.scaled
+    M, K = x.shape
+    N = weight.shape[0]
+    if silu_mul and N % 16:
+        raise KernelError("skinny_gemm_scaled: the SiLU-mul epilogue needs N % 16 == 0")
+    out = torch.empty((M, N // 2 if silu_mul else N), dtype=torch.bfloat16, device=x.device)
+    _ok(_fn("gemm_skinny_fused", "rg_skinny_gemm_scaled")(
+        _ptr(weight), _ptr(x), c_int(x.stride(0)), c_float(rows.eps), _ptr(rows.partials),
+        c_int(rows.partials.stride(0)), c_int(rows.blocks), _ptr(out), c_int(out.shape[1]),
+        c_int(1 if silu_mul else 0), c_int(M), c_int(N), c_int(K), _stream()), "skinny_gemm_scaled")
+    return out
+
+
 def rope_cache_write(qkv: torch.Tensor, table, positions: torch.Tensor, slots, kv_cache,
                      nh: int, nkv: int, d: int, page_size: int, err_flag=None) -> None:
     """Rotate the q and k heads of qkv [T, (nh+2nkv)d] in place by ``table``
@@ -493,6 +593,10 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype=None) -> torch.Tenso
     are library GEMMs (crates/vllm-models/src/llama/attention.rs:94-96,133).
     32-bit inputs run in true 32-bit: the reduced-precision matrix mode is
     refused."""
+    if isinstance(x, NormedRows):
+        if (out_dtype is None or out_dtype == torch.bfloat16) and skinny_scaled_ok(x, weight):
+            return skinny_gemm_scaled(x, weight)              # the norm is finished inside the product
+        x = x.materialize()
     if not x.is_cuda:
         raise KernelError("linear: CUDA tensors only (there is no CPU path)")
     if x.dtype == torch.float32 and torch.backends.cuda.matmul.allow_tf32:

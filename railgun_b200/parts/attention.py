@@ -65,7 +65,10 @@ class PagedAttention(Mixer):
             self.position = tensors.shared_part(("position", pos), lambda: POSITION_ENCODINGS.get(pos.kind)(
                 pos.params, prefix, env, tensors))
 
-    def forward(self, x, batch, cache, writes=True):
+    takes_normed_rows = True
+    defers_output = True
+
+    def forward(self, x, batch, cache, writes=True, defer=False):
         nh, nkv, d = self.nh, self.nkv, self.d
         qkv = ops.linear(x, self.w_qkv)
         slots = batch.slot_mapping[cache.group]
@@ -77,7 +80,7 @@ class PagedAttention(Mixer):
             ops.rope_cache_write(qkv, None, batch.positions, slots, cache.kv, nh, nkv, d, cache.page_size,
                                  batch.err_flag)
         out = self.attend(qkv, batch, cache)
-        return ops.linear(out, self.w_o)
+        return ops.PendingLinear(out, self.w_o) if defer else ops.linear(out, self.w_o)
 
     def attend(self, qkv, batch, cache):
         """Pick the attention kernels for this step's shape and precision:

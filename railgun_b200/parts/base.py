@@ -11,6 +11,8 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 
+from .. import ops
+
 
 class Part:
     @classmethod
@@ -27,7 +29,14 @@ class Norm(Part):
     """``add_norm(resid, pending, rows=None)``: add ``pending`` (or nothing) to
     the 32-bit residual stream in place and return the normed rows in the
     activation dtype.  With ``rows`` only those rows are returned and the
-    residual is left as it was."""
+    residual is left as it was.
+
+    A norm that sets ``fuses_pending_linear`` also takes ``pending`` as an
+    ``ops.PendingLinear`` (a product not computed yet) and may return
+    ``ops.NormedRows`` (a norm not computed yet); ``normed_input`` below keeps
+    both away from parts that did not ask for them."""
+
+    fuses_pending_linear = False
 
     def add_norm(self, resid, pending, rows=None):
         raise NotImplementedError
@@ -44,6 +53,19 @@ class PositionEncoding(Part):
         raise NotImplementedError
 
 
+def normed_input(norm, part, stream, rows=None):
+    """The rows that ``part`` reads: ``norm`` of the stream with what is pending
+    added.  Values that are not computed yet pass only between a norm and a
+    part that both declare that they take them."""
+    pending = stream.pending
+    if isinstance(pending, ops.PendingLinear) and not getattr(norm, "fuses_pending_linear", False):
+        pending = pending.materialize()
+    h = norm.add_norm(stream.resid, pending) if rows is None else norm.add_norm(stream.resid, pending, rows=rows)
+    if isinstance(h, ops.NormedRows) and not getattr(part, "takes_normed_rows", False):
+        h = h.materialize()
+    return h
+
+
 class Mixer(Part):
     """Mixes information between positions of a request.
 
@@ -51,7 +73,16 @@ class Mixer(Part):
     ``PagedKVNeed``, a ``StateNeed`` or None.  ``forward(x, batch, cache,
     writes)`` takes the normed rows [T, H] of the step's tokens and returns
     [T, H]; ``cache`` is a ``CacheView`` of what the need asked for; ``writes``
-    False means the layer reads a cache that another layer fills."""
+    False means the layer reads a cache that another layer fills.
+
+    Optional, for mixers and feed-forwards alike: ``takes_normed_rows`` = True
+    says that ``x`` may be an ``ops.NormedRows`` (which ``ops.linear`` takes in
+    place of a tensor); ``defers_output`` = True says that ``forward`` has a
+    keyword ``defer`` and, when it is True, may return its last product as an
+    ``ops.PendingLinear``."""
+
+    takes_normed_rows = False
+    defers_output = False
 
     @classmethod
     def cache_need(cls, params: dict):
@@ -63,6 +94,9 @@ class Mixer(Part):
 
 class FeedForward(Part):
     """``forward(x, batch)``: [T, H] -> [T, H], each row on its own."""
+
+    takes_normed_rows = False
+    defers_output = False
 
     def forward(self, x, batch):
         raise NotImplementedError

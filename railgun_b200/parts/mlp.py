@@ -36,14 +36,22 @@ class SwiGLU(FeedForward):
         tensors.drop(m + "gate_proj.weight", m + "up_proj.weight")
         self.w_down = tensors.get(m + "down_proj.weight", env.dtype)
 
-    def forward(self, x, batch):
+    takes_normed_rows = True
+    defers_output = True
+
+    def forward(self, x, batch, defer=False):
+        if isinstance(x, ops.NormedRows):
+            if self.interleaved and ops.skinny_scaled_ok(x, self.w_gate_up):
+                act = ops.skinny_gemm_scaled(x, self.w_gate_up, silu_mul=True)   # decode: norm, product and SiLU-mul in one
+                return ops.PendingLinear(act, self.w_down) if defer else ops.linear(act, self.w_down)
+            x = x.materialize()
         if self.interleaved and x.shape[0] <= ops.SKINNY_AUTO_ROWS and ops.skinny_gemm_ok(x, self.w_gate_up):
             act = ops.skinny_gemm(x, self.w_gate_up, silu_mul=True)              # decode: weights streamed once
         elif self.interleaved and x.shape[0] >= ops.TC_GEMM_MIN_ROWS and ops.tc_gemm_ok(x, self.w_gate_up):
             act = ops.tc_gemm(x, self.w_gate_up, silu_mul=True)                  # prefill: tcgen05, SiLU-mul in the epilogue
         else:
             act = ops.silu_mul(ops.linear(x, self.w_gate_up), interleaved=self.interleaved)
-        return ops.linear(act, self.w_down)
+        return ops.PendingLinear(act, self.w_down) if defer else ops.linear(act, self.w_down)
 
 
 register_feed_forward("swiglu", SwiGLU)

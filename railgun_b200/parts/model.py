@@ -11,7 +11,7 @@ from dataclasses import dataclass
 
 import torch
 
-from .base import CacheView, Stream
+from .base import CacheView, Stream, normed_input
 from .registry import ARRANGEMENTS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS
 from .spec import BuildEnv, ModelSpec
 # importing the modules registers the built-in parts
@@ -130,5 +130,5 @@ class DecoderModel:
             layer.arrangement.run(layer, stream, batch, cache.view(e.cache), e.writes)
         if batch.num_wanted == 0:
             return None
-        h = self.final_norm.add_norm(stream.resid, stream.pending, rows=batch.want_rows)
+        h = normed_input(self.final_norm, None, stream, rows=batch.want_rows)
         return self.head.logits(h)

@@ -27,7 +27,15 @@ class RMSNorm(Norm):
         self.eps = float(params["eps"])
         self.weight = tensors.get(prefix + params["name"], torch.float32)
 
+    fuses_pending_linear = True
+
     def add_norm(self, resid, pending, rows=None):
+        if isinstance(pending, ops.PendingLinear):
+            # small decode batches: the product adds its result to the residual itself and prepares this
+            # norm; the product that reads the result finishes it
+            if rows is None and self.env.dtype == torch.bfloat16 and ops.skinny_fused_ok(pending.x, pending.weight, resid):
+                return ops.skinny_gemm_residual(pending.x, pending.weight, resid, self.weight, self.eps)
+            pending = pending.materialize()
         return ops.add_rmsnorm(resid, pending, self.weight, self.eps, self.env.dtype, rows)
 
 

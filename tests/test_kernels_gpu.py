@@ -465,6 +465,72 @@ def test_skinny_gemm_refusals():
     assert y.shape == (2, 32) and float(y[0, 0]) == 20.0
 
 
+# ---- the decode product with the residual addition and the norm folded in --------------------------------
+
+@pytest.mark.parametrize("M", [1, 3, 8, 13, 16])
+@pytest.mark.parametrize("H,K", [(48, 64), (200, 136), (1000, 72), (2048, 2048), (2048, 8192), (3080, 520)])
+def test_skinny_gemm_residual_then_scaled(M, H, K):
+    """resid += x W^T in the product's kernel, then the next product finishes the RMSNorm of the new rows:
+    against 64-bit references and against the stand-alone kernels."""
+    from railgun_b200 import ops
+    g = torch.Generator().manual_seed(M * 7 + H + K)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(H, K, generator=g) / K ** 0.5).to(torch.bfloat16).to(DEV)
+    resid0 = (torch.randn(M, H, generator=g) * 3).to(DEV)
+    nw = (torch.rand(H, generator=g) + 0.5).to(DEV)
+    eps = 1e-3
+    resid = resid0.clone()
+    rows = ops.skinny_gemm_residual(x, w, resid, nw, eps)
+    ref_resid = resid0.double() + x.double() @ w.double().T
+    assert rel_err(resid, ref_resid) < 2e-6                                    # 32-bit sums added to a 32-bit residual
+    # the stand-alone route: bf16 product added inside the norm kernel (one more rounding)
+    resid_b = resid0.clone()
+    ops.add_rmsnorm(resid_b, ops.skinny_gemm(x, w), nw, eps, torch.bfloat16)
+    assert rel_err(resid_b, ref_resid) < 5e-3
+    assert torch.equal(rows.scaled, (resid * nw).to(torch.bfloat16))           # one rounding, of the 32-bit product
+    ss = rows.partials[:rows.blocks, :M].double().sum(0)
+    assert rel_err(ss, (resid.double() ** 2).sum(1)) < 1e-6
+    assert float(rows.partials[:rows.blocks, M:].abs().max()) == 0.0 if rows.partials.shape[1] > M else True
+    # a row's result does not depend on the batch around it
+    alone = resid0[M - 1:].clone()
+    ops.skinny_gemm_residual(x[M - 1:].contiguous(), w, alone, nw, eps)
+    assert torch.equal(alone[0], resid[M - 1])
+    # the consumer
+    normed = ref_resid * torch.rsqrt((ref_resid ** 2).mean(1, keepdim=True) + eps) * nw.double()
+    for N2, silu in ((136, False), (1008, True), (3072, False)):
+        w2 = (torch.randn(N2, H, generator=g) / H ** 0.5).to(torch.bfloat16).to(DEV)
+        assert ops.skinny_scaled_ok(rows, w2) == (M <= ops.SKINNY_AUTO_ROWS)
+        if M > ops.SKINNY_AUTO_ROWS:
+            y = ops.linear(rows, w2)                                           # falls back to norm kernel + product
+            assert rel_err(y, normed @ w2.double().T) < 1e-2
+            continue
+        y = ops.skinny_gemm_scaled(rows, w2, silu_mul=silu)
+        z = normed @ w2.double().T
+        if silu:
+            z = z.view(M, N2 // 16, 2, 8)
+            z = (z[:, :, 0] / (1 + torch.exp(-z[:, :, 0])) * z[:, :, 1]).reshape(M, N2 // 2)
+        assert y.dtype == torch.bfloat16 and rel_err(y, z) < 1e-2
+        if not silu:
+            assert torch.equal(ops.linear(rows, w2), y)                        # linear() takes the unfinished norm
+    assert rel_err(rows.materialize(), normed) < 1e-2
+
+
+def test_skinny_fused_refusals():
+    from railgun_b200 import ops
+    x = torch.zeros(4, 64, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(48, 64, dtype=torch.bfloat16, device=DEV)
+    nw = torch.ones(48, device=DEV)
+    assert ops.skinny_fused_ok(x, w, torch.zeros(4, 48, device=DEV))
+    assert not ops.skinny_fused_ok(x, w, torch.zeros(4, 48, dtype=torch.bfloat16, device=DEV))            # residual is 32-bit
+    assert not ops.skinny_fused_ok(torch.zeros(9, 64, dtype=torch.bfloat16, device=DEV), w,
+                                   torch.zeros(9, 48, device=DEV))                                       # beyond the decode sizes
+    with pytest.raises(ops.KernelError):
+        ops.skinny_gemm_residual(torch.zeros(17, 64, dtype=torch.bfloat16, device=DEV), w, torch.zeros(17, 48, device=DEV),
+                                 nw, 1e-5)
+    with pytest.raises(ops.KernelError):
+        ops.skinny_gemm_residual(x, w, torch.zeros(4, 40, device=DEV), nw, 1e-5)                         # wrong residual width
+
+
 # ---- the tcgen05 / TMA matrix product -------------------------------------------------------------------
 
 @pytest.mark.parametrize("wide", [False, True])

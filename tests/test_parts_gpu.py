@@ -69,6 +69,76 @@ def test_feed_forward_part(dtype):
     assert rel(part.forward(x, None), ref) < TOL[dtype]
 
 
+@pytest.mark.parametrize("rows", [1, 5, 8, 12])
+def test_prenorm_block_hands_unfinished_values_only_to_parts_that_take_them(rows):
+    """At small decode batches the built-in parts pass products and norms on unfinished (the residual addition
+    and the norm then run inside the products' kernels).  Parts that did not ask for that see tensors only, and
+    both routes give the block's result."""
+    from railgun_b200 import ops
+    from railgun_b200.parts.base import Mixer, Norm, Stream
+    from railgun_b200.parts.block import PreNorm
+    from railgun_b200.parts.model import Layer
+    from railgun_b200.parts.registry import FEED_FORWARDS, NORMS
+    dtype, H, I, eps = torch.bfloat16, 72, 200, 1e-5
+    rng = np.random.default_rng(rows)
+    w = {}
+    for l in ("a.", "b."):
+        w.update({l + "n1": 1 + 0.1 * rng.normal(size=H), l + "n2": 1 + 0.1 * rng.normal(size=H),
+                  l + "mix1": rng.normal(size=(H, H)) * 0.2, l + "mix2": rng.normal(size=(H, H)) * 0.2,
+                  l + "mlp.gate_proj.weight": rng.normal(size=(I, H)) * 0.2,
+                  l + "mlp.up_proj.weight": rng.normal(size=(I, H)) * 0.2,
+                  l + "mlp.down_proj.weight": rng.normal(size=(H, I)) * 0.2})
+    r = rounded(w, dtype)
+    x0 = rng.normal(size=(rows, H))
+    ref = x0.copy()
+    for l in ("a.", "b."):
+        ref = ref + P.linear(P.linear(P.rms_norm(ref, r[l + "n1"], eps), r[l + "mix1"]), r[l + "mix2"])
+        ref = ref + P.swiglu(P.rms_norm(ref, r[l + "n2"], eps), r[l + "mlp.gate_proj.weight"],
+                             r[l + "mlp.up_proj.weight"], r[l + "mlp.down_proj.weight"])
+    seen = []
+
+    class TwoLinears(Mixer):
+        def __init__(self, prefix, tensors, lazy):
+            self.w1, self.w2 = tensors.get(prefix + "mix1", dtype), tensors.get(prefix + "mix2", dtype)
+            self.takes_normed_rows = self.defers_output = lazy
+
+        def forward(self, x, batch, cache, writes=True, defer=False):
+            seen.append(("mixer", type(x).__name__))
+            y = ops.linear(x, self.w1)
+            return ops.PendingLinear(y, self.w2) if defer else ops.linear(y, self.w2)
+
+    class PlainNorm(Norm):
+        def __init__(self, weight):
+            self.weight = weight
+
+        def add_norm(self, resid, pending, rows=None):
+            seen.append(("norm", type(pending).__name__))
+            return ops.add_rmsnorm(resid, pending, self.weight, eps, dtype, rows)
+
+    def run(lazy):
+        seen.clear()
+        env, tensors = env_of(dtype, H), bank_of(w, dtype)
+        layers = []
+        for l in ("a.", "b."):
+            norm = lambda name: (NORMS.get("rmsnorm")(dict(size=H, eps=eps, name=name), l, env, tensors) if lazy
+                                 else PlainNorm(tensors.get(l + name, torch.float32)))
+            layers.append(Layer(mixer_norm=norm("n1"), mixer=TwoLinears(l, tensors, lazy), ffn_norm=norm("n2"),
+                                ffn=FEED_FORWARDS.get("swiglu")(dict(hidden_size=H, intermediate_size=I), l, env, tensors),
+                                arrangement=PreNorm()))
+        stream = Stream(torch.tensor(x0, dtype=torch.float32, device=DEV))
+        for layer in layers:
+            layer.arrangement.run(layer, stream, None, None, True)
+        pending = stream.pending.materialize() if isinstance(stream.pending, ops.PendingLinear) else stream.pending
+        return stream.resid.double().cpu().numpy() + pending.double().cpu().numpy(), list(seen)
+
+    out_lazy, seen_lazy = run(True)
+    out_plain, seen_plain = run(False)
+    assert rel(out_lazy, ref) < TOL[dtype] and rel(out_plain, ref) < TOL[dtype]
+    assert all(kind == "Tensor" or kind == "NoneType" for _, kind in seen_plain)
+    small = rows <= ops.SKINNY_AUTO_ROWS
+    assert seen_lazy == [("mixer", "Tensor"), ("mixer", "NormedRows" if small else "Tensor")]
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_embedding_and_head_parts_share_a_tied_tensor(dtype):
     from railgun_b200.parts.registry import EMBEDDINGS, HEADS
