@@ -259,7 +259,7 @@ skinny_gemm_kernel(const bf16* __restrict__ W, const bf16* __restrict__ x, int l
 
 template <int MT, int NW, int CS, int RT, int EPI, int PRO, typename OUT>
 static int launch_skinny(const bf16* W, const bf16* x, int ldx, OUT* out, int ldo, int M, int N, int K,
-                         SkinnyFusion fu, int* row_blocks, cudaStream_t s, bool early_start = true) {
+                         SkinnyFusion fu, int* row_blocks, cudaStream_t s) {
     const size_t smem = (size_t)(NW + 1) * RT * 16 * 8 * MT * sizeof(float);
     auto kernel = skinny_gemm_kernel<MT, NW, CS, RT, EPI, PRO, OUT>;
     if (smem > 48 * 1024) {
@@ -268,7 +268,6 @@ static int launch_skinny(const bf16* W, const bf16* x, int ldx, OUT* out, int ld
     }
     const unsigned blocks = (unsigned)(((N + RT * 16 - 1) / (RT * 16)) * CS);
     if (row_blocks) *row_blocks = (int)(blocks / CS);
-    RgStreamOrder in_order(!early_start);
     return rg_launch(kernel, dim3(blocks), dim3(NW * 32), smem, s, CS, W, x, ldx, out, ldo, M, N, K, fu);
 }
 
@@ -283,9 +282,6 @@ static int dispatch_skinny(const bf16* W, const bf16* x, int ldx, OUT* out, int 
     //   many rows (gate|up: 16384)                4 warps, 2 row tiles          5.3 TB/s with SiLU-mul
     //   few rows, long K (down: 2048 x 8192)      8 warps, 2 row tiles, K over a cluster of 4
     //   few rows (QKV: 3072 / O: 2048)            16 warps, 2 / 1 row tiles
-    // The last shape starts in stream order, not early: in a decoder layer it follows the short kernel that
-    // merges the attention splits, and its 128 blocks of 512 threads arriving during that kernel cost a
-    // batch-8 step 4 % (measured with and without).
     const long long tiles = (N + 15) / 16;
     const int shape = tiles >= 16 * 148 ? 0 : tiles >= 4 * 148 ? 1 : (K >= 4096 && tiles < 2 * 148) ? 2
                     : tiles >= 160 ? 3 : 4;
@@ -293,7 +289,7 @@ static int dispatch_skinny(const bf16* W, const bf16* x, int ldx, OUT* out, int 
                   : shape == 1 ? launch_skinny<MT_, 4, 1, 2, EPI, PRO, OUT>(W, x, ldx, out, ldo, M, N, K, fu, row_blocks, s) \
                   : shape == 2 ? launch_skinny<MT_, 8, 4, 2, EPI, PRO, OUT>(W, x, ldx, out, ldo, M, N, K, fu, row_blocks, s) \
                   : shape == 3 ? launch_skinny<MT_, 16, 1, 2, EPI, PRO, OUT>(W, x, ldx, out, ldo, M, N, K, fu, row_blocks, s) \
-                               : launch_skinny<MT_, 16, 1, 1, EPI, PRO, OUT>(W, x, ldx, out, ldo, M, N, K, fu, row_blocks, s, false))
+                               : launch_skinny<MT_, 16, 1, 1, EPI, PRO, OUT>(W, x, ldx, out, ldo, M, N, K, fu, row_blocks, s))
     if (M <= 8) return RG_SK(1);
     if (M <= 16) return RG_SK(2);
     if constexpr (MAX_MT >= 4) {
