@@ -90,6 +90,58 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&v)[32]) {
     tc_ld_wait();
 }
 
+// ---- CTA pairs (cta_group::2): two CTAs of a cluster work on one tile of 256 rows.  Each holds its own 128
+// rows of A and its own half of B's rows in shared memory; one thread of the pair's first CTA issues the MMAs
+// for both, and the accumulator rows of each CTA land in its own tensor memory.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// The address, in the cluster's shared window, that `addr` (a shared address of this CTA) has in CTA `rank`.
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+// All threads of all CTAs of the cluster.
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// A box into this CTA's shared memory; the bytes are counted on a barrier that may sit in the pair's other CTA
+// (its address in the cluster's window).  No multicast: each CTA fetches what it holds.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar_cluster, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+                 "[%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar_cluster), "r"(x), "r"(y) : "memory");
+}
+// Arrive, once the pair's MMAs issued so far have completed, on the barrier at this shared address in every CTA
+// of `cta_mask`.
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar, uint16_t cta_mask) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"(cta_mask) : "memory");
+}
+// Issued by the same warp of both CTAs of the pair, with the same slot address.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* slot, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_addr(slot)), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_free_pair(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+// D[256 x N] (+)= A[256 x 16] B[N x 16]^T over the pair: rows 0-127 and B rows 0..N/2-1 from the first CTA's
+// shared memory, the rest from the second's, at the same shared addresses.
+__device__ __forceinline__ void tc_mma_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "setp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+
 // Operand descriptors for tiles whose rows are 128 bytes (64 bfloat16) with the 128-byte swizzle (what TMA
 // writes), groups of 8 rows 1024 bytes apart: start address >> 4 in bits [0,14), leading byte offset >> 4 in
 // [16,30), stride byte offset >> 4 in [32,46), version 1 in [46,48), SWIZZLE_128B = 2 in [61,64).

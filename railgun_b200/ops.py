@@ -443,13 +443,22 @@ def tc_gemm_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
             and weight.is_contiguous() and weight.data_ptr() % 16 == 0)
 
 
+TC_TILES = {"128x128": 0, "128x256": 1, "256x256": 2, "256x128": 3}
+
+
 def tc_gemm(x: torch.Tensor, weight: torch.Tensor, out_dtype=None, silu_mul: bool = False, wide: bool = True,
-            check: bool = False) -> torch.Tensor:
+            check: bool = False, tile: str | None = None) -> torch.Tensor:
     """y = x W^T on the tcgen05 tensor cores (TMA-fed, accumulators in tensor
     memory).  ``silu_mul``: W is interleaved gate|up storage and y = silu(gate)
-    * up.  ``wide``: 128 x 256 tiles instead of 128 x 128.  The kernel's waits
-    are bounded; ``tc_gemm_check()`` (or ``check=True``, which synchronises)
-    raises if one gave up."""
+    * up.  ``tile`` (rows of x by rows of W): "128x128" or "128x256", one CTA
+    per tile, or "256x256" / "256x128", a pair of CTAs on two SMs per tile
+    (cta_group::2); without it ``wide`` picks between the first two.  The
+    kernel's waits are bounded; ``tc_gemm_check()`` (or ``check=True``, which
+    synchronises) raises if one gave up."""
+    if tile is None:
+        tile = "128x256" if wide else "128x128"
+    if tile not in TC_TILES:
+        raise KernelError(f"tc_gemm: tile {tile!r} is not one of {sorted(TC_TILES)}")
     if not tc_gemm_ok(x, weight):
         raise KernelError(f"tc_gemm refuses x {tuple(x.shape)} {x.dtype} stride {x.stride()}, "
                           f"W {tuple(weight.shape)} {weight.dtype}: bfloat16, K a multiple of 8, 16-byte aligned")
@@ -468,7 +477,7 @@ def tc_gemm(x: torch.Tensor, weight: torch.Tensor, out_dtype=None, silu_mul: boo
     out = torch.empty((M, N // 2 if silu_mul else N), dtype=out_dtype, device=x.device)
     _ok(_fn("gemm_tcgen05", "rg_tc_gemm")(
         _ptr(x), c_int(x.stride(0)), _ptr(weight), _ptr(out), c_int(out.shape[1]), c_int(_dtype_code(out)),
-        c_int(1 if silu_mul else 0), c_int(M), c_int(N), c_int(K), c_int(1 if wide else 0), _ptr(err), _stream()),
+        c_int(1 if silu_mul else 0), c_int(M), c_int(N), c_int(K), c_int(TC_TILES[tile]), _ptr(err), _stream()),
         "tc_gemm")
     if check:
         tc_gemm_check(x.device)

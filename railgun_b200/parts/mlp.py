@@ -48,7 +48,8 @@ class SwiGLU(FeedForward):
         if self.interleaved and x.shape[0] <= ops.SKINNY_AUTO_ROWS and ops.skinny_gemm_ok(x, self.w_gate_up):
             act = ops.skinny_gemm(x, self.w_gate_up, silu_mul=True)              # decode: weights streamed once
         elif self.interleaved and x.shape[0] >= ops.TC_GEMM_MIN_ROWS and ops.tc_gemm_ok(x, self.w_gate_up):
-            act = ops.tc_gemm(x, self.w_gate_up, silu_mul=True)                  # prefill: tcgen05, SiLU-mul in the epilogue
+            # prefill: tcgen05 on CTA pairs, SiLU-mul in the epilogue
+            act = ops.tc_gemm(x, self.w_gate_up, silu_mul=True, tile="256x256")
         else:
             act = ops.silu_mul(ops.linear(x, self.w_gate_up), interleaved=self.interleaved)
         return ops.PendingLinear(act, self.w_down) if defer else ops.linear(act, self.w_down)

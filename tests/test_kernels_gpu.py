@@ -533,27 +533,28 @@ def test_skinny_fused_refusals():
 
 # ---- the tcgen05 / TMA matrix product -------------------------------------------------------------------
 
-@pytest.mark.parametrize("wide", [False, True])
+@pytest.mark.parametrize("tile", ["128x128", "128x256", "256x128", "256x256"])
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (200, 300, 200), (1, 48, 64), (333, 1000, 176), (1024, 3072, 2048),
-                                   (129, 257 * 8, 8 * 37)])
-def test_tc_gemm(M, N, K, wide):
+                                   (129, 257 * 8, 8 * 37), (700, 520, 4104)])
+def test_tc_gemm(M, N, K, tile):
     from railgun_b200 import ops
     g = torch.Generator().manual_seed(M + N + K)
     x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
     w = (torch.randn(N, K, generator=g) / K ** 0.5).to(torch.bfloat16).to(DEV)
     ref = x.double() @ w.double().T
-    out = ops.tc_gemm(x, w, wide=wide, check=True)
+    out = ops.tc_gemm(x, w, tile=tile, check=True)
     assert out.dtype == torch.bfloat16 and rel_err(out, ref) < 1e-2
-    out32 = ops.tc_gemm(x, w, out_dtype=torch.float32, wide=wide, check=True)
+    out32 = ops.tc_gemm(x, w, out_dtype=torch.float32, tile=tile, check=True)
     assert rel_err(out32, ref) < 2e-5                        # exact products, 32-bit accumulation
     # x as a view with a longer row pitch
     pitch = torch.zeros(M, K + 24, dtype=torch.bfloat16, device=DEV)
     pitch[:, :K] = x
-    assert torch.equal(ops.tc_gemm(pitch[:, :K], w, out_dtype=torch.float32, wide=wide, check=True), out32)
+    assert torch.equal(ops.tc_gemm(pitch[:, :K], w, out_dtype=torch.float32, tile=tile, check=True), out32)
 
 
+@pytest.mark.parametrize("tile", ["128x256", "256x128", "256x256"])
 @pytest.mark.parametrize("M,I,K", [(100, 504, 136), (1100, 8192, 2048)])
-def test_tc_gemm_silu_mul(M, I, K):
+def test_tc_gemm_silu_mul(M, I, K, tile):
     from railgun_b200 import ops
     g = torch.Generator().manual_seed(M + I + K)
     x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
@@ -561,7 +562,7 @@ def test_tc_gemm_silu_mul(M, I, K):
     up = (torch.randn(I, K, generator=g) / K ** 0.5 * 2).to(torch.bfloat16).to(DEV)
     a, b = x.double() @ gate.double().T, x.double() @ up.double().T
     ref = a / (1 + torch.exp(-a)) * b
-    out = ops.tc_gemm(x, ops.interleave_gate_up(gate, up), silu_mul=True, check=True)
+    out = ops.tc_gemm(x, ops.interleave_gate_up(gate, up), silu_mul=True, tile=tile, check=True)
     assert out.shape == (M, I) and rel_err(out, ref) < 1e-2
 
 
@@ -572,6 +573,9 @@ def test_tc_gemm_refusals():
     assert not ops.tc_gemm_ok(torch.zeros(2, 24, device=DEV), torch.zeros(32, 24, device=DEV))  # 32-bit
     with pytest.raises(ops.KernelError):
         ops.tc_gemm(torch.zeros(2, 20, dtype=torch.bfloat16, device=DEV), w)
+    with pytest.raises(ops.KernelError):
+        ops.tc_gemm(torch.zeros(2, 24, dtype=torch.bfloat16, device=DEV),
+                    torch.zeros(32, 24, dtype=torch.bfloat16, device=DEV), tile="512x512")
 
 
 # ---- the tcgen05 flash attention kernel (head size 64) ----------------------------------------------------
