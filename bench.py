@@ -273,6 +273,108 @@ def run_ours(args):
     return 0
 
 
+def run_kernels(args):
+    """Times the hot kernels one by one, each as a CUDA graph of 16 calls over 16 different operand sets (so
+    that weights and caches come from HBM, not L2), with CUDA events around replays.  One JSON line per case."""
+    import torch
+    from railgun_b200 import ops
+    dev, L = "cuda:0", 16
+    cfg = LLAMA_3_2_1B
+    H, I, nh, nkv, d = cfg["hidden_size"], cfg["intermediate_size"], cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    QKV, page = (nh + 2 * nkv) * d, 16
+
+    def timed(fn, reps=20):
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            fn()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn()
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(reps):
+            g.replay()
+        t1.record()
+        torch.cuda.synchronize()
+        ops.tc_gemm_check()
+        return t0.elapsed_time(t1) / reps * 1e3 / L          # microseconds per call
+
+    def weights(n, k):
+        return [(torch.randn(n, k, device=dev) / k ** 0.5).to(torch.bfloat16) for _ in range(L)]
+
+    def out(case, us, **more):
+        print(json.dumps(dict(case=case, us=round(us, 2), **more)), flush=True)
+
+    want = set(args.cases.split(",")) if args.cases else None
+    on = lambda name: want is None or name in want
+
+    if on("decode_gemm"):
+        for M in (1, 8):
+            x = torch.randn(M, H, device=dev).to(torch.bfloat16)
+            xi = torch.randn(M, I, device=dev).to(torch.bfloat16)
+            resid, nw = torch.randn(M, H, device=dev), torch.ones(H, device=dev)
+            for name, n, k, silu in (("qkv", QKV, H, False), ("o", H, H, False), ("gate_up", 2 * I, H, True), ("down", H, I, False)):
+                ws = weights(n, k)
+                inp = xi if k == I else x
+                us = timed(lambda: [ops.skinny_gemm(inp, w, silu_mul=silu) for w in ws])
+                us_lib = timed(lambda: [torch.mm(inp, w.t()) for w in ws])
+                more = {}
+                if name in ("o", "down"):
+                    more["residual_epilogue_us"] = round(timed(lambda: [ops.skinny_gemm_residual(inp, w, resid, nw, 1e-5) for w in ws]), 2)
+                else:
+                    rows = ops.skinny_gemm_residual(x, weights(H, H)[0], resid, nw, 1e-5)
+                    more["norm_finishing_us"] = round(timed(lambda: [ops.skinny_gemm_scaled(rows, w, silu_mul=silu) for w in ws]), 2)
+                out(f"decode product {name} M{M} ({n} x {k})", us, GBs=round(n * k * 2 / us / 1e3, 1), cublas_us=round(us_lib, 2), **more)
+    if on("decode_attention"):
+        for B, ctx in ((1, 1024), (8, 1024), (64, 1024), (8, 8192)):
+            blocks = -(-ctx // page)
+            kvs = [torch.randn(B * blocks, 2, nkv, page, d, device=dev).to(torch.bfloat16) for _ in range(L)]
+            bt = torch.arange(B * blocks, dtype=torch.int32, device=dev).view(B, blocks).contiguous()
+            q = torch.randn(B, QKV, device=dev).to(torch.bfloat16)
+            o = torch.empty(B, nh * d, dtype=torch.bfloat16, device=dev)
+            req = torch.arange(B, dtype=torch.int32, device=dev)
+            pos = torch.full((B,), ctx - 1, dtype=torch.int32, device=dev)
+            splits = ops.decode_splits(B, nkv, ctx)
+            us = timed(lambda: [ops.decode_attention(q, QKV, o, kv, bt, None, B, req, pos, nh, nkv, d, 0, d ** -0.5, splits)
+                                for kv in kvs])
+            out(f"decode attention B{B} ctx{ctx} splits{splits}", us, GBs=round(B * ctx * nkv * d * 4 / us / 1e3, 1))
+    if on("prefill_gemm"):
+        for M in (2048, 8192):
+            x = torch.randn(M, H, device=dev).to(torch.bfloat16)
+            xi = torch.randn(M, I, device=dev).to(torch.bfloat16)
+            for name, n, k, silu in (("qkv", QKV, H, False), ("o", H, H, False), ("gate_up", 2 * I, H, True), ("down", H, I, False)):
+                ws = weights(n, k)
+                inp = xi if k == I else x
+                fl = 2 * M * n * k
+                res = {}
+                for tile in ops.TC_TILES:
+                    us = timed(lambda: [ops.tc_gemm(inp, w, silu_mul=silu, tile=tile) for w in ws])
+                    res[tile] = f"{us:.1f} us, {fl / us / 1e6:.0f} TFLOP/s"
+                us_lib = timed(lambda: [ops.silu_mul(torch.mm(inp, w.t()), interleaved=True) if silu else torch.mm(inp, w.t()) for w in ws])
+                out(f"prefill product {name} M{M} ({n} x {k})", us_lib, cublas_TFLOPs=round(fl / us_lib / 1e6), **res)
+    if on("prefill_attention"):
+        for T in (2048, 8192):
+            blocks = -(-T // page)
+            kvs = [torch.randn(blocks, 2, nkv, page, d, device=dev).to(torch.bfloat16) for _ in range(L)]
+            bt = torch.arange(blocks, dtype=torch.int32, device=dev).view(1, blocks).contiguous()
+            q = torch.randn(T, QKV, device=dev).to(torch.bfloat16)
+            o = torch.empty(T, nh * d, dtype=torch.bfloat16, device=dev)
+            pos = torch.arange(T, dtype=torch.int32, device=dev)
+            t128 = torch.tensor([(k, min(128, T - k), 0) for k in range(0, T, 128)], dtype=torch.int32, device=dev)
+            t64 = torch.tensor([(k, min(64, T - k), 0) for k in range(0, T, 64)], dtype=torch.int32, device=dev)
+            fl = nh * 4 * d * T * (T + 1) / 2
+            us = timed(lambda: [ops.prefill_attention_tc(q, o, kv, bt, t128, pos, nh, nkv, d, 0, d ** -0.5) for kv in kvs])
+            us2 = timed(lambda: [ops.prefill_attention(q, QKV, o, kv, bt, t64, pos, nh, nkv, d, 0, d ** -0.5) for kv in kvs])
+            out(f"prefill attention T{T} tcgen05", us, TFLOPs=round(fl / us / 1e6, 1), mma_sync_us=round(us2, 2))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -280,8 +382,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the named configuration (0: all)")
-    ap.add_argument("--mode", default="all", choices=["all", "decode", "prefill"],
-                    help="all: the contract's line; decode / prefill: one short measurement (for profiling)")
+    ap.add_argument("--mode", default="all", choices=["all", "decode", "prefill", "kernels"],
+                    help="all: the contract's line; decode / prefill: one short measurement (for profiling); "
+                         "kernels: the hot kernels one by one")
+    ap.add_argument("--cases", default="", help="--mode kernels: comma-separated subset of decode_gemm, "
+                    "decode_attention, prefill_gemm, prefill_attention")
     ap.add_argument("--batch", type=int, default=8, help="--mode decode: requests in the batch")
     ap.add_argument("--tokens", type=int, default=PREFILL_TOKENS, help="--mode prefill: prompt length")
     args = ap.parse_args()
@@ -294,6 +399,8 @@ def main():
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     args.warmup = max(3, args.warmup)
+    if args.mode == "kernels":
+        return run_kernels(args)
     return run_ours(args)
 
 
