@@ -23,6 +23,7 @@ namespace cg = cooperative_groups;
 #define EPI_NONE 0
 #define EPI_SILU_MUL 1
 #define EPI_RESIDUAL 2            // out (32-bit) += product; also the next norm's input and sums of squares
+#define EPI_ROPE_CACHE 3          // the fused q|k|v projection: rotate q and k, write q out and k, v into the paged cache
 #define PRO_PLAIN 0
 #define PRO_SCALED 1              // x is a residual row times the norm's weight; 1 / rms is applied to the sums
 
@@ -34,6 +35,13 @@ namespace cg = cooperative_groups;
 //                             before the epilogue (and before SiLU-mul).
 // Sums of squares, 1 / rms and both products are 32-bit; the one rounding to bfloat16 is the one every
 // product's input has.  ss rows are ss_ld floats apart; partial sums are added in a fixed order.
+//
+// EPI_ROPE_CACHE: the product is the q|k|v projection of single tokens, N = (nh + 2 nkv) d with d % 16 == 0 and the
+// rows of every q and k head reordered so that rotation pair i sits at (16 (i / 8) + i % 8, + 8) (rope_cache.cu's
+// `paired8` layout): every 16-row tile of W holds 8 whole pairs, so the block that owns the rows rotates them
+// (32-bit sums, angles from the table [max_pos, d] = cos | sin at the token's position, one rounding), writes q
+// to out and k and v straight into the token's slot of the paged cache [pages, 2, nkv, page_size, d]; the k and v
+// columns of out are not written.  One kernel instead of the product followed by rope_cache.cu's.
 struct SkinnyFusion {
     const float* norm_w;
     bf16* scaled_out;             // [M, N], rows ldo apart like out
@@ -42,6 +50,12 @@ struct SkinnyFusion {
     int ss_in_blocks;
     int ss_ld;
     float eps;
+    const float* rope_table;      // EPI_ROPE_CACHE from here
+    const int* positions;
+    const int* slots;             // nullptr: nothing is written to the cache
+    bf16* kv_cache;
+    int nh, nkv, d, page_size, max_pos;
+    int* err;                     // set to 1 when a position is outside the table (never read outside it)
 };
 
 __device__ __forceinline__ uint4 ld_stream16(const void* p) {
@@ -237,6 +251,45 @@ skinny_gemm_kernel(const bf16* __restrict__ W, const bf16* __restrict__ x, int l
 #pragma unroll
             for (int off = ROWS / 2; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
             if (row == 0) fu.ss_out[(size_t)block_row * fu.ss_ld + m] = s;
+        }
+    } else if (EPI == EPI_ROPE_CACHE) {
+        const int half = fu.d >> 1;
+        for (int idx = threadIdx.x; idx < (ROWS / 2) * COLS; idx += NW * 32) {
+            const int m = idx / (ROWS / 2), pr = idx - m * (ROWS / 2);        // pair pr of the block: tile pr / 8, row pr % 8
+            const int row = (pr >> 3) * 16 + (pr & 7);
+            const int f = n0 + row;                                           // output feature of the pair's first element
+            if (m < M && f + 8 < N) {
+                const float sc = PRO == PRO_SCALED ? inv_rms(m) : 1.f;
+                const float x0 = fin[row * COLS + m] * sc, x1 = fin[(row + 8) * COLS + m] * sc;
+                const int head = f / fu.d, e = f - head * fu.d;               // e: storage index inside the head
+                float y0 = x0, y1 = x1;
+                if (head < fu.nh + fu.nkv) {
+                    int pos = fu.positions[m];
+                    if (pos < 0 || pos >= fu.max_pos) {
+                        if (fu.err) atomicExch(fu.err, 1);
+                        pos = 0;
+                    }
+                    const int i = ((e >> 4) << 3) + (e & 7);                  // the pair's number = its angle's index
+                    const float c = __ldg(fu.rope_table + (size_t)pos * fu.d + i);
+                    const float sn = __ldg(fu.rope_table + (size_t)pos * fu.d + half + i);
+                    y0 = x0 * c - x1 * sn;
+                    y1 = x1 * c + x0 * sn;
+                }
+                if (head < fu.nh) {
+                    bf16* o = reinterpret_cast<bf16*>(out) + (size_t)m * ldo + f;
+                    o[0] = __float2bfloat16_rn(y0);
+                    o[8] = __float2bfloat16_rn(y1);
+                } else if (fu.slots) {
+                    const int slot = fu.slots[m];
+                    if (slot >= 0) {
+                        const int kind = head < fu.nh + fu.nkv ? 0 : 1, kvh = head - fu.nh - kind * fu.nkv;
+                        const int page = slot / fu.page_size, off = slot - page * fu.page_size;
+                        bf16* dst = fu.kv_cache + ((((size_t)page * 2 + kind) * fu.nkv + kvh) * fu.page_size + off) * fu.d + e;
+                        dst[0] = __float2bfloat16_rn(y0);
+                        dst[8] = __float2bfloat16_rn(y1);
+                    }
+                }
+            }
         }
     } else if (EPI == EPI_NONE) {
         for (int idx = threadIdx.x; idx < ROWS * COLS; idx += NW * 32) {

@@ -9,18 +9,27 @@
 // (crates/vllm-cuda/src/kernels/paged_attention.cu:111-138).  The reference
 // never calls its rope kernel; here rotation happens once, before the write,
 // so cached keys are rotated by their absolute position.
+//
+// Row layout `paired8` (head sizes that are multiples of 16): the projection's rows of every q and k head were
+// reordered at load so that pair i = (i, i + d/2) sits at storage indices (16 (i / 8) + i % 8, + 8): every 16
+// consecutive features hold 8 whole pairs, which lets the decode product rotate in its own epilogue
+// (gemm_skinny.cuh).  q.k is unchanged by a reordering that q and k share; the cache then holds k in that order.
 #include "common.cuh"
+
+// storage index of the first element of pair i
+__device__ __forceinline__ int rope_lo_index(int i, bool paired8) { return paired8 ? ((i >> 3) << 4) + (i & 7) : i; }
 
 // qkv: [T, (nh + 2 nkv) d], q rotated in place.  kv_cache: [NP, 2, nkv, ps, d].
 template <typename A>
 __global__ void rope_cache_kernel(A* __restrict__ qkv, const float* __restrict__ table,
                                   const int* __restrict__ positions, const int* __restrict__ slots,
                                   A* __restrict__ kv_cache, int nh, int nkv, int d, int page_size,
-                                  int max_pos, int* __restrict__ err) {
+                                  int max_pos, int* __restrict__ err, int paired8) {
     pdl_wait();
     pdl_trigger();
     const int t = blockIdx.x;
     const int half = d >> 1;
+    const int apart = paired8 ? 8 : half;            // distance between the two elements of a pair
     int pos = positions[t];
     if (pos < 0 || pos >= max_pos) {          // host-validated; never read outside the table
         if (threadIdx.x == 0 && err) atomicExch(err, 1);
@@ -41,8 +50,9 @@ __global__ void rope_cache_kernel(A* __restrict__ qkv, const float* __restrict__
     const int n_rot = (nh + nkv) * half;
     for (int w = threadIdx.x; w < n_rot; w += blockDim.x) {
         const int h = w / half, i = w - h * half;
+        const int e = rope_lo_index(i, paired8);
         A* x = row + (size_t)h * d;
-        const float lo = to_f32(x[i]), hi = to_f32(x[i + half]);
+        const float lo = to_f32(x[e]), hi = to_f32(x[e + apart]);
         float nlo = lo, nhi = hi;
         if (cs) {
             const float c = cs[i], s = cs[half + i];
@@ -50,12 +60,12 @@ __global__ void rope_cache_kernel(A* __restrict__ qkv, const float* __restrict__
             nhi = hi * c + lo * s;
         }
         const A olo = from_f32<A>(nlo), ohi = from_f32<A>(nhi);
-        x[i] = olo;
-        x[i + half] = ohi;
+        x[e] = olo;
+        x[e + apart] = ohi;
         if (h >= nh && kdst) {
             A* kd = kdst + (size_t)(h - nh) * head_stride;
-            kd[i] = olo;
-            kd[i + half] = ohi;
+            kd[e] = olo;
+            kd[e + apart] = ohi;
         }
     }
     if (vdst) {
@@ -84,11 +94,12 @@ template <typename A>
 __global__ void rope_cache_vec2_kernel(A* __restrict__ qkv, const float* __restrict__ table,
                                        const int* __restrict__ positions, const int* __restrict__ slots,
                                        A* __restrict__ kv_cache, int nh, int nkv, int d, int page_size,
-                                       int max_pos, int* __restrict__ err) {
+                                       int max_pos, int* __restrict__ err, int paired8) {
     pdl_wait();
     pdl_trigger();
     const int t = blockIdx.x;
     const int half = d >> 1, hq = half >> 1;          // hq: element pairs per half head
+    const int apart = paired8 ? 8 : half;
     int pos = positions[t];
     if (pos < 0 || pos >= max_pos) {
         if (threadIdx.x == 0 && err) atomicExch(err, 1);
@@ -107,21 +118,22 @@ __global__ void rope_cache_vec2_kernel(A* __restrict__ qkv, const float* __restr
     const size_t head_stride = (size_t)page_size * d;
     const int n_rot = (nh + nkv) * hq;
     for (int w = threadIdx.x; w < n_rot; w += blockDim.x) {
-        const int h = w / hq, i = (w - h * hq) * 2;
+        const int h = w / hq, i = (w - h * hq) * 2;   // pairs i and i + 1: neighbours in storage in both layouts
+        const int e = rope_lo_index(i, paired8);
         A* x = row + (size_t)h * d;
-        const float2 lo = Pair<A>::load(x + i), hi = Pair<A>::load(x + i + half);
+        const float2 lo = Pair<A>::load(x + e), hi = Pair<A>::load(x + e + apart);
         float2 nlo = lo, nhi = hi;
         if (cs) {
             const float2 c = *reinterpret_cast<const float2*>(cs + i), s = *reinterpret_cast<const float2*>(cs + half + i);
             nlo = make_float2(lo.x * c.x - hi.x * s.x, lo.y * c.y - hi.y * s.y);
             nhi = make_float2(hi.x * c.x + lo.x * s.x, hi.y * c.y + lo.y * s.y);
         }
-        Pair<A>::store(x + i, nlo);
-        Pair<A>::store(x + i + half, nhi);
+        Pair<A>::store(x + e, nlo);
+        Pair<A>::store(x + e + apart, nhi);
         if (h >= nh && kdst) {
             A* kd = kdst + (size_t)(h - nh) * head_stride;
-            Pair<A>::store(kd + i, nlo);
-            Pair<A>::store(kd + i + half, nhi);
+            Pair<A>::store(kd + e, nlo);
+            Pair<A>::store(kd + e + apart, nhi);
         }
     }
     if (vdst) {
@@ -134,27 +146,28 @@ __global__ void rope_cache_vec2_kernel(A* __restrict__ qkv, const float* __restr
     }
 }
 
+// paired8: 0 pairs (i, i + d/2) as stored by the model; 1 the reordered layout above (d % 16 == 0).
 extern "C" int rg_rope_cache(void* qkv, int dtype, const float* table, const int* positions,
                              const int* slots, void* kv_cache, int T, int nh, int nkv, int d,
-                             int page_size, int max_pos, int* err, void* stream) {
+                             int page_size, int max_pos, int* err, int paired8, void* stream) {
     if (T <= 0) return 0;
-    if (d % 2) return RG_ERR_UNSUPPORTED;
+    if (d % 2 || (paired8 && d % 16)) return RG_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = 256;
     if (d % 4 == 0 && (uintptr_t)qkv % 8 == 0 && (uintptr_t)kv_cache % 8 == 0 && (uintptr_t)table % 8 == 0) {
         if (dtype == RG_DTYPE_BF16)
             return rg_launch(rope_cache_vec2_kernel<bf16>, dim3(T), dim3(threads), 0, s, 1, (bf16*)qkv, table, positions,
-                             slots, (bf16*)kv_cache, nh, nkv, d, page_size, max_pos, err);
+                             slots, (bf16*)kv_cache, nh, nkv, d, page_size, max_pos, err, paired8);
         if (dtype == RG_DTYPE_F32)
             return rg_launch(rope_cache_vec2_kernel<float>, dim3(T), dim3(threads), 0, s, 1, (float*)qkv, table,
-                             positions, slots, (float*)kv_cache, nh, nkv, d, page_size, max_pos, err);
+                             positions, slots, (float*)kv_cache, nh, nkv, d, page_size, max_pos, err, paired8);
         return RG_ERR_UNSUPPORTED;
     }
     if (dtype == RG_DTYPE_BF16)
         return rg_launch(rope_cache_kernel<bf16>, dim3(T), dim3(threads), 0, s, 1, (bf16*)qkv, table, positions, slots,
-                         (bf16*)kv_cache, nh, nkv, d, page_size, max_pos, err);
+                         (bf16*)kv_cache, nh, nkv, d, page_size, max_pos, err, paired8);
     if (dtype == RG_DTYPE_F32)
         return rg_launch(rope_cache_kernel<float>, dim3(T), dim3(threads), 0, s, 1, (float*)qkv, table, positions,
-                         slots, (float*)kv_cache, nh, nkv, d, page_size, max_pos, err);
+                         slots, (float*)kv_cache, nh, nkv, d, page_size, max_pos, err, paired8);
     return RG_ERR_UNSUPPORTED;
 }

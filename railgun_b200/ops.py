@@ -294,11 +294,30 @@ def skinny_gemm_scaled(rows: NormedRows, weight: torch.Tensor, silu_mul: bool = 
     return out
 
 
+def rope_pair_order(d: int) -> torch.Tensor:
+    """The "paired8" order of a head's features (d % 16 == 0): storage index ->
+    original feature, such that rotation pair i = (i, i + d/2) sits at storage
+    indices (16 (i // 8) + i % 8, + 8): every 16 consecutive features hold 8
+    whole pairs.  q . k does not notice a reordering that q and k share."""
+    if d % 16:
+        raise KernelError(f"the paired8 order needs a head size that is a multiple of 16, not {d}")
+    s = torch.arange(d)
+    blk, r = s // 16, s % 16
+    return torch.where(r < 8, 8 * blk + r, d // 2 + 8 * blk + (r - 8))
+
+
+def reorder_rope_rows(weight: torch.Tensor, n_heads: int, d: int) -> torch.Tensor:
+    """Rows of a q or k projection [n_heads * d, K] in the paired8 order."""
+    order = rope_pair_order(d).to(weight.device)
+    return weight.view(n_heads, d, -1)[:, order, :].reshape(n_heads * d, -1).contiguous()
+
+
 def rope_cache_write(qkv: torch.Tensor, table, positions: torch.Tensor, slots, kv_cache,
-                     nh: int, nkv: int, d: int, page_size: int, err_flag=None) -> None:
+                     nh: int, nkv: int, d: int, page_size: int, err_flag=None, paired8: bool = False) -> None:
     """Rotate the q and k heads of qkv [T, (nh+2nkv)d] in place by ``table``
     [max_pos, d] (None: no rotation) and write k, v to the paged cache
-    [NP, 2, nkv, page_size, d] at ``slots`` (None: no write)."""
+    [NP, 2, nkv, page_size, d] at ``slots`` (None: no write).  ``paired8``: the
+    heads' features are in ``rope_pair_order``."""
     _check(qkv, "qkv")
     _check(positions, "positions", torch.int32)
     T = qkv.shape[0]
@@ -319,7 +338,53 @@ def rope_cache_write(qkv: torch.Tensor, table, positions: torch.Tensor, slots, k
     _ok(_fn("rope_cache", "rg_rope_cache")(
         _ptr(qkv), c_int(_dtype_code(qkv)), _ptr(table), _ptr(positions), _ptr(slots),
         _ptr(kv_cache if slots is not None else None), c_int(T), c_int(nh), c_int(nkv), c_int(d),
-        c_int(page_size), c_int(max_pos), _ptr(err_flag), _stream()), "rope_cache_write")
+        c_int(page_size), c_int(max_pos), _ptr(err_flag), c_int(1 if paired8 else 0), _stream()), "rope_cache_write")
+
+
+def skinny_gemm_rope_cache(x, weight: torch.Tensor, table: torch.Tensor, positions: torch.Tensor, slots, kv_cache,
+                           nh: int, nkv: int, d: int, err_flag=None) -> torch.Tensor:
+    """The q|k|v projection of up to 8 single tokens with the rotary encoding
+    and the cache write inside the product's kernel: returns [M, (nh+2nkv)d]
+    whose q heads are rotated (its k and v columns are not written); k
+    (rotated) and v go to ``kv_cache`` at ``slots`` (None: no write).  ``x``:
+    bfloat16 rows or a ``NormedRows``; ``weight``'s q and k rows are in
+    ``rope_pair_order``."""
+    rows = x if isinstance(x, NormedRows) else None
+    xin = rows.scaled if rows is not None else x
+    if not skinny_rope_ok(x, weight, d):
+        raise KernelError(f"skinny_gemm_rope_cache refuses rows {tuple(xin.shape)}, W {tuple(weight.shape)}, head size {d}")
+    M, K = xin.shape
+    N = weight.shape[0]
+    if weight.shape[1] != K or N != (nh + 2 * nkv) * d:
+        raise KernelError(f"skinny_gemm_rope_cache: W {tuple(weight.shape)} is not [({nh} + 2 x {nkv}) x {d}, {K}]")
+    _check(table, "rope table", torch.float32)
+    _check(positions, "positions", torch.int32)
+    if table.shape[1] != d or positions.numel() < M:
+        raise KernelError("skinny_gemm_rope_cache: the table's head size or the number of positions does not match")
+    page_size = 0
+    if slots is not None:
+        _check(slots, "slots", torch.int32)
+        _check(kv_cache, "kv_cache", torch.bfloat16)
+        page_size = kv_cache.shape[3]
+        if tuple(kv_cache.shape[1:]) != (2, nkv, page_size, d) or slots.numel() < M:
+            raise KernelError(f"kv cache shape {tuple(kv_cache.shape)} does not match [pages, 2, {nkv}, page, {d}]")
+    out = torch.empty((M, N), dtype=torch.bfloat16, device=xin.device)
+    _ok(_fn("gemm_skinny_fused", "rg_skinny_gemm_rope_cache")(
+        _ptr(weight), _ptr(xin), c_int(xin.stride(0)), c_float(rows.eps if rows is not None else 0.0),
+        _ptr(rows.partials if rows is not None else None), c_int(rows.partials.stride(0) if rows is not None else 0),
+        c_int(rows.blocks if rows is not None else 0), _ptr(out), c_int(N), c_int(M), c_int(N), c_int(K), _ptr(table),
+        _ptr(positions), _ptr(slots), _ptr(kv_cache if slots is not None else None), c_int(nh), c_int(nkv), c_int(d),
+        c_int(page_size), c_int(table.shape[0]), _ptr(err_flag), _stream()), "skinny_gemm_rope_cache")
+    return out
+
+
+def skinny_rope_ok(x, weight: torch.Tensor, d: int) -> bool:
+    """Can the q|k|v projection of these rows rotate and write the cache in its own kernel?"""
+    if d % 16:
+        return False
+    if isinstance(x, NormedRows):
+        return skinny_scaled_ok(x, weight)
+    return x.shape[0] <= min(SKINNY_AUTO_ROWS, SKINNY_FUSED_MAX_ROWS) and skinny_gemm_ok(x, weight)
 
 
 def paged_attention_general(q: torch.Tensor, q_stride: int, kv_cache: torch.Tensor, block_table: torch.Tensor,

@@ -54,31 +54,44 @@ class PagedAttention(Mixer):
         self.window = int(p.get("window") or 0)
         self.scale = float(p["scale"]) if p.get("scale") is not None else float(self.d) ** -0.5
         a = prefix + "self_attn."
-        self.w_qkv = torch.cat([tensors.get(a + "q_proj.weight", env.dtype),
-                                tensors.get(a + "k_proj.weight", env.dtype),
-                                tensors.get(a + "v_proj.weight", env.dtype)], dim=0).contiguous()
-        tensors.drop(a + "q_proj.weight", a + "k_proj.weight", a + "v_proj.weight")
-        self.w_o = tensors.get(a + "o_proj.weight", env.dtype)
         pos = p.get("position")
         self.position = None
         if pos is not None:
             self.position = tensors.shared_part(("position", pos), lambda: POSITION_ENCODINGS.get(pos.kind)(
                 pos.params, prefix, env, tensors))
+        wq, wk = tensors.get(a + "q_proj.weight", env.dtype), tensors.get(a + "k_proj.weight", env.dtype)
+        # With a rotary table and a head size in steps of 16, q and k rows are kept in the order in which every
+        # 16 rows hold 8 whole rotation pairs (q . k does not notice; the cache then holds k in that order): the
+        # projection of a few single tokens can then rotate and write the cache in its own kernel.
+        self.paired8 = getattr(self.position, "rotary_table", None) is not None and self.d % 16 == 0
+        if self.paired8:
+            wq, wk = ops.reorder_rope_rows(wq, self.nh, self.d), ops.reorder_rope_rows(wk, self.nkv, self.d)
+        self.w_qkv = torch.cat([wq, wk, tensors.get(a + "v_proj.weight", env.dtype)], dim=0).contiguous()
+        tensors.drop(a + "q_proj.weight", a + "k_proj.weight", a + "v_proj.weight")
+        self.w_o = tensors.get(a + "o_proj.weight", env.dtype)
 
     takes_normed_rows = True
     defers_output = True
 
     def forward(self, x, batch, cache, writes=True, defer=False):
         nh, nkv, d = self.nh, self.nkv, self.d
-        qkv = ops.linear(x, self.w_qkv)
         slots = batch.slot_mapping[cache.group]
-        kv_dest = (cache.kv, slots) if writes else None
-        wrote = False
-        if self.position is not None:
-            wrote = self.position.apply(qkv, batch, nh, nkv, d, kv_dest)
-        if writes and not wrote:
-            ops.rope_cache_write(qkv, None, batch.positions, slots, cache.kv, nh, nkv, d, cache.page_size,
-                                 batch.err_flag)
+        if self.paired8 and self.env.dtype == torch.bfloat16 and ops.skinny_rope_ok(x, self.w_qkv, d):
+            # a few single tokens: projection, rotation and cache write in one kernel
+            qkv = ops.skinny_gemm_rope_cache(x, self.w_qkv, self.position.rotary_table, batch.positions,
+                                             slots if writes else None, cache.kv, nh, nkv, d, batch.err_flag)
+        else:
+            qkv = ops.linear(x, self.w_qkv)
+            kv_dest = (cache.kv, slots) if writes else None
+            wrote = False
+            if self.position is not None:
+                if self.paired8:
+                    wrote = self.position.apply(qkv, batch, nh, nkv, d, kv_dest, paired8=True)
+                else:
+                    wrote = self.position.apply(qkv, batch, nh, nkv, d, kv_dest)
+            if writes and not wrote:
+                ops.rope_cache_write(qkv, None, batch.positions, slots, cache.kv, nh, nkv, d, cache.page_size,
+                                     batch.err_flag)
         out = self.attend(qkv, batch, cache)
         return ops.PendingLinear(out, self.w_o) if defer else ops.linear(out, self.w_o)
 

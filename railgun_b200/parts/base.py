@@ -47,7 +47,15 @@ class PositionEncoding(Part):
     and k heads of ``qkv`` [T, (nh+2nkv)d] in place.  ``kv_dest`` is None or
     ``(kv tensor, slot mapping)``; an encoding that can write k and v to the
     cache in the same pass does so and returns True, otherwise it returns False
-    and the mixer writes them."""
+    and the mixer writes them.
+
+    Optional: an encoding that is a rotation of pairs (i, i + d/2) by angles from
+    a table [max_position, d] = cos | sin may expose it as ``rotary_table`` and
+    take a keyword ``paired8`` in ``apply``; the attention part then keeps its q
+    and k rows in ``ops.rope_pair_order`` and, for a few single tokens, rotates
+    inside the projection's kernel."""
+
+    rotary_table = None
 
     def apply(self, qkv, batch, nh, nkv, d, kv_dest) -> bool:
         raise NotImplementedError

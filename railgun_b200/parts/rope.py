@@ -55,10 +55,16 @@ class RotaryEncoding(PositionEncoding):
         self.table = rope_table(params["head_dim"], params["theta"], params.get("scaling"),
                                 params["max_position"]).to(env.device)
 
-    def apply(self, qkv, batch, nh, nkv, d, kv_dest) -> bool:
+    @property
+    def rotary_table(self):
+        """[max_position, d] = cos | sin: lets a mixer rotate inside its own kernels."""
+        return self.table
+
+    def apply(self, qkv, batch, nh, nkv, d, kv_dest, paired8: bool = False) -> bool:
         kv, slots = kv_dest if kv_dest is not None else (None, None)
         page_size = kv.shape[3] if kv is not None else 1
-        ops.rope_cache_write(qkv, self.table, batch.positions, slots, kv, nh, nkv, d, page_size, batch.err_flag)
+        ops.rope_cache_write(qkv, self.table, batch.positions, slots, kv, nh, nkv, d, page_size, batch.err_flag,
+                             paired8=paired8)
         return kv is not None
 
 

@@ -214,6 +214,92 @@ def test_rope_and_cache_write(nh, nkv, d, page, dtype):
     assert torch.equal(kv_d2.cpu()[s0 // page, 0, :, s0 % page].reshape(-1), qkv[0, nh * d:(nh + nkv) * d])
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,d,page", [(5, 1, 48, 8), (4, 2, 16, 16), (3, 3, 128, 32)])
+def test_rope_in_the_paired_row_order(nh, nkv, d, page, dtype):
+    """The same rotation when every head's features are stored in the order that puts 8 whole pairs into every 16
+    features: the results are the standard ones, reordered."""
+    from railgun_b200 import ops
+    from railgun_b200.parts.rope import rope_table
+    g = torch.Generator().manual_seed(d + nh)
+    T, NP, max_pos = 13, 5, 200
+    table = rope_table(d, 10000.0, None, max_pos).to(DEV)
+    order = ops.rope_pair_order(d)
+    assert sorted(order.tolist()) == list(range(d))
+    pairs = order.view(d // 16, 2, 8)                           # every 16 stored features: 8 firsts, then their partners
+    assert torch.equal(pairs[:, 1], pairs[:, 0] + d // 2)
+    qkv = torch.randn(T, nh + 2 * nkv, d, generator=g).to(dtype)
+    stored = qkv.clone()
+    stored[:, :nh + nkv] = qkv[:, :nh + nkv][:, :, order]       # q and k heads reordered, v as it is
+    positions = torch.randint(0, max_pos, (T,), generator=g, dtype=torch.int32).to(DEV)
+    slots = torch.randperm(NP * page, generator=g)[:T].to(torch.int32).to(DEV)
+    a, kv_a = qkv.reshape(T, -1).to(DEV), torch.zeros(NP, 2, nkv, page, d, dtype=dtype, device=DEV)
+    b, kv_b = stored.reshape(T, -1).to(DEV), torch.zeros(NP, 2, nkv, page, d, dtype=dtype, device=DEV)
+    ops.rope_cache_write(a, table, positions, slots, kv_a, nh, nkv, d, page)
+    ops.rope_cache_write(b, table, positions, slots, kv_b, nh, nkv, d, page, paired8=True)
+    a, b = a.view(T, nh + 2 * nkv, d).cpu(), b.view(T, nh + 2 * nkv, d).cpu()
+    assert torch.equal(b[:, :nh + nkv], a[:, :nh + nkv][:, :, order]) and torch.equal(b[:, nh + nkv:], a[:, nh + nkv:])
+    assert torch.equal(kv_b[:, 0].cpu(), kv_a[:, 0].cpu()[..., order]) and torch.equal(kv_b[:, 1], kv_a[:, 1])
+    with pytest.raises(ops.KernelError):
+        ops.rope_pair_order(24)
+
+
+@pytest.mark.parametrize("M", [1, 5, 8])
+@pytest.mark.parametrize("nh,nkv,d,K,page", [(4, 2, 64, 256, 16), (32, 8, 64, 2048, 16), (6, 3, 48, 136, 8), (40, 8, 128, 1024, 32)])
+def test_projection_with_rotation_and_cache_write_in_its_kernel(M, nh, nkv, d, K, page):
+    """q|k|v projection of a few single tokens, rotated and written to the cache by the product's own kernel,
+    against the product followed by the rope kernel, and against 64-bit arithmetic; from plain rows and from rows
+    whose norm the product finishes."""
+    from railgun_b200 import ops
+    from railgun_b200.parts.rope import rope_table
+    g = torch.Generator().manual_seed(M + nh + d + K)
+    N, NP, max_pos = (nh + 2 * nkv) * d, 7, 300
+    table = rope_table(d, 500000.0, None, max_pos).to(DEV)
+    w = (torch.randn(N, K, generator=g) / K ** 0.5).to(torch.bfloat16).to(DEV)
+    positions = torch.randint(0, max_pos, (M,), generator=g, dtype=torch.int32).to(DEV)
+    slots = torch.randperm(NP * page, generator=g)[:M].to(torch.int32)
+    if M > 2:
+        slots[1] = -1                                           # a token whose keys are not stored
+    slots = slots.to(DEV)
+
+    def check(x):
+        kv_f = torch.zeros(NP, 2, nkv, page, d, dtype=torch.bfloat16, device=DEV)
+        kv_u = torch.zeros_like(kv_f)
+        fused = ops.skinny_gemm_rope_cache(x, w, table, positions, slots, kv_f, nh, nkv, d)
+        plain = ops.linear(x, w)                                # a NormedRows goes through the norm-finishing product
+        exact = plain.double().clone()
+        ops.rope_cache_write(plain, table, positions, slots, kv_u, nh, nkv, d, page, paired8=True)
+        # the unfused route rounds the projection to bfloat16 before it rotates: equal within that rounding
+        assert rel_err(fused[:, :nh * d], plain[:, :nh * d].double()) < 1e-2
+        assert rel_err(kv_f, kv_u.double()) < 1e-2
+        used = kv_u != 0
+        assert torch.equal(kv_f != 0, used)                     # the same places written, nothing else
+        # against the rotation in 64-bit of the unrounded... (here: of the rounded projection; one rounding apart)
+        q = exact[:, :nh * d].view(M, nh, d)
+        i = ops.rope_pair_order(d).to(DEV)
+        inv_order = torch.argsort(i)
+        std = q[:, :, inv_order]                                # back to the model's feature order
+        ang = table[positions.long()].double()
+        c, sn = ang[:, None, :d // 2], ang[:, None, d // 2:]
+        rot = torch.cat([std[..., :d // 2] * c - std[..., d // 2:] * sn, std[..., d // 2:] * c + std[..., :d // 2] * sn], -1)
+        assert rel_err(fused[:, :nh * d].view(M, nh, d)[:, :, inv_order], rot) < 1e-2
+
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+    check(x)
+    # rows whose norm is finished inside the product
+    wp = (torch.randn(K, 64, generator=g) / 8).to(torch.bfloat16).to(DEV)
+    resid = torch.randn(M, K, generator=g).to(DEV)
+    rows = ops.skinny_gemm_residual(torch.randn(M, 64, generator=g).to(torch.bfloat16).to(DEV), wp, resid,
+                                    (torch.rand(K, generator=g) + 0.5).to(DEV), 1e-5)
+    check(rows)
+    # without slots nothing is written
+    kv = torch.zeros(NP, 2, nkv, page, d, dtype=torch.bfloat16, device=DEV)
+    ops.skinny_gemm_rope_cache(x, w, table, positions, None, kv, nh, nkv, d)
+    assert not kv.any()
+    assert not ops.skinny_rope_ok(torch.zeros(9, K, dtype=torch.bfloat16, device=DEV), w, d)
+    assert not ops.skinny_rope_ok(x, w, 24)
+
+
 @pytest.mark.parametrize("V", [1000, 128256])
 def test_argmax_with_ties(V):
     from railgun_b200 import ops
