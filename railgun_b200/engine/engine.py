@@ -75,7 +75,9 @@ class Engine:
             return []
         params = [self._params[r] for r in wanted]
         if self.runner.last_greedy is not None and all(p.temperature == 0.0 for p in params):
-            sampled = self.runner.last_greedy.cpu().numpy()     # the decode graph already took the argmax
+            sampled = self.runner.greedy_tokens_host()          # the decode graph took the argmax and copied it out
+            if sampled is None:
+                sampled = self.runner.last_greedy.cpu().numpy()
         else:
             sampled = self.sampler.sample(logits, params, [self.scheduler.num_generated(r) for r in wanted])
         ops.tc_gemm_check()                 # the tokens are on the host: the step has finished

@@ -90,6 +90,8 @@ class StaticDecodeBatch:
         n_ints = (5 + G) * B + G * B * MB
         self.host = torch.zeros(n_ints, dtype=torch.int32, pin_memory=True)
         self.host_np = self.host.numpy()
+        self.host_out = torch.zeros(B, dtype=torch.int32, pin_memory=True)     # the step's greedy tokens, copied by the graph
+        self.host_out_np = self.host_out.numpy()
         self.dev = torch.zeros(n_ints, dtype=torch.int32, device=dev)
         seg = lambda i: self.dev[i * B:(i + 1) * B]
         ar = torch.arange(B + 1, dtype=torch.int32, device=dev)
@@ -104,6 +106,12 @@ class StaticDecodeBatch:
                          for g in range(G)],
             err_flag=runner.err_flag, decode_only=True)
         self.step_graph = None
+        self.in_flight = None          # an event after the last replay that reads ``host`` and writes ``host_out``
+
+    def wait_until_reusable(self) -> None:
+        """The pinned buffers may be written again once the last replay that copies them has run."""
+        if self.in_flight is not None and not self.in_flight.query():
+            self.in_flight.synchronize()
 
     def upload(self) -> int:
         self.dev.copy_(self.host, non_blocking=True)
@@ -158,6 +166,7 @@ class ModelRunner:
         self._ctx_hint = 0
         self.last_h2d_bytes = 0
         self.last_greedy = None
+        self._greedy_host = None
 
     @property
     def alloc(self):
@@ -212,12 +221,18 @@ class ModelRunner:
         counter = ops.launch_counter()
 
         def body():
+            if loop is None:
+                # a single step carries its own transfers: the packed inputs from pinned memory first, the greedy
+                # tokens to pinned memory last, so that one graph launch and one wait are all the host does
+                static.dev.copy_(static.host, non_blocking=True)
             logits = self.model.forward(static.batch, self.views)
             sampled = ops.argmax(logits)
             if loop is not None:
                 b = static.batch
                 ops.decode_advance(b.token_ids, sampled, b.positions, b.context_lens, b.start_pos,
                                    b.slot_mapping[0], b.block_table[0], self.page_sizes[0], loop[0], loop[1])
+            else:
+                static.host_out.copy_(sampled, non_blocking=True)
             return logits, sampled
 
         # a first run outside capture, so that libraries set themselves up before it
@@ -257,6 +272,7 @@ class ModelRunner:
         ctx = max(self._ctx_hint + 1, 1)
         while True:
             static = self._static_for(R, ctx)
+            static.wait_until_reusable()
             try:
                 self.alloc.pack_decode(ids, static.B, static.MB, static.host_np[static.B:])
                 break
@@ -272,15 +288,29 @@ class ModelRunner:
                              f"{self.model.spec.max_position}")
         static.host_np[:R] = tokens
         static.host_np[R:B] = 0
-        self.last_h2d_bytes = static.upload()
+        self.last_h2d_bytes = static.host.numel() * 4
         if static.step_graph is None:
             static.step_graph = self._capture(static)
         cap = static.step_graph
-        cap.graph.replay()
+        cap.graph.replay()                                  # upload, the step, greedy tokens back to pinned memory
+        if static.in_flight is None:
+            static.in_flight = torch.cuda.Event()
+        static.in_flight.record()
         ops.launch_counter().value += cap.launches
         self.alloc.advance(ids, 1)
         self.last_greedy = cap.sampled[:R]
+        self._greedy_host = (static, R)
         return cap.logits[:R]
+
+    def greedy_tokens_host(self):
+        """The greedy tokens of the last graph-replayed decode step as a numpy
+        array (waits for the step; the graph itself copied them to pinned
+        memory), or None if the last step was not such a step."""
+        if self.last_greedy is None or self._greedy_host is None:
+            return None
+        static, R = self._greedy_host
+        static.in_flight.synchronize()
+        return static.host_out_np[:R].copy()
 
     def decode_state(self, request_ids, first_tokens, max_steps: int) -> DecodeState:
         """Prepare ``max_steps`` decode steps that run on the device without
