@@ -244,7 +244,7 @@ def test_rope_in_the_paired_row_order(nh, nkv, d, page, dtype):
         ops.rope_pair_order(24)
 
 
-@pytest.mark.parametrize("M", [1, 5, 8])
+@pytest.mark.parametrize("M", [1, 5, 8, 13, 16])
 @pytest.mark.parametrize("nh,nkv,d,K,page", [(4, 2, 64, 256, 16), (32, 8, 64, 2048, 16), (6, 3, 48, 136, 8), (40, 8, 128, 1024, 32)])
 def test_projection_with_rotation_and_cache_write_in_its_kernel(M, nh, nkv, d, K, page):
     """q|k|v projection of a few single tokens, rotated and written to the cache by the product's own kernel,
@@ -296,7 +296,7 @@ def test_projection_with_rotation_and_cache_write_in_its_kernel(M, nh, nkv, d, K
     kv = torch.zeros(NP, 2, nkv, page, d, dtype=torch.bfloat16, device=DEV)
     ops.skinny_gemm_rope_cache(x, w, table, positions, None, kv, nh, nkv, d)
     assert not kv.any()
-    assert not ops.skinny_rope_ok(torch.zeros(9, K, dtype=torch.bfloat16, device=DEV), w, d)
+    assert not ops.skinny_rope_ok(torch.zeros(ops.SKINNY_AUTO_ROWS + 1, K, dtype=torch.bfloat16, device=DEV), w, d)
     assert not ops.skinny_rope_ok(x, w, 24)
 
 
@@ -608,8 +608,8 @@ def test_skinny_fused_refusals():
     nw = torch.ones(48, device=DEV)
     assert ops.skinny_fused_ok(x, w, torch.zeros(4, 48, device=DEV))
     assert not ops.skinny_fused_ok(x, w, torch.zeros(4, 48, dtype=torch.bfloat16, device=DEV))            # residual is 32-bit
-    assert not ops.skinny_fused_ok(torch.zeros(9, 64, dtype=torch.bfloat16, device=DEV), w,
-                                   torch.zeros(9, 48, device=DEV))                                       # beyond the decode sizes
+    assert not ops.skinny_fused_ok(torch.zeros(17, 64, dtype=torch.bfloat16, device=DEV), w,
+                                   torch.zeros(17, 48, device=DEV))                                      # beyond the decode sizes
     with pytest.raises(ops.KernelError):
         ops.skinny_gemm_residual(torch.zeros(17, 64, dtype=torch.bfloat16, device=DEV), w, torch.zeros(17, 48, device=DEV),
                                  nw, 1e-5)
