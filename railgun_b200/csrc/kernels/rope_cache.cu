@@ -146,6 +146,70 @@ __global__ void rope_cache_vec2_kernel(A* __restrict__ qkv, const float* __restr
     }
 }
 
+// Eight neighbouring pairs per thread, 16-byte accesses: bfloat16 with d % 16 == 0 (both layouts: the first
+// elements of pairs 8 b .. 8 b + 7 are 8 consecutive features, and so are their partners).  One thread block per
+// token, as above; this is the kernel that long prompts go through.
+__global__ void rope_cache_vec8_kernel(bf16* __restrict__ qkv, const float* __restrict__ table,
+                                       const int* __restrict__ positions, const int* __restrict__ slots,
+                                       bf16* __restrict__ kv_cache, int nh, int nkv, int d, int page_size,
+                                       int max_pos, int* __restrict__ err, int paired8) {
+    pdl_wait();
+    pdl_trigger();
+    const int t = blockIdx.x;
+    const int half = d >> 1, groups = half >> 3;       // groups of 8 pairs per head
+    const int apart = paired8 ? 8 : half;
+    int pos = positions[t];
+    if (pos < 0 || pos >= max_pos) {
+        if (threadIdx.x == 0 && err) atomicExch(err, 1);
+        pos = 0;
+    }
+    bf16* row = qkv + (size_t)t * (nh + 2 * nkv) * d;
+    const float* cs = table ? table + (size_t)pos * d : nullptr;
+    const int slot = slots ? slots[t] : -1;
+    bf16* kdst = nullptr;
+    bf16* vdst = nullptr;
+    if (slot >= 0) {
+        const int page = slot / page_size, off = slot - page * page_size;
+        kdst = kv_cache + (((size_t)page * 2 + 0) * nkv * page_size + off) * d;
+        vdst = kv_cache + (((size_t)page * 2 + 1) * nkv * page_size + off) * d;
+    }
+    const size_t head_stride = (size_t)page_size * d;
+    for (int w = threadIdx.x; w < (nh + nkv) * groups; w += blockDim.x) {
+        const int h = w / groups, i = (w - h * groups) * 8;          // pairs i .. i + 7
+        const int e = rope_lo_index(i, paired8);
+        bf16* x = row + (size_t)h * d;
+        uint4 lo = *reinterpret_cast<const uint4*>(x + e), hi = *reinterpret_cast<const uint4*>(x + e + apart);
+        if (cs) {
+            const float4 c0 = *reinterpret_cast<const float4*>(cs + i), c1 = *reinterpret_cast<const float4*>(cs + i + 4);
+            const float4 s0 = *reinterpret_cast<const float4*>(cs + half + i), s1 = *reinterpret_cast<const float4*>(cs + half + i + 4);
+            const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+            const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+            __nv_bfloat162* l2 = reinterpret_cast<__nv_bfloat162*>(&lo);
+            __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&hi);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float2 a = __bfloat1622float2(l2[k]), b = __bfloat1622float2(h2[k]);
+                l2[k] = __floats2bfloat162_rn(a.x * c[2 * k] - b.x * sn[2 * k], a.y * c[2 * k + 1] - b.y * sn[2 * k + 1]);
+                h2[k] = __floats2bfloat162_rn(b.x * c[2 * k] + a.x * sn[2 * k], b.y * c[2 * k + 1] + a.y * sn[2 * k + 1]);
+            }
+            *reinterpret_cast<uint4*>(x + e) = lo;
+            *reinterpret_cast<uint4*>(x + e + apart) = hi;
+        }
+        if (h >= nh && kdst) {
+            bf16* kd = kdst + (size_t)(h - nh) * head_stride;
+            *reinterpret_cast<uint4*>(kd + e) = lo;
+            *reinterpret_cast<uint4*>(kd + e + apart) = hi;
+        }
+    }
+    if (vdst) {
+        const bf16* v = row + (size_t)(nh + nkv) * d;
+        for (int w = threadIdx.x; w < nkv * (d >> 3); w += blockDim.x) {
+            const int h = (w * 8) / d, i = w * 8 - h * d;
+            *reinterpret_cast<uint4*>(vdst + (size_t)h * head_stride + i) = *reinterpret_cast<const uint4*>(v + w * 8);
+        }
+    }
+}
+
 // paired8: 0 pairs (i, i + d/2) as stored by the model; 1 the reordered layout above (d % 16 == 0).
 extern "C" int rg_rope_cache(void* qkv, int dtype, const float* table, const int* positions,
                              const int* slots, void* kv_cache, int T, int nh, int nkv, int d,
@@ -154,6 +218,10 @@ extern "C" int rg_rope_cache(void* qkv, int dtype, const float* table, const int
     if (d % 2 || (paired8 && d % 16)) return RG_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = 256;
+    if (dtype == RG_DTYPE_BF16 && d % 16 == 0 && (uintptr_t)qkv % 16 == 0 && (uintptr_t)kv_cache % 16 == 0 &&
+        (uintptr_t)table % 16 == 0 && ((size_t)(nh + 2 * nkv) * d) % 8 == 0)
+        return rg_launch(rope_cache_vec8_kernel, dim3(T), dim3(threads), 0, s, 1, (bf16*)qkv, table, positions, slots,
+                         (bf16*)kv_cache, nh, nkv, d, page_size, max_pos, err, paired8);
     if (d % 4 == 0 && (uintptr_t)qkv % 8 == 0 && (uintptr_t)kv_cache % 8 == 0 && (uintptr_t)table % 8 == 0) {
         if (dtype == RG_DTYPE_BF16)
             return rg_launch(rope_cache_vec2_kernel<bf16>, dim3(T), dim3(threads), 0, s, 1, (bf16*)qkv, table, positions,
