@@ -719,6 +719,34 @@ def test_prefill_attention_tcgen05_finds_a_far_key():
         assert rel_err(out, ref) < 1e-2
 
 
+def test_prefill_attention_tcgen05_rescales_when_the_maximum_jumps():
+    """The kernel keeps a reference maximum and raises it (rescaling what it has accumulated) only when a tile's
+    weights outgrow it.  Keys that align with some queries ever more strongly make that happen several times in
+    a row's life, for some rows of a warp and not for others, in interior tiles and on the diagonal."""
+    from railgun_b200 import ops
+    nh, nkv, d, page = 2, 1, 64, 16
+    T = 300
+    c = make_paged_case(1, [T], [T], nh, nkv, d, page, torch.bfloat16, seed=77)
+    q = c["q"]                                                   # [T, nh, d]
+    for kp, strength, row in ((70, 1.5, 299), (130, 2.5, 299), (200, 3.5, 299), (290, 5.0, 299), (100, 4.0, 150),
+                              (3, 3.0, 40), (260, 4.5, 270)):
+        pg, off = c["tables"][0][kp // page], kp % page
+        c["kv"][pg, 0, 0, off, :] = (q[row, 0, :] * strength).to(torch.bfloat16)
+    ref = attention_reference(c, nh, nkv, d, page, 0, d ** -0.5)
+    wide = torch.zeros(T, (nh + 2 * nkv) * d, dtype=torch.bfloat16)
+    wide[:, :nh * d] = q.reshape(T, nh * d)
+    tiles = [(k, min(128, T - k), 0) for k in range(0, T, 128)]
+    out = torch.full((T, nh * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.prefill_attention_tc(wide.to(DEV), out, c["kv"].to(DEV), c["bt"].to(DEV),
+                             torch.tensor(tiles, dtype=torch.int32, device=DEV),
+                             torch.tensor(c["positions"], dtype=torch.int32, device=DEV), nh, nkv, d, 0, d ** -0.5)
+    ops.tc_gemm_check()
+    assert rel_err(out, ref) < 1e-2
+    # the rows that the needles were made for are dominated by their needle's value
+    v290 = c["kv"][c["tables"][0][290 // page], 1, 0, 290 % page].double()
+    assert (out[299, :d].double().cpu() - v290).abs().max() < 0.05 * v290.abs().max() + 0.05
+
+
 def test_prefill_attention_tcgen05_refuses_other_shapes():
     from railgun_b200 import ops
     q = torch.zeros(4, 3 * 128, dtype=torch.bfloat16, device=DEV)
