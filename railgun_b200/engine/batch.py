@@ -56,6 +56,8 @@ class StepBatch:
     host_state_slots: np.ndarray | None = None
     request_ids: list = field(default_factory=list)
     h2d_bytes: int = 0
+    host_buffer: torch.Tensor | None = None      # the pinned buffer the step was packed in (alive until the copy ran)
+    layout: tuple = ()               # (token counts, wanted places, block-table widths): equal layouts, equal offsets
     decode_only: bool = False        # every request brings exactly one token
     # how attention splits the step: requests with several tokens in tiles of up to 64 consecutive
     # positions, [n, 3] = first row, rows, request; requests with one token as a list of rows
@@ -68,16 +70,23 @@ class StepBatch:
 
 
 def build_step_batch(entries, alloc, page_sizes, vocab_size: int, max_position: int, device,
-                     err_flag=None) -> StepBatch:
+                     err_flag=None, into=None) -> StepBatch:
     """Validate the entries against the cache's bookkeeping, reserve pages and
     pack everything into one host buffer that goes to the device in one copy.
 
     ``alloc`` is the PageAllocator; a request it does not know yet is added.
-    Nothing is launched and nothing is reserved if any entry is invalid."""
+    Nothing is launched and nothing is reserved if any entry is invalid.
+    Block tables are as wide as the longest one rounded up to a power of two,
+    so that steps of the same token counts have the same layout.  ``into``:
+    called with the layout (token counts, wanted places, block-table widths)
+    once it is known; if it returns a device int32 buffer (of exactly the
+    layout's size) the step is copied into that buffer, whose address is what a
+    captured graph reads, and the batch's tensors are views of it."""
     if not entries:
         raise BatchError("a step needs at least one entry")
     seen = set()
     starts = []
+    token_arrays = []
     for e in entries:
         if e.request_id in seen:
             raise BatchError(f"request {e.request_id} appears twice in one step")
@@ -86,6 +95,7 @@ def build_step_batch(entries, alloc, page_sizes, vocab_size: int, max_position: 
         if n < 1:
             raise BatchError(f"request {e.request_id}: an entry needs at least one token")
         toks = np.asarray(e.tokens)
+        token_arrays.append(toks)
         if toks.min() < 0 or toks.max() >= vocab_size:
             raise BatchError(f"request {e.request_id}: token ids must be in [0, {vocab_size})")
         start = alloc.num_computed(e.request_id) if alloc.has(e.request_id) else 0
@@ -115,7 +125,7 @@ def build_step_batch(entries, alloc, page_sizes, vocab_size: int, max_position: 
     W = sum(len(e.want) for e in entries)
     G = len(page_sizes)
     tables = [[alloc.block_table(e.request_id, g) for e in entries] for g in range(G)]
-    max_blocks = [max(1, max(len(t) for t in tables[g])) for g in range(G)]
+    max_blocks = [1 << (max(1, max(len(t) for t in tables[g])) - 1).bit_length() for g in range(G)]
 
     tiles, tiles128, dec_rows = [], [], []
     off = 0
@@ -137,7 +147,7 @@ def build_step_batch(entries, alloc, page_sizes, vocab_size: int, max_position: 
     seg = lambda i: host[offs[i]:offs[i + 1]]
     cu = np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
     start_arr = np.array(starts, dtype=np.int32)
-    seg(0)[:] = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries])
+    seg(0)[:] = np.concatenate(token_arrays)
     pos = np.concatenate([np.arange(s, s + c, dtype=np.int32) for s, c in zip(starts, counts)])
     seg(1)[:] = pos
     req = np.repeat(np.arange(R, dtype=np.int32), counts)
@@ -164,7 +174,15 @@ def build_step_batch(entries, alloc, page_sizes, vocab_size: int, max_position: 
         seg(9 + 2 * G)[:] = np.asarray(dec_rows, dtype=np.int32)
     if tiles128:
         seg(10 + 2 * G)[:] = np.asarray(tiles128, dtype=np.int32).reshape(-1)
-    dev = buf.to(device, non_blocking=True)
+    layout = (tuple(int(c) for c in counts), W, tuple(max_blocks))
+    static = into(layout) if into is not None else None
+    if static is not None:
+        if static.numel() != buf.numel():
+            raise BatchError(f"the step packs {buf.numel()} ints, the buffer to copy into holds {static.numel()}")
+        static.copy_(buf, non_blocking=True)
+        dev = static
+    else:
+        dev = buf.to(device, non_blocking=True)
     d = lambda i: dev[int(offs[i]):int(offs[i + 1])]
     return StepBatch(
         num_tokens=T, num_requests=R, num_wanted=W,
@@ -174,7 +192,8 @@ def build_step_batch(entries, alloc, page_sizes, vocab_size: int, max_position: 
         slot_mapping=[d(8 + 2 * g) for g in range(G)],
         block_table=[d(9 + 2 * g).view(R, max_blocks[g]) for g in range(G)],
         err_flag=err_flag, host_cu_seqlens=cu, host_start_pos=start_arr, host_state_slots=slots,
-        request_ids=[e.request_id for e in entries], h2d_bytes=int(offs[-1]) * 4,
+        request_ids=[e.request_id for e in entries], h2d_bytes=int(offs[-1]) * 4, host_buffer=buf,
+        layout=layout,
         decode_only=bool(counts.max() == 1),
         prefill_tiles=d(8 + 2 * G).view(-1, 3) if tiles else None, num_prefill_tiles=len(tiles),
         decode_rows=d(9 + 2 * G) if dec_rows else None, num_decode_rows=len(dec_rows),

@@ -26,6 +26,12 @@ _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.
            "f32": torch.float32}
 
 
+# Steps of at least this many tokens go through a graph captured for their layout once that layout repeats
+# (below it the launches are few and short; single tokens have their own graphs), and so many layouts are kept.
+SHAPE_GRAPH_MIN_TOKENS = 256
+SHAPE_GRAPHS_KEPT = 4
+
+
 def parse_dtype(name):
     if isinstance(name, torch.dtype):
         if name not in (torch.bfloat16, torch.float32):
@@ -118,6 +124,16 @@ class StaticDecodeBatch:
         return self.host.numel() * 4
 
 
+class ShapeGraph:
+    """A captured step for one packed layout: the static device buffer the step's
+    data is copied into, the batch whose tensors are views of it, the graph and
+    its output."""
+
+    def __init__(self, dev, batch, graph, logits, launches):
+        self.dev, self.batch, self.graph, self.logits, self.launches = dev, batch, graph, logits, launches
+        self.hold = None               # the last packed step (keeps its pinned buffer alive until the copy has run)
+
+
 class CapturedStep:
     def __init__(self, graph, logits, sampled, launches):
         self.graph, self.logits, self.sampled, self.launches = graph, logits, sampled, launches
@@ -162,6 +178,9 @@ class ModelRunner:
         # that plan on the host (none of the built-in ones) switch them off
         self.use_graphs = bool(use_graphs) and not self.cache.state and len(self.page_sizes) >= 1
         self._static: dict = {}
+        self._shape_steps: dict = {}       # layout -> ShapeGraph: steps of a layout seen before replay a captured graph
+        self._shape_seen: dict = {}
+        self.shape_graph_min_tokens = SHAPE_GRAPH_MIN_TOKENS
         self._graph_pool = None
         self._ctx_hint = 0
         self.last_h2d_bytes = 0
@@ -182,13 +201,71 @@ class ModelRunner:
         if self.use_graphs and entries and all(
                 len(e.tokens) == 1 and list(e.want) == [0] and self.alloc.has(e.request_id) for e in entries):
             return self._step_decode_graph(entries)
+        if self.use_graphs and sum(len(e.tokens) for e in entries) >= self.shape_graph_min_tokens:
+            return self._step_shape_graph(entries)
         batch = build_step_batch(entries, self.alloc, self.page_sizes, self.model.vocab_size,
                                  self.model.spec.max_position, self.device, self.err_flag)
         self.last_h2d_bytes = batch.h2d_bytes
         logits = self.model.forward(batch, self.views)
+        self._commit(entries, batch)
+        return logits
+
+    def _commit(self, entries, batch) -> None:
         for e, start in zip(entries, batch.host_start_pos):
             self.alloc.commit(e.request_id, int(start) + len(e.tokens))
-        return logits
+
+    def _step_shape_graph(self, entries):
+        """Large steps (portions of prompts) whose packed layout was seen before
+        replay a CUDA graph captured for that layout: token counts, wanted places
+        and block-table widths fix every shape, everything else is data in the
+        step's one device buffer.  The first step of a layout runs eagerly, the
+        second is captured while it runs, later ones replay; a few layouts
+        (the portions a scheduler cuts are mostly of one size) are kept."""
+        build = lambda into: build_step_batch(entries, self.alloc, self.page_sizes, self.model.vocab_size,
+                                              self.model.spec.max_position, self.device, self.err_flag, into=into)
+        known = lambda layout: self._shape_steps[layout].dev if layout in self._shape_steps else None
+        batch = build(known)
+        self.last_h2d_bytes = batch.h2d_bytes
+        key = batch.layout
+        shape = self._shape_steps.get(key)
+        if shape is not None:
+            # the step was packed straight into the graph's buffer: launch
+            shape.hold = batch
+            shape.graph.replay()
+            ops.launch_counter().value += shape.launches
+            ops.mark_tc_unchecked()
+            self._commit(entries, batch)
+            return shape.logits
+        seen = self._shape_seen.get(key, 0) + 1
+        if len(self._shape_seen) > 64:
+            self._shape_seen.clear()
+        self._shape_seen[key] = seen
+        if seen < 2:
+            logits = self.model.forward(batch, self.views)
+            self._commit(entries, batch)
+            return logits
+        # the layout repeats: a static copy of the packed buffer, one eager run over it (this step), the capture
+        if len(self._shape_steps) >= SHAPE_GRAPHS_KEPT:
+            self._shape_steps.pop(next(iter(self._shape_steps)))
+        dev = torch.empty(batch.host_buffer.numel(), dtype=torch.int32, device=self.device)
+        batch = build(lambda layout: dev)
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            eager = self.model.forward(batch, self.views)
+            eager = eager.clone() if eager is not None else None
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        counter = ops.launch_counter()
+        n0 = counter.value
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            logits = self.model.forward(batch, self.views)
+        launches = counter.value - n0
+        counter.value = n0
+        self._shape_steps[key] = ShapeGraph(dev, batch, graph, logits, launches)
+        self._commit(entries, batch)
+        return eager
 
     def end(self, request_ids) -> None:
         """The requests are finished: their pages and slots come back."""

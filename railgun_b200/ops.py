@@ -43,7 +43,13 @@ def _ptr(t) -> c_void_p:
     return c_void_p(0 if t is None else t.data_ptr())
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> c_void_p:
+    """The current CUDA stream of the current device (what torch.cuda.stream and graph capture set)."""
+    if _raw_stream is not None:
+        return c_void_p(_raw_stream(torch.cuda.current_device()))
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
@@ -551,6 +557,12 @@ def tc_gemm(x: torch.Tensor, weight: torch.Tensor, out_dtype=None, silu_mul: boo
 
 
 _tc_unchecked = False
+
+
+def mark_tc_unchecked() -> None:
+    """A replayed graph may have run tcgen05 kernels: the next ``tc_gemm_check`` looks at their error flag."""
+    global _tc_unchecked
+    _tc_unchecked = True
 
 
 def prefill_attention_tc_ok(q, kv_cache, d: int, page_size: int) -> bool:

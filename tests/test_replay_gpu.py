@@ -83,6 +83,54 @@ def test_replay_matches_plain(name, dtype, mode, tmp_path):
     print(f"tiny {name} {dtype} {mode}: worst relative error {worst:.3e}")
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_steps_of_a_repeated_layout_replay_a_graph(name, dtype, tmp_path):
+    """Large steps whose packed layout repeats are captured the second time and replayed from then on.  With
+    the threshold lowered to two tokens, equal portions of several requests (alone, and beside single tokens of
+    another request) go through the eager run, the capture and the replays, over pages that are used again; every
+    logit is compared with the plain implementation."""
+    from railgun_b200.engine.runner import ModelRunner
+    from railgun_b200.replay import Replayer
+    cfg, _, page = helpers.TINY[name]
+    reqs, logits = oracle(name)
+    names = [k for k, v in reqs.items() if len(v) >= 63][:4]
+    decoder = next(k for k, v in reqs.items() if len(v) >= 40 and k not in names)
+    steps, n = [], 0
+    # the decoder's prompt but for its last 12 tokens, then it decodes beside the others' portions
+    dt = reqs[decoder]
+    steps.append({"step": n, "entries": [{"id": decoder, "tokens": dt[:len(dt) - 12], "want": list(range(len(dt) - 12))}],
+                  "end": []})
+    n += 1
+    fed = len(dt) - 12
+    for r in names:
+        toks = reqs[r][:63]                                      # three portions of 21 tokens: the same layout 12 times
+        for p in range(3):
+            entries = [{"id": r, "tokens": toks[21 * p:21 * p + 21], "want": list(range(21))}]
+            if fed < len(dt):
+                entries.append({"id": decoder, "tokens": [dt[fed]], "want": [0]})
+                fed += 1
+            steps.append({"step": n, "entries": entries, "end": [r] if p == 2 else []})
+            n += 1
+    steps[-1]["end"].append(decoder)
+    runner = ModelRunner(helpers.model_dir(name), dtype=dtype, page_size=page,
+                         max_tokens=helpers.peak_tokens(steps, 64), max_requests=4)
+    runner.shape_graph_min_tokens = 2
+    rp = Replayer(runner, tmp_path)
+    for s in steps:
+        rp.feed(s)
+    assert len(runner._shape_steps) >= 1                          # something was captured ...
+    assert any(v >= 2 for v in runner._shape_seen.values())
+    runner.check_device_errors()
+    runner.alloc.check()
+    rows = helpers.collect(steps, tmp_path, cfg["vocab_size"])
+    some = {r: reqs[r][:63] for r in names}
+    some[decoder] = dt
+    ref = {r: logits[r][:len(t)] for r, t in some.items()}
+    # rows of a prefix do not depend on what follows it, so the prefix's reference rows are the request's own
+    compare(rows, some, ref, dtype, f"repeated layouts {name} {dtype}")
+
+
 def test_pages_are_used_again(tmp_path):
     """The mixed trace needs more pages over its life than the pool has."""
     from railgun_b200.engine.runner import ModelRunner
