@@ -74,6 +74,10 @@ def _lib():
         lib.rg_cache_free_pages.argtypes = [c_void_p, c_int]
         lib.rg_cache_pack_decode.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
         lib.rg_cache_advance.argtypes = [c_void_p, c_void_p, c_int, c_int]
+        lib.rg_cache_plan_step.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p,
+                                           c_void_p, c_void_p, c_void_p]
+        lib.rg_cache_fill_step.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                           c_void_p, c_int, c_void_p, c_void_p]
         for name in ("free_slots", "num_requests", "check"):
             getattr(lib, f"rg_cache_{name}").argtypes = [c_void_p]
         lib.rg_sched_create.restype = c_void_p
@@ -188,6 +192,31 @@ class PageAllocator:
         code = self._lib.rg_cache_pack_decode(self._h, ids.ctypes.data, ids.size, B, MB, out.ctypes.data)
         if code:
             self._raise(code, "pack_decode")
+
+    def plan_step(self, ids: np.ndarray, counts: np.ndarray, want: np.ndarray, want_offsets: np.ndarray,
+                  max_position: int):
+        """Check a step of any shape (``ids`` int64, the others int32), add the requests that are new and
+        reserve pages for all.  Returns (status, entry, value, starts, max_blocks): status 0, or a
+        negative code about entry ``entry`` (-7: beyond ``max_position``; -8: wanted place ``value``
+        is outside the entry's tokens; others as ``_STATUS``), with nothing added that was not there."""
+        R = ids.size
+        starts = np.empty(R, dtype=np.int32)
+        max_blocks = np.empty(len(self.page_sizes), dtype=np.int32)
+        bad = np.zeros(2, dtype=np.int32)
+        code = self._lib.rg_cache_plan_step(self._h, ids.ctypes.data, counts.ctypes.data, R, want.ctypes.data,
+                                            want_offsets.ctypes.data, int(max_position), starts.ctypes.data,
+                                            max_blocks.ctypes.data, bad.ctypes.data, bad[1:].ctypes.data)
+        return code, int(bad[0]), int(bad[1]), starts, max_blocks
+
+    def fill_step(self, ids, counts, starts, tokens, want, want_offsets, max_blocks, tile_rows: int,
+                  segments: np.ndarray, out_ptr: int) -> None:
+        """Write a planned step into its packed buffer (layout in csrc/host/runtime.cpp,
+        rg_cache_fill_step); ``tokens`` int64, ``segments`` int64 offsets of the buffer's parts."""
+        code = self._lib.rg_cache_fill_step(self._h, ids.ctypes.data, counts.ctypes.data, starts.ctypes.data, ids.size,
+                                            tokens.ctypes.data, want.ctypes.data, want_offsets.ctypes.data,
+                                            max_blocks.ctypes.data, int(tile_rows), segments.ctypes.data, out_ptr)
+        if code:
+            self._raise(code, "fill_step")
 
     def advance(self, ids: np.ndarray, n: int = 1) -> None:
         code = self._lib.rg_cache_advance(self._h, ids.ctypes.data, ids.size, n)

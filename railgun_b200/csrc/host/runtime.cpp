@@ -2,6 +2,8 @@
 // from Python through ctypes.  Handles are opaque pointers; every function
 // returns a status or a count, never throws across the boundary.
 #include <cstring>
+#include <unordered_map>
+#include <vector>
 
 #include "cache_manager.hpp"
 #include "scheduler.hpp"
@@ -86,6 +88,128 @@ int rg_cache_pack_decode(void* h, const long long* ids, int R, int B, int MB, in
                 for (size_t i = 0; i < t.size(); ++i) row[i] = t[i] < 0 ? 0 : t[i];
                 slot_map[g * B + b] = t[pos / ps] * ps + pos % ps;
             }
+        }
+        return CACHE_OK;
+    } catch (...) { return CACHE_CORRUPT; }
+}
+// Plans a step of any shape: request b brings counts[b] >= 1 next tokens and asks for the logits at the places
+// want[want_offsets[b] .. want_offsets[b+1]) among them.  Everything is checked before anything is reserved; then
+// unknown requests are added and pages reserved for every request (a request added here is released again if a
+// reservation fails).  Writes every request's start position and, per group, the width of the widest block table
+// rounded up to a power of two.  Returns CACHE_OK, or a status with *bad = the entry it is about:
+// CACHE_DUPLICATE (a request twice in one step), CACHE_BAD_ARGUMENT (no tokens), STEP_BEYOND_MAX_POSITION,
+// STEP_BAD_WANT (a wanted place outside the entry's tokens; *bad_value = the place), or a reservation's status.
+enum StepStatus : int { STEP_BEYOND_MAX_POSITION = -7, STEP_BAD_WANT = -8 };
+
+int rg_cache_plan_step(void* h, const long long* ids, const int* counts, int R, const int* want,
+                       const int* want_offsets, int max_position, int* starts, int* max_blocks, int* bad,
+                       int* bad_value) {
+    try {
+        CacheManager* c = (CacheManager*)h;
+        const int G = c->num_groups();
+        std::unordered_map<long long, int> seen;
+        seen.reserve((size_t)R * 2);
+        for (int b = 0; b < R; ++b) {
+            *bad = b;
+            if (!seen.emplace(ids[b], b).second) return CACHE_DUPLICATE;
+            if (counts[b] < 1) return CACHE_BAD_ARGUMENT;
+            const CacheRequest* r = c->find(ids[b]);
+            starts[b] = r ? r->num_computed : 0;
+            if ((long long)starts[b] + counts[b] > max_position) return STEP_BEYOND_MAX_POSITION;
+            for (int w = want_offsets[b]; w < want_offsets[b + 1]; ++w)
+                if (want[w] < 0 || want[w] >= counts[b]) { *bad_value = want[w]; return STEP_BAD_WANT; }
+        }
+        std::vector<long long> added;
+        int status = CACHE_OK;
+        for (int b = 0; b < R && status == CACHE_OK; ++b) {
+            *bad = b;
+            if (!c->has(ids[b])) {
+                const int slot = c->add_request(ids[b]);
+                if (slot < 0) { status = slot; break; }
+                added.push_back(ids[b]);
+            }
+            status = c->reserve(ids[b], starts[b] + counts[b]);
+        }
+        if (status != CACHE_OK) {
+            for (long long id : added) c->release(id);
+            return status;
+        }
+        for (int g = 0; g < G; ++g) {
+            size_t widest = 1;
+            for (int b = 0; b < R; ++b) {
+                const size_t n = c->find(ids[b])->tables[g].size();
+                if (n > widest) widest = n;
+            }
+            int p2 = 1;
+            while ((size_t)p2 < widest) p2 <<= 1;
+            max_blocks[g] = p2;
+        }
+        return CACHE_OK;
+    } catch (...) { return CACHE_CORRUPT; }
+}
+
+// Writes a planned step into its packed buffer.  seg[i] is the offset (in ints) of segment i of `out`:
+//   0 token ids [T] | 1 positions [T] | 2 request of token [T] | 3 wanted rows [W] | 4 cu_seqlens [R+1] |
+//   5 context lens [R] | 6 start positions [R] | 7 state slots [R] | per group g: 8+2g cache slot of each token [T],
+//   9+2g block table [R, max_blocks[g]] (released pages as 0: they are never read) |
+//   8+2G tiles of <= tile_rows consecutive rows of requests with several tokens, (first row, rows, request) |
+//   9+2G rows of requests with one token | 10+2G the same tiles with <= 2 * tile_rows rows.
+int rg_cache_fill_step(void* h, const long long* ids, const int* counts, const int* starts, int R,
+                       const long long* tokens, const int* want, const int* want_offsets, const int* max_blocks,
+                       int tile_rows, const long long* seg, int* out) {
+    try {
+        CacheManager* c = (CacheManager*)h;
+        const int G = c->num_groups();
+        int* tok = out + seg[0];
+        int* pos = out + seg[1];
+        int* req = out + seg[2];
+        int* want_rows = out + seg[3];
+        int* cu = out + seg[4];
+        int* ctx = out + seg[5];
+        int* start = out + seg[6];
+        int* slots = out + seg[7];
+        int* tiles = out + seg[8 + 2 * G];
+        int* dec = out + seg[9 + 2 * G];
+        int* tiles2 = out + seg[10 + 2 * G];
+        int off = 0, nw = 0;
+        cu[0] = 0;
+        for (int b = 0; b < R; ++b) {
+            const CacheRequest* r = c->find(ids[b]);
+            if (!r) return CACHE_UNKNOWN_REQUEST;
+            const int n = counts[b], s = starts[b];
+            for (int k = 0; k < n; ++k) {
+                tok[off + k] = (int)tokens[off + k];
+                pos[off + k] = s + k;
+                req[off + k] = b;
+            }
+            for (int w = want_offsets[b]; w < want_offsets[b + 1]; ++w) want_rows[nw++] = off + want[w];
+            cu[b + 1] = off + n;
+            ctx[b] = s + n;
+            start[b] = s;
+            slots[b] = r->slot;
+            for (int g = 0; g < G; ++g) {
+                const std::vector<int>& t = r->tables[g];
+                const int ps = c->group(g).page_size, MB = max_blocks[g];
+                if ((int)t.size() > MB || (size_t)(s + n - 1) / ps >= t.size()) return CACHE_BAD_ARGUMENT;
+                int* row = out + seg[9 + 2 * g] + (size_t)b * MB;
+                for (int i = 0; i < MB; ++i) row[i] = i < (int)t.size() && t[i] > 0 ? t[i] : 0;
+                int* sm = out + seg[8 + 2 * g] + off;
+                for (int k = 0; k < n; ++k) {
+                    const int p = s + k;
+                    sm[k] = row[p / ps] * ps + p % ps;
+                }
+            }
+            if (n == 1) {
+                *dec++ = off;
+            } else {
+                for (int k = 0; k < n; k += tile_rows) {
+                    *tiles++ = off + k; *tiles++ = n - k < tile_rows ? n - k : tile_rows; *tiles++ = b;
+                }
+                for (int k = 0; k < n; k += 2 * tile_rows) {
+                    *tiles2++ = off + k; *tiles2++ = n - k < 2 * tile_rows ? n - k : 2 * tile_rows; *tiles2++ = b;
+                }
+            }
+            off += n;
         }
         return CACHE_OK;
     } catch (...) { return CACHE_CORRUPT; }

@@ -134,8 +134,9 @@ prefill_attention_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
 
     pdl_wait();
     pdl_trigger();
-    // later tiles of a prompt attend more keys: they are started first so that the short ones fill the tail
-    const int tile = gridDim.x - 1 - blockIdx.x, h = blockIdx.y;
+    // later tiles of a prompt attend more keys: blocks are handed out in index order, so every head's
+    // last tile starts first and the short ones fill the tail
+    const int tile = gridDim.x / nh - 1 - blockIdx.x / nh, h = blockIdx.x % nh;
     const int row0 = tiles[tile * 3 + 0], nrows = tiles[tile * 3 + 1], r = tiles[tile * 3 + 2];
     const int kvh = h / (nh / nkv);
     const int* bt = block_table + (size_t)r * max_blocks;
@@ -654,13 +655,13 @@ extern "C" int rg_prefill_attention(const void* q, int q_stride, void* out, cons
                                     const int* positions, int nh, int nkv, int d, int page_size, int window,
                                     float scale, void* stream) {
     if (n_tiles <= 0) return 0;
-    if (d % 16 || d < 16 || d > 256 || nh % nkv || nh > 65535) return RG_ERR_UNSUPPORTED;
+    if (d % 16 || d < 16 || d > 256 || nh % nkv || (long long)n_tiles * nh > 0x7fffffffll) return RG_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     const float scale_log2 = scale * 1.4426950408889634f;
     const size_t smem = prefill_smem(d);
     int page_shift = -1;                                            // log2 of the page size when it is a power of two
     for (int b = 0; b < 31; ++b) if (page_size == (1 << b)) page_shift = b;
-    dim3 grid(n_tiles, nh);
+    dim3 grid(n_tiles * nh);
 #define RG_PREFILL(DM, EX) { int e = allow_smem(prefill_attention_kernel<DM, EX>, smem); if (e) return e; \
     return rg_launch(prefill_attention_kernel<DM, EX>, grid, dim3(NTHREADS), smem, s, 1, (const bf16*)q, q_stride, \
         (bf16*)out, (const bf16*)kv_cache, block_table, max_blocks, tiles, positions, nh, nkv, d, page_size, page_shift, \

@@ -73,8 +73,9 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ 
     __shared__ int abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // later tiles of a prompt attend more keys: start them first
-    const int tile = gridDim.x - 1 - blockIdx.x, h = blockIdx.y;
+    // later tiles of a prompt attend more keys: blocks are handed out in index order, so every head's
+    // last tile starts first and the shortest tiles fill the gaps at the end
+    const int tile = gridDim.x / nh - 1 - blockIdx.x / nh, h = blockIdx.x % nh;
     const int row0 = tiles[tile * 3 + 0], nrows = tiles[tile * 3 + 1], r = tiles[tile * 3 + 2];
     const int kvh = h / (nh / nkv);
     const int* bt = block_table + (size_t)r * max_blocks;
@@ -355,7 +356,7 @@ extern "C" int rg_prefill_attention_tc(const void* q, int q_stride, int n_rows_t
                                        int window, float scale, int* err, void* stream) {
     if (n_tiles <= 0) return 0;
     if (d != FA_D || nh % nkv || page_size % 8 || page_size > 128 || 128 % page_size || q_stride % 8 ||
-        ((uintptr_t)q & 15) || ((uintptr_t)kv_cache & 15) || nh > 65535)
+        ((uintptr_t)q & 15) || ((uintptr_t)kv_cache & 15) || (long long)n_tiles * nh > 0x7fffffffll)
         return RG_ERR_UNSUPPORTED;
     CUtensorMap qm, kvm;
     int e = rg_make_map(&qm, q, (unsigned long long)n_rows_total, (unsigned long long)q_stride, (unsigned long long)q_stride, FA_BM);
@@ -365,7 +366,7 @@ extern "C" int rg_prefill_attention_tc(const void* q, int q_stride, int n_rows_t
     if (e) return e;
     cudaError_t ce = cudaFuncSetAttribute(fa_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FA_SMEM_BYTES);
     if (ce != cudaSuccess) return (int)ce;
-    return rg_launch(fa_tc_kernel, dim3(n_tiles, nh), dim3(FA_THREADS), FA_SMEM_BYTES, (cudaStream_t)stream, 1, qm, kvm,
+    return rg_launch(fa_tc_kernel, dim3(n_tiles * nh), dim3(FA_THREADS), FA_SMEM_BYTES, (cudaStream_t)stream, 1, qm, kvm,
                      (bf16*)out, block_table, max_blocks, tiles, positions, nh, nkv, page_size, window,
                      scale * 1.4426950408889634f, err);
 }

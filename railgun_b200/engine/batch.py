@@ -11,7 +11,9 @@ positions that let one attention call serve every cut of the work.
 """
 from __future__ import annotations
 
+import array
 from dataclasses import dataclass, field
+from itertools import accumulate, chain
 
 import numpy as np
 import torch
@@ -22,6 +24,28 @@ ATTENTION_TILE_ROWS = 64      # query rows per tile of the prefill attention ker
 
 class BatchError(ValueError):
     """A step that cannot run: bad token ids, positions or requests."""
+
+
+_PINNED = None
+
+
+def _pinned() -> bool:
+    """Whether host buffers are page-locked (asked once: the answer costs 20 us each time)."""
+    global _PINNED
+    if _PINNED is None:
+        _PINNED = torch.cuda.is_available()
+    return _PINNED
+
+
+def _token_array(tokens) -> np.ndarray:
+    """A request's tokens as an integer array; a list of Python ints goes through ``array``, which
+    converts several times faster than numpy's type discovery."""
+    if isinstance(tokens, np.ndarray):
+        return tokens
+    try:
+        return np.frombuffer(array.array("q", tokens), dtype=np.int64)
+    except (TypeError, OverflowError):
+        return np.asarray(tokens)
 
 
 @dataclass
@@ -84,97 +108,53 @@ def build_step_batch(entries, alloc, page_sizes, vocab_size: int, max_position: 
     captured graph reads, and the batch's tensors are views of it."""
     if not entries:
         raise BatchError("a step needs at least one entry")
-    seen = set()
-    starts = []
-    token_arrays = []
-    for e in entries:
-        if e.request_id in seen:
-            raise BatchError(f"request {e.request_id} appears twice in one step")
-        seen.add(e.request_id)
-        n = len(e.tokens)
-        if n < 1:
-            raise BatchError(f"request {e.request_id}: an entry needs at least one token")
-        toks = np.asarray(e.tokens)
-        token_arrays.append(toks)
-        if toks.min() < 0 or toks.max() >= vocab_size:
-            raise BatchError(f"request {e.request_id}: token ids must be in [0, {vocab_size})")
-        start = alloc.num_computed(e.request_id) if alloc.has(e.request_id) else 0
-        if start + n > max_position:
-            raise BatchError(f"request {e.request_id}: position {start + n - 1} is beyond the model's "
-                             f"max_position_embeddings {max_position}")
-        for w in e.want:
-            if not 0 <= w < n:
-                raise BatchError(f"request {e.request_id}: wanted place {w} is outside its {n} tokens")
-        starts.append(start)
-    # reserve (atomic per request; on failure give back what this call added)
-    added = []
-    try:
-        for e, start in zip(entries, starts):
-            if not alloc.has(e.request_id):
-                alloc.add_request(e.request_id)
-                added.append(e.request_id)
-            alloc.reserve(e.request_id, start + len(e.tokens))
-    except Exception:
-        for rid in added:
-            alloc.release(rid)
-        raise
-
     R = len(entries)
-    counts = np.array([len(e.tokens) for e in entries], dtype=np.int64)
-    T = int(counts.sum())
-    W = sum(len(e.want) for e in entries)
     G = len(page_sizes)
-    tables = [[alloc.block_table(e.request_id, g) for e in entries] for g in range(G)]
-    max_blocks = [1 << (max(1, max(len(t) for t in tables[g])) - 1).bit_length() for g in range(G)]
-
-    tiles, tiles128, dec_rows = [], [], []
-    off = 0
-    for i, c in enumerate(counts):
-        c = int(c)
-        if c == 1:
-            dec_rows.append(off)
-        else:
-            tiles += [(off + k, min(ATTENTION_TILE_ROWS, c - k), i) for k in range(0, c, ATTENTION_TILE_ROWS)]
-            tiles128 += [(off + k, min(128, c - k), i) for k in range(0, c, 128)]
-        off += c
+    token_arrays = [_token_array(e.tokens) for e in entries]
+    for e, toks in zip(entries, token_arrays):
+        if toks.size < 1:
+            raise BatchError(f"request {e.request_id}: an entry needs at least one token")
+        if toks.dtype.kind not in "iu" or toks.min() < 0 or toks.max() >= vocab_size:
+            raise BatchError(f"request {e.request_id}: token ids must be in [0, {vocab_size})")
+    ids = np.fromiter((e.request_id for e in entries), dtype=np.int64, count=R)
+    counts = np.fromiter((t.size for t in token_arrays), dtype=np.int32, count=R)
+    want_offsets = np.zeros(R + 1, dtype=np.int32)
+    np.cumsum([len(e.want) for e in entries], out=want_offsets[1:])
+    W = int(want_offsets[-1])
+    want = np.fromiter(chain.from_iterable(e.want for e in entries), dtype=np.int32, count=W)
+    # checked, then reserved (all or nothing new) by the cache manager
+    code, bad, value, starts, max_blocks = alloc.plan_step(ids, counts, want, want_offsets, max_position)
+    if code:
+        rid, n = entries[bad].request_id, int(counts[bad])
+        if code == -2:
+            raise BatchError(f"request {rid} appears twice in one step")
+        if code == -7:
+            raise BatchError(f"request {rid}: position {int(starts[bad]) + n - 1} is beyond the model's "
+                             f"max_position_embeddings {max_position}")
+        if code == -8:
+            raise BatchError(f"request {rid}: wanted place {value} is outside its {n} tokens")
+        alloc._raise(code, f"reserve({rid}, {int(starts[bad]) + n})")
+    T = int(counts.sum())
+    several = counts[counts > 1]
+    n_tiles = int((-(-several // ATTENTION_TILE_ROWS)).sum())
+    n_tiles128 = int((-(-several // (2 * ATTENTION_TILE_ROWS))).sum())
+    n_dec = R - several.size
+    max_blocks_t = tuple(int(m) for m in max_blocks)
     sizes = [T, T, T, W, R + 1, R, R, R]
     for g in range(G):
-        sizes += [T, R * max_blocks[g]]
-    sizes += [3 * len(tiles), len(dec_rows), 3 * len(tiles128)]
-    offs = np.concatenate([[0], np.cumsum(sizes)])
-    buf = torch.empty(int(offs[-1]), dtype=torch.int32, pin_memory=torch.cuda.is_available())
+        sizes += [T, R * max_blocks_t[g]]
+    sizes += [3 * n_tiles, n_dec, 3 * n_tiles128]
+    offs = [0, *accumulate(sizes)]
+    buf = torch.empty(offs[-1], dtype=torch.int32, pin_memory=_pinned())
+    tokens = token_arrays[0] if R == 1 else np.concatenate(token_arrays)
+    if tokens.dtype != np.int64:
+        tokens = tokens.astype(np.int64)
+    alloc.fill_step(ids, counts, starts, np.ascontiguousarray(tokens), want, want_offsets, max_blocks,
+                    ATTENTION_TILE_ROWS, np.asarray(offs, dtype=np.int64), buf.data_ptr())
     host = buf.numpy()
-    seg = lambda i: host[offs[i]:offs[i + 1]]
-    cu = np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
-    start_arr = np.array(starts, dtype=np.int32)
-    seg(0)[:] = np.concatenate(token_arrays)
-    pos = np.concatenate([np.arange(s, s + c, dtype=np.int32) for s, c in zip(starts, counts)])
-    seg(1)[:] = pos
-    req = np.repeat(np.arange(R, dtype=np.int32), counts)
-    seg(2)[:] = req
-    if W:
-        seg(3)[:] = np.concatenate([cu[i] + np.asarray(e.want, dtype=np.int32)
-                                    for i, e in enumerate(entries) if len(e.want)])
-    seg(4)[:] = cu
-    seg(5)[:] = start_arr + counts.astype(np.int32)
-    seg(6)[:] = start_arr
-    slots = np.array([alloc.slot(e.request_id) for e in entries], dtype=np.int32)
-    seg(7)[:] = slots
-    for g in range(G):
-        ps = page_sizes[g]
-        bt = np.zeros((R, max_blocks[g]), dtype=np.int32)
-        for i, t in enumerate(tables[g]):
-            bt[i, :len(t)] = np.maximum(t, 0)          # released pages are never read
-        page_of = bt[req, pos // ps]
-        seg(8 + 2 * g)[:] = page_of * ps + pos % ps
-        seg(9 + 2 * g)[:] = bt.reshape(-1)
-    if tiles:
-        seg(8 + 2 * G)[:] = np.asarray(tiles, dtype=np.int32).reshape(-1)
-    if dec_rows:
-        seg(9 + 2 * G)[:] = np.asarray(dec_rows, dtype=np.int32)
-    if tiles128:
-        seg(10 + 2 * G)[:] = np.asarray(tiles128, dtype=np.int32).reshape(-1)
-    layout = (tuple(int(c) for c in counts), W, tuple(max_blocks))
+    cu = host[offs[4]:offs[5]].copy()
+    slots = host[offs[7]:offs[8]].copy()
+    layout = (tuple(counts.tolist()), W, max_blocks_t)
     static = into(layout) if into is not None else None
     if static is not None:
         if static.numel() != buf.numel():
@@ -183,19 +163,19 @@ def build_step_batch(entries, alloc, page_sizes, vocab_size: int, max_position: 
         dev = static
     else:
         dev = buf.to(device, non_blocking=True)
-    d = lambda i: dev[int(offs[i]):int(offs[i + 1])]
+    d = dev.split(sizes).__getitem__                       # views, cut in one call
     return StepBatch(
         num_tokens=T, num_requests=R, num_wanted=W,
-        max_query_len=int(counts.max()), max_context_len=int((start_arr + counts).max()),
+        max_query_len=int(counts.max()), max_context_len=int((starts + counts).max()),
         token_ids=d(0), positions=d(1), req_of_token=d(2), want_rows=d(3), cu_seqlens=d(4),
         context_lens=d(5), start_pos=d(6), state_slots=d(7),
         slot_mapping=[d(8 + 2 * g) for g in range(G)],
-        block_table=[d(9 + 2 * g).view(R, max_blocks[g]) for g in range(G)],
-        err_flag=err_flag, host_cu_seqlens=cu, host_start_pos=start_arr, host_state_slots=slots,
-        request_ids=[e.request_id for e in entries], h2d_bytes=int(offs[-1]) * 4, host_buffer=buf,
+        block_table=[d(9 + 2 * g).view(R, max_blocks_t[g]) for g in range(G)],
+        err_flag=err_flag, host_cu_seqlens=cu, host_start_pos=starts, host_state_slots=slots,
+        request_ids=[e.request_id for e in entries], h2d_bytes=offs[-1] * 4, host_buffer=buf,
         layout=layout,
         decode_only=bool(counts.max() == 1),
-        prefill_tiles=d(8 + 2 * G).view(-1, 3) if tiles else None, num_prefill_tiles=len(tiles),
-        decode_rows=d(9 + 2 * G) if dec_rows else None, num_decode_rows=len(dec_rows),
-        prefill_tiles128=d(10 + 2 * G).view(-1, 3) if tiles128 else None, num_prefill_tiles128=len(tiles128),
+        prefill_tiles=d(8 + 2 * G).view(-1, 3) if n_tiles else None, num_prefill_tiles=n_tiles,
+        decode_rows=d(9 + 2 * G) if n_dec else None, num_decode_rows=n_dec,
+        prefill_tiles128=d(10 + 2 * G).view(-1, 3) if n_tiles128 else None, num_prefill_tiles128=n_tiles128,
     )
