@@ -72,7 +72,7 @@ def _lib():
         lib.rg_cache_can_reserve.argtypes = [c_void_p, c_longlong, c_int, c_int]
         lib.rg_cache_table.argtypes = [c_void_p, c_longlong, c_int, c_void_p, c_int]
         lib.rg_cache_free_pages.argtypes = [c_void_p, c_int]
-        lib.rg_cache_pack_decode.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+        lib.rg_cache_pack_decode.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int]
         lib.rg_cache_advance.argtypes = [c_void_p, c_void_p, c_int, c_int]
         lib.rg_cache_plan_step.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p,
                                            c_void_p, c_void_p, c_void_p]
@@ -97,7 +97,7 @@ def _lib():
         lib.rg_sched_error.argtypes = [c_void_p, c_longlong, c_void_p, c_int]
         lib.rg_sched_forget.argtypes = [c_void_p, c_longlong]
         lib.rg_sched_forget.restype = None
-        for name in ("num_waiting", "num_running"):
+        for name in ("num_waiting", "num_running", "next_step_predictable"):
             getattr(lib, f"rg_sched_{name}").argtypes = [c_void_p]
         lib._rg_typed = True
     return lib
@@ -185,11 +185,13 @@ class PageAllocator:
             n = self._lib.rg_cache_table(self._h, req_id, group, self._buf.ctypes.data, self._buf.size)
         return self._buf[:n].copy()
 
-    def pack_decode(self, ids: np.ndarray, B: int, MB: int, out: np.ndarray) -> None:
+    def pack_decode(self, ids: np.ndarray, B: int, MB: int, out: np.ndarray, ahead: int = 0) -> None:
         """Reserve one more token for each request in ``ids`` (int64) and write
         the decode step's positions, slots and block tables into ``out``
-        (int32; layout in csrc/host/runtime.cpp, rg_cache_pack_decode)."""
-        code = self._lib.rg_cache_pack_decode(self._h, ids.ctypes.data, ids.size, B, MB, out.ctypes.data)
+        (int32; layout in csrc/host/runtime.cpp, rg_cache_pack_decode).
+        ``ahead`` = 1 packs the step after a step that is launched but not yet
+        committed."""
+        code = self._lib.rg_cache_pack_decode(self._h, ids.ctypes.data, ids.size, B, MB, out.ctypes.data, int(ahead))
         if code:
             self._raise(code, "pack_decode")
 

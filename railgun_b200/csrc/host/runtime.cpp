@@ -52,11 +52,13 @@ int rg_cache_table(void* h, long long id, int group, int* out, int cap) {
 // batch of `B` rows and block tables `MB` wide:
 //   positions[B] | context_lens[B] | start_pos[B] | state_slots[B] | per group: slots[B] | per group: table[B*MB]
 // Rows R..B-1 are padding: position 0, context 1, slot -1 (nothing is written), table of zeros.
-// Pages for the new token are reserved here.  Returns 0, or a negative status (nothing half-reserved matters:
-// a failed request keeps what it had).
-int rg_cache_pack_decode(void* h, const long long* ids, int R, int B, int MB, int* out) {
+// Pages for the new token are reserved here.  `ahead` > 0 packs the step that many steps after the next one (for a
+// step launched before the one before it has been committed): its position is num_computed + ahead.  Returns 0, or
+// a negative status (nothing half-reserved matters: a failed request keeps what it had).
+int rg_cache_pack_decode(void* h, const long long* ids, int R, int B, int MB, int* out, int ahead) {
     try {
         CacheManager* c = (CacheManager*)h;
+        if (ahead < 0) return CACHE_BAD_ARGUMENT;
         const int G = c->num_groups();
         int* positions = out;
         int* context = out + B;
@@ -72,7 +74,7 @@ int rg_cache_pack_decode(void* h, const long long* ids, int R, int B, int MB, in
         for (int b = 0; b < R; ++b) {
             const CacheRequest* r = c->find(ids[b]);
             if (!r) return CACHE_UNKNOWN_REQUEST;
-            const int pos = r->num_computed;
+            const int pos = r->num_computed + ahead;
             const int st = c->reserve(ids[b], pos + 1);
             if (st != CACHE_OK) return st;
             r = c->find(ids[b]);
@@ -323,6 +325,7 @@ int rg_sched_error(void* h, long long id, char* out, int cap) {
     return (int)e.size();
 }
 void rg_sched_forget(void* h, long long id) { ((Scheduler*)h)->forget(id); }
+int rg_sched_next_step_predictable(void* h) { RG_GUARD(return ((Scheduler*)h)->next_step_predictable() ? 1 : 0) }
 int rg_sched_num_waiting(void* h) { return ((Scheduler*)h)->num_waiting(); }
 int rg_sched_num_running(void* h) { return ((Scheduler*)h)->num_running(); }
 

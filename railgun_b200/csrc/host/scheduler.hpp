@@ -188,6 +188,20 @@ public:
         return finished;
     }
 
+    // Whether the step after the one just decided is known before this one's tokens are: every entry decodes one
+    // token of a request that this step's token cannot end by length, nothing waits for admission, and nothing was
+    // preempted.  (A stop token may still end a request; the caller checks its guess against the next decision.)
+    bool next_step_predictable() const {
+        if (entries_.empty() || !waiting_.empty() || !preempted_.empty()) return false;
+        if (entries_.size() != running_.size()) return false;
+        for (const StepEntry& e : entries_) {
+            if (e.count != 1 || !e.want_last) return false;
+            const SchedRequest& r = all_.at(e.id);
+            if (r.num_generated() + 1 >= r.max_new_tokens) return false;
+        }
+        return true;
+    }
+
     int abort(int64_t id) {
         auto it = all_.find(id);
         if (it == all_.end()) return SCHED_UNKNOWN;

@@ -34,6 +34,9 @@ class Engine:
         self._params: dict = {}
         self._next_id = 1
         self.steps_run = 0
+        self.run_ahead = True          # launch the next decode step before this one's tokens are on the host
+        self._ahead = None             # the step launched that way, if any (runner.FollowStep)
+        self.steps_ahead = 0           # how many steps were taken from a launch made ahead
 
     # ---- low level --------------------------------------------------------------------------
     def add_request(self, prompt_ids, params: SamplingParams | None = None) -> int:
@@ -50,13 +53,30 @@ class Engine:
 
     def step(self) -> list:
         """One scheduler decision and one model step.  Returns the (request id,
-        sampled token) pairs of this step, or None if nothing could be scheduled."""
+        sampled token) pairs of this step, or None if nothing could be scheduled.
+
+        While every running request decodes greedily and nothing waits, the
+        step after this one is launched before this one's tokens are read: its
+        token ids stay on the device, and its positions and pages are known.
+        The next call checks the guess against the scheduler's decision: the
+        same requests, or some of them (a stop token ended the others; rows
+        are independent), take the launched step's results; anything else
+        drops them and runs the decision as usual, which recomputes the same
+        cache entries."""
         ids, starts, counts, wants, tokens = self.scheduler.schedule_flat()
         n = len(ids)
+        ahead, self._ahead = self._ahead, None
         if n == 0:
             return None
         self.steps_run += 1
-        if self.runner.use_graphs and len(tokens) == n and wants.all():
+        decode_only = self.runner.use_graphs and len(tokens) == n and bool(wants.all())
+        rows = self._rows_of_launched(ahead, ids) if decode_only and ahead is not None else None
+        logits, launched = None, None
+        if rows is not None:
+            wanted = ids.tolist()
+            launched = ahead
+            self.steps_ahead += 1
+        elif decode_only:
             # every request brings one token and wants its logits: straight to the decode graph
             wanted = ids.tolist()
             logits = self.runner.decode_step_flat(ids, tokens)
@@ -70,11 +90,17 @@ class Engine:
                     wanted.append(rid)
                 off += c
             logits = self.runner.step(batch)
-        if logits is None:
+        if logits is None and launched is None:
             self.scheduler.update([], [])
             return []
         params = [self._params[r] for r in wanted]
-        if self.runner.last_greedy is not None and all(p.temperature == 0.0 for p in params):
+        greedy = all(p.temperature == 0.0 for p in params)
+        if (self.run_ahead and decode_only and greedy and (launched is None or len(launched.ids) == n)
+                and self.scheduler.next_step_predictable()):
+            self._ahead = self.runner.decode_follow(ids, launched)
+        if launched is not None:
+            sampled = launched.tokens()[rows]
+        elif self.runner.last_greedy is not None and greedy:
             sampled = self.runner.greedy_tokens_host()          # the decode graph took the argmax and copied it out
             if sampled is None:
                 sampled = self.runner.last_greedy.cpu().numpy()
@@ -83,6 +109,15 @@ class Engine:
         ops.tc_gemm_check()                 # the tokens are on the host: the step has finished
         self.scheduler.update(wanted, sampled)
         return list(zip(wanted, sampled.tolist()))
+
+    @staticmethod
+    def _rows_of_launched(launched, ids):
+        """The rows of the step launched ahead that answer the decision ``ids``, or None if it does not cover it."""
+        if len(ids) == len(launched.ids) and (ids == launched.ids).all():
+            return slice(0, len(ids))
+        row = {int(r): i for i, r in enumerate(launched.ids)}
+        rows = [row.get(int(r), -1) for r in ids]
+        return None if min(rows) < 0 else np.asarray(rows)
 
     def abort(self, request_id: int) -> None:
         self.scheduler.abort(request_id)

@@ -9,6 +9,8 @@ crates/vllm-models/src/llama/architecture.rs:141-156).
 """
 from __future__ import annotations
 
+import dataclasses
+
 import numpy as np
 import torch
 
@@ -111,7 +113,9 @@ class StaticDecodeBatch:
             block_table=[self.dev[tables_off + g * B * MB:tables_off + (g + 1) * B * MB].view(B, MB)
                          for g in range(G)],
             err_flag=runner.err_flag, decode_only=True)
+        self.sampled = torch.zeros(B, dtype=torch.int32, device=dev)           # the last step's greedy tokens
         self.step_graph = None
+        self.follow = [None, None]     # FollowStep: the same step fed with ``sampled`` instead of host tokens
         self.in_flight = None          # an event after the last replay that reads ``host`` and writes ``host_out``
 
     def wait_until_reusable(self) -> None:
@@ -122,6 +126,30 @@ class StaticDecodeBatch:
     def upload(self) -> int:
         self.dev.copy_(self.host, non_blocking=True)
         return self.host.numel() * 4
+
+
+class FollowStep:
+    """A decode step launched before the tokens of the step before it are on the
+    host: its graph takes positions, slots and block tables from this object's
+    own pinned buffer, the token ids from the static batch's ``sampled``, and
+    copies its greedy tokens into this object's pinned ``host_out``.  Two of
+    them alternate per static batch, so that a step in flight never shares a
+    pinned buffer with the step that is being read."""
+
+    def __init__(self, static: StaticDecodeBatch):
+        self.static = static
+        self.host_in = torch.zeros(static.host.numel(), dtype=torch.int32, pin_memory=True)
+        self.host_in_np = self.host_in.numpy()
+        self.host_out = torch.zeros(static.B, dtype=torch.int32, pin_memory=True)
+        self.host_out_np = self.host_out.numpy()
+        self.done = torch.cuda.Event()
+        self.captured = None
+        self.ids = None                # the requests of the launched step, in row order
+
+    def tokens(self) -> np.ndarray:
+        """The launched step's greedy tokens, one per row (waits for the step)."""
+        self.done.synchronize()
+        return self.host_out_np
 
 
 class ShapeGraph:
@@ -291,34 +319,43 @@ class ModelRunner:
             self._static[key] = StaticDecodeBatch(self, *key)
         return self._static[key]
 
-    def _capture(self, static: StaticDecodeBatch, loop=None) -> CapturedStep:
+    def _capture(self, static: StaticDecodeBatch, loop=None, follow: FollowStep | None = None) -> CapturedStep:
         """Capture one decode step over the static buffers: forward, greedy
         tokens and, with ``loop`` = (out_tokens, step_counter), the feedback of
-        those tokens so that the next replay is the next step."""
+        those tokens so that the next replay is the next step.  With ``follow``
+        the step takes its token ids from the step before it on the device and
+        everything else from ``follow``'s pinned buffer."""
         counter = ops.launch_counter()
+        B = static.B
 
         def body():
-            if loop is None:
+            if follow is not None:
+                static.dev[B:].copy_(follow.host_in[B:], non_blocking=True)
+            elif loop is None:
                 # a single step carries its own transfers: the packed inputs from pinned memory first, the greedy
                 # tokens to pinned memory last, so that one graph launch and one wait are all the host does
                 static.dev.copy_(static.host, non_blocking=True)
-            logits = self.model.forward(static.batch, self.views)
-            sampled = ops.argmax(logits)
+            # a following step reads its token ids where the step before left its greedy tokens
+            batch = static.batch if follow is None else dataclasses.replace(static.batch, token_ids=static.sampled)
+            logits = self.model.forward(batch, self.views)
             if loop is not None:
+                sampled = ops.argmax(logits)
                 b = static.batch
                 ops.decode_advance(b.token_ids, sampled, b.positions, b.context_lens, b.start_pos,
                                    b.slot_mapping[0], b.block_table[0], self.page_sizes[0], loop[0], loop[1])
             else:
-                static.host_out.copy_(sampled, non_blocking=True)
+                sampled = ops.argmax(logits, out=static.sampled)
+                (follow or static).host_out.copy_(sampled, non_blocking=True)
             return logits, sampled
 
         # a first run outside capture, so that libraries set themselves up before it
         side = torch.cuda.Stream(device=self.device)
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
-            saved = static.dev.clone()
+            saved, saved_sampled = static.dev.clone(), static.sampled.clone()
             body()
             static.dev.copy_(saved)
+            static.sampled.copy_(saved_sampled)             # a following step is fed with the tokens before this run
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
@@ -388,6 +425,47 @@ class ModelRunner:
         static, R = self._greedy_host
         static.in_flight.synchronize()
         return static.host_out_np[:R].copy()
+
+    def decode_follow(self, ids: np.ndarray, after) -> FollowStep | None:
+        """Launch the decode step that follows a launched one for the same
+        requests (``ids`` int64, in its row order) before that one's tokens are
+        on the host: the token ids stay on the device.  ``after`` is what that
+        step ran on: the FollowStep it was, or None for the step that
+        ``decode_step_flat`` launched last.  Nothing is committed: the caller
+        commits the step once it knows that the requests went on.  Returns None
+        if the step cannot be launched this way (no pages, a context beyond the
+        static batch's tables or the model's positions)."""
+        if after is None:
+            if self._greedy_host is None:
+                return None
+            static, R = self._greedy_host
+            k = 0
+        else:
+            static, R = after.static, len(after.ids)
+            k = 1 - static.follow.index(after)
+        if R != len(ids):
+            return None
+        if static.follow[k] is None:
+            static.follow[k] = FollowStep(static)
+        f = static.follow[k]
+        if not f.done.query():                              # only after a launch that was dropped: its copies may be pending
+            f.done.synchronize()
+        B = static.B
+        ahead = 0 if after is None else 1                   # decode_step_flat has advanced its requests already
+        try:
+            self.alloc.pack_decode(ids, B, static.MB, f.host_in_np[B:], ahead=ahead)
+        except CacheError:
+            return None
+        if int(f.host_in_np[2 * B:2 * B + R].max()) > self.model.spec.max_position:
+            return None
+        if f.captured is None:
+            f.captured = self._capture(static, follow=f)
+        f.captured.graph.replay()
+        f.done.record()
+        ops.launch_counter().value += f.captured.launches
+        self.last_h2d_bytes = (static.host.numel() - B) * 4
+        f.ids = ids.copy()
+        return f
 
     def decode_state(self, request_ids, first_tokens, max_steps: int) -> DecodeState:
         """Prepare ``max_steps`` decode steps that run on the device without

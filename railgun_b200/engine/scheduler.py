@@ -119,6 +119,12 @@ class Scheduler:
             raise SchedulerError(f"update failed with status {n}")
         return n
 
+    def next_step_predictable(self) -> bool:
+        """Whether the decision after the one just made is known already, unless
+        a stop token ends a request: all running requests decode, none can end
+        by length at this step, nothing waits and nothing was preempted."""
+        return bool(self._lib.rg_sched_next_step_predictable(self._h))
+
     def abort(self, request_id: int) -> None:
         if self._lib.rg_sched_abort(self._h, int(request_id)) != 0:
             raise SchedulerError(f"abort: unknown request {request_id}")

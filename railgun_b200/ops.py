@@ -619,11 +619,17 @@ def tc_gemm_check(device=None) -> None:
             raise KernelError(f"a tcgen05 kernel: {who} gave up waiting on a barrier; the result is invalid")
 
 
-def argmax(logits: torch.Tensor) -> torch.Tensor:
-    """Index of the largest logit of every row, ties to the lowest index."""
+def argmax(logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Index of the largest logit of every row, ties to the lowest index
+    (into ``out``, int32 [rows], if given)."""
     _check(logits, "logits", torch.float32)
     rows, V = logits.shape
-    out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    if out is None:
+        out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    else:
+        _check(out, "out", torch.int32)
+        if out.shape != (rows,):
+            raise KernelError(f"argmax: out has shape {tuple(out.shape)}, the logits have {rows} rows")
     pieces = min(64, -(-V // 2048))            # wide rows are cut into pieces so that many blocks share a row
     pv = pi = None
     if pieces > 1:

@@ -133,6 +133,55 @@ def test_preemption_does_not_change_the_outputs():
     assert outs[1].finish_reason == "error" and "out of KV cache blocks" in outs[1].error
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_launched_ahead_change_nothing(dtype):
+    """Decode steps are launched before the tokens of the step before are read.
+    Requests that end at different lengths and on stop tokens, a request added
+    in the middle, a request aborted in the middle and few pages (preemption):
+    the outputs equal those of an engine that launches nothing ahead, step by
+    step, and steps were indeed taken from launches made ahead."""
+    from railgun_b200.engine.engine import Engine
+    from railgun_b200.engine.request import SamplingParams
+    cfg, _, page = helpers.TINY["B"]
+    prompts = helpers.prompts(cfg["vocab_size"], [9, 40, 3, 63, 20], seed=21)
+    plain = P.PlainLlama(helpers.model_dir("B"))
+    stop = plain.greedy(prompts[1], 12)[7]               # ends request 1 in the middle of the others' decoding
+    params = [SamplingParams(max_new_tokens=n, stop_token_ids=st)
+              for n, st in ((30, []), (40, [stop]), (5, []), (17, []), (25, []))]
+
+    def run(ahead, blocks):
+        eng = Engine(helpers.model_dir("B"), dtype=dtype, block_size=page, num_gpu_blocks=blocks, max_num_seqs=4,
+                     max_num_batched_tokens=64, max_model_len=256)
+        eng.run_ahead = ahead
+        rids = [eng.add_request(p, sp) for p, sp in zip(prompts[:3], params[:3])]
+        trace, steps = [], 0
+        while eng.has_unfinished():
+            out = eng.step()
+            trace.append(sorted(out) if out else out)
+            steps += 1
+            if steps == 6:
+                rids.append(eng.add_request(prompts[3], params[3]))     # arrives while the others decode
+            if steps == 9:
+                rids.append(eng.add_request(prompts[4], params[4]))
+            if steps == 14:
+                eng.abort(rids[4])
+            assert steps < 400
+        outs = [eng.collect(r) for r in rids]
+        eng.runner.alloc.check()
+        assert eng.stats()["num_free_blocks"] == blocks
+        return outs, trace, eng.steps_ahead
+
+    for blocks in (64, 22):
+        base, base_trace, none_ahead = run(False, blocks)
+        outs, trace, taken_ahead = run(True, blocks)
+        assert none_ahead == 0 and taken_ahead > 10
+        assert trace == base_trace
+        for a, b in zip(outs, base):
+            assert a.token_ids == b.token_ids and a.finish_reason == b.finish_reason
+    assert base[1].finish_reason == "stop_token" and base[4].finish_reason == "cancelled"
+    assert base[0].token_ids == plain.greedy(prompts[0], 30) or dtype == "bfloat16"
+
+
 def test_engine_refuses_bad_requests():
     from railgun_b200.engine.engine import Engine
     from railgun_b200.engine.request import SamplingParams
