@@ -335,8 +335,9 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
     // last stage, which is first filled inside the loop
     bf16* sQ = Q_IN_REGS ? sKV + (DEC_STAGES - 1) * stage_elems : sKV + DEC_STAGES * stage_elems;
 
-    pdl_wait();
-    pdl_trigger();
+    // Positions, tables and every key but the token's own were written before the kernel that runs just before
+    // this one started (its blocks all passed their own wait before this kernel could launch), so the first
+    // tiles of K and V are requested ahead of the wait; q and the token's own key come from that kernel.
     const int split = blockIdx.z;
     const int kvh = blockIdx.y / head_tiles, ht = blockIdx.y - kvh * head_tiles;
     const int ti = blockIdx.x;
@@ -389,6 +390,8 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
         }
     };
     if (k_begin >= k_end) {                                         // an empty split: zero weight in the reduction
+        pdl_wait();
+        pdl_trigger();
         for (int i = threadIdx.x; i < nheads; i += NTHREADS) {
             float* ml = part_ml + (((size_t)ti * nh + h0 + i) * num_splits + split) * 2;
             ml[0] = -INFINITY;
@@ -465,22 +468,33 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
         }
     };
 
+    int page_next[KD];
+    // a tile that holds the token's own position waits for the kernel before this one
+    auto early = [&](int st) { return st < n_tiles && k_begin + (st + 1) * BN <= pos; };
+#pragma unroll
+    for (int st = 0; st < DEC_STAGES - 1; ++st) {
+        if (early(st)) {
+            pages_of(k_begin + st * BN, page_next);
+            gather(st, page_next, k_begin + st * BN);
+        }
+        cp_async_commit();
+    }
+    pdl_wait();
+    pdl_trigger();
     for (int idx = threadIdx.x; idx < 16 * d8; idx += NTHREADS) {
         const int row = idx / d8, c = idx - row * d8;
         const bool valid = row < nheads;
         const bf16* src = valid ? q + (size_t)t * q_stride + (size_t)(h0 + row) * d + c * 8 : q;
         cp_async16(sQ + row * stride + c * 8, src, valid);
     }
-    cp_async_commit();
-    int page_next[KD];
 #pragma unroll
     for (int st = 0; st < DEC_STAGES - 1; ++st) {
-        if (st < n_tiles) {
+        if (st < n_tiles && !early(st)) {
             pages_of(k_begin + st * BN, page_next);
             gather(st, page_next, k_begin + st * BN);
         }
-        cp_async_commit();
     }
+    cp_async_commit();                                               // Q and the tiles that had to wait: the newest group
     pages_of(k_begin + (DEC_STAGES - 1) * BN, page_next);            // beyond the split: all -1
 
     float oT[KD][4];                                                // O^T: dims (16 kd + g, + 8) x heads (2 tq, 2 tq + 1)
@@ -492,7 +506,7 @@ decode_attention_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
     const int vt_key = (lane & 7) + (lane >> 4) * 8, vt_dim = ((lane >> 3) & 1) * 8;   // V^T as A operand (.trans)
 
     uint32_t qf[Q_IN_REGS ? KD : 1][4];
-    cp_async_wait<DEC_STAGES - 1>();                                 // the Q group is the oldest: it has landed
+    cp_async_wait<0>();                                              // Q (and the first tiles) have landed
     __syncthreads();                                                 // Q was gathered by all threads
     if (Q_IN_REGS) {
 #pragma unroll
