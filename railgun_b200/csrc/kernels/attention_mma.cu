@@ -714,7 +714,7 @@ extern "C" int rg_decode_attention(const void* q, int q_stride, void* out, const
 #undef RG_DECODE
     if (e || counters != nullptr) return e;
     dim3 rgrid(n_tokens, nh);
-    RgStreamOrder in_order(true);       // measured: the merge starting early, beside the splits, costs a batch-8 step 2 %
+    RgStreamOrder in_order(true);       // measured: the merge starting early, beside the splits, costs a batch-8 step 4 %
     return rg_launch(decode_reduce_kernel, rgrid, dim3(d >= 128 ? 128 : 64), 0, s, 1, (const float*)part_o,
                      (const float*)part_ml, (bf16*)out, rows, nh, d, num_splits);
 }
