@@ -203,8 +203,9 @@ class ModelRunner:
         self.page_sizes = [g.page_size for g in self.cache.groups]
         self.err_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
         # graphs need every part to work from device-side descriptions only; parts with state of their own
-        # that plan on the host (none of the built-in ones) switch them off
-        self.use_graphs = bool(use_graphs) and not self.cache.state and len(self.page_sizes) >= 1
+        # and parts that say they plan on the host (none of the built-in ones) switch them off
+        self.use_graphs = (bool(use_graphs) and not self.cache.state and len(self.page_sizes) >= 1
+                           and self.model.graph_safe)
         self._static: dict = {}
         self._shape_steps: dict = {}       # layout -> ShapeGraph: steps of a layout seen before replay a captured graph
         self._shape_seen: dict = {}

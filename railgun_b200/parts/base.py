@@ -15,6 +15,10 @@ from .. import ops
 
 
 class Part:
+    # False for a part that plans on the host while it runs (reads device values back, launches a number of
+    # kernels that depends on the data): steps of a model with such a part are never captured in a CUDA graph.
+    graph_safe = True
+
     @classmethod
     def tensor_specs(cls, params: dict, prefix: str) -> dict:
         return {}

@@ -106,6 +106,18 @@ class DecoderModel:
     def vocab_size(self) -> int:
         return self.spec.vocab_size
 
+    def parts(self):
+        yield self.embedding
+        for layer in self.layers:
+            yield from (layer.mixer_norm, layer.mixer, layer.ffn_norm, layer.ffn)
+        yield self.final_norm
+        yield self.head
+
+    @property
+    def graph_safe(self) -> bool:
+        """Whether a step of this model can be captured in a CUDA graph: every part says so."""
+        return all(getattr(p, "graph_safe", True) for p in self.parts())
+
     def cache_needs(self) -> dict:
         """cache id -> what the writing layer's mixer keeps between steps."""
         needs = {}
