@@ -93,6 +93,7 @@ def _lib():
         lib.rg_sched_update.argtypes = [c_void_p, c_void_p, c_void_p, c_int]
         for name in ("abort", "finish_reason", "num_generated", "num_preemptions"):
             getattr(lib, f"rg_sched_{name}").argtypes = [c_void_p, c_longlong]
+        lib.rg_sched_num_generated_many.argtypes = [c_void_p, c_void_p, c_int, c_void_p]
         lib.rg_sched_outputs.argtypes = [c_void_p, c_longlong, c_void_p, c_int]
         lib.rg_sched_error.argtypes = [c_void_p, c_longlong, c_void_p, c_int]
         lib.rg_sched_forget.argtypes = [c_void_p, c_longlong]

@@ -304,6 +304,17 @@ int rg_sched_num_generated(void* h, long long id) {
     const SchedRequest* r = ((Scheduler*)h)->find(id);
     return r ? r->num_generated() : SCHED_UNKNOWN;
 }
+// How many tokens each of the n requests has generated; returns 0, or SCHED_UNKNOWN at the first unknown id.
+int rg_sched_num_generated_many(void* h, const long long* ids, int n, long long* out) {
+    try {
+        for (int i = 0; i < n; ++i) {
+            const SchedRequest* r = ((Scheduler*)h)->find(ids[i]);
+            if (!r) return SCHED_UNKNOWN;
+            out[i] = r->num_generated();
+        }
+        return 0;
+    } catch (...) { return SCHED_BAD_ARGUMENT; }
+}
 int rg_sched_num_preemptions(void* h, long long id) {
     const SchedRequest* r = ((Scheduler*)h)->find(id);
     return r ? r->num_preemptions : SCHED_UNKNOWN;

@@ -13,7 +13,7 @@ from __future__ import annotations
 import numpy as np
 
 from .. import ops
-from ..sampling.sampler import Sampler
+from ..sampling.sampler import Sampler, _as_i64
 from .batch import StepEntry
 from .request import RequestOutput, SamplingParams
 from .runner import ModelRunner
@@ -36,6 +36,7 @@ class Engine:
         self.steps_run = 0
         self.run_ahead = True          # launch the next decode step before this one's tokens are on the host
         self._ahead = None             # the step launched that way, if any (runner.FollowStep)
+        self._sampling = None          # the sampling parameters of the requests of the last sampled decode step
         self.steps_ahead = 0           # how many steps were taken from a launch made ahead
 
     # ---- low level --------------------------------------------------------------------------
@@ -71,15 +72,19 @@ class Engine:
         self.steps_run += 1
         decode_only = self.runner.use_graphs and len(tokens) == n and bool(wants.all())
         rows = self._rows_of_launched(ahead, ids) if decode_only and ahead is not None else None
-        logits, launched = None, None
-        if rows is not None:
+        logits, launched, sampling, greedy = None, None, None, True
+        if decode_only:
             wanted = ids.tolist()
+            params = [self._params[r] for r in wanted]
+            greedy = all(p.temperature == 0.0 for p in params)
+            if not greedy:
+                sampling = self._sampling_of(ids, wanted, params)   # the graph draws with the requests' parameters
+        if rows is not None:
             launched = ahead
             self.steps_ahead += 1
         elif decode_only:
             # every request brings one token and wants its logits: straight to the decode graph
-            wanted = ids.tolist()
-            logits = self.runner.decode_step_flat(ids, tokens)
+            logits = self.runner.decode_step_flat(ids, tokens, sampling)
         else:
             batch, off, wanted = [], 0, []
             for i in range(n):
@@ -90,25 +95,40 @@ class Engine:
                     wanted.append(rid)
                 off += c
             logits = self.runner.step(batch)
+            params = [self._params[r] for r in wanted]
+            greedy = all(p.temperature == 0.0 for p in params)
         if logits is None and launched is None:
             self.scheduler.update([], [])
             return []
-        params = [self._params[r] for r in wanted]
-        greedy = all(p.temperature == 0.0 for p in params)
-        if (self.run_ahead and decode_only and greedy and (launched is None or len(launched.ids) == n)
+        if (self.run_ahead and decode_only and (launched is None or len(launched.ids) == n)
                 and self.scheduler.next_step_predictable()):
-            self._ahead = self.runner.decode_follow(ids, launched)
+            after = None if sampling is None else dict(sampling, counter=sampling["counter"] + 1)
+            self._ahead = self.runner.decode_follow(ids, launched, after)
         if launched is not None:
             sampled = launched.tokens()[rows]
+        elif decode_only and self.runner.last_greedy is not None:
+            sampled = self.runner.greedy_tokens_host()          # the decode graph chose the tokens and copied them out
         elif self.runner.last_greedy is not None and greedy:
-            sampled = self.runner.greedy_tokens_host()          # the decode graph took the argmax and copied it out
-            if sampled is None:
-                sampled = self.runner.last_greedy.cpu().numpy()
+            sampled = self.runner.last_greedy.cpu().numpy()
         else:
             sampled = self.sampler.sample(logits, params, [self.scheduler.num_generated(r) for r in wanted])
         ops.tc_gemm_check()                 # the tokens are on the host: the step has finished
         self.scheduler.update(wanted, sampled)
         return list(zip(wanted, sampled.tolist()))
+
+    def _sampling_of(self, ids, wanted, params) -> dict:
+        """The requests' sampling parameters as arrays, one entry per request: the constant ones are kept while
+        the same requests decode; the count of generated tokens, which numbers the draw, is read every step."""
+        kept = self._sampling
+        if kept is None or len(kept["ids"]) != len(ids) or not (kept["ids"] == ids).all():
+            kept = self._sampling = dict(
+                ids=ids.copy(),
+                temperature=np.array([p.temperature for p in params], dtype=np.float32),
+                top_k=np.array([p.top_k for p in params], dtype=np.int32),
+                top_p=np.array([p.top_p for p in params], dtype=np.float32),
+                seed=np.array([_as_i64(p.seed) for p in params], dtype=np.int64))
+        return dict(temperature=kept["temperature"], top_k=kept["top_k"], top_p=kept["top_p"], seed=kept["seed"],
+                    counter=self.scheduler.num_generated_many(ids))
 
     @staticmethod
     def _rows_of_launched(launched, ids):

@@ -89,13 +89,15 @@ class StaticDecodeBatch:
     is copied into them in one transfer.  A graph captured over these buffers
     can be replayed for any such step.  Layout (int32): token ids | positions |
     context lengths | start positions | state slots | per group slot mapping |
-    per group block table [B, MB]."""
+    per group block table [B, MB] | the rows' sampling parameters (seed and
+    draw counter as 64-bit, temperature, top-k, top-p)."""
 
     def __init__(self, runner, B: int, MB: int):
         dev = runner.device
         G = len(runner.page_sizes)
         self.B, self.MB, self.G = B, MB, G
-        n_ints = (5 + G) * B + G * B * MB
+        self.sampling_off = -(-((5 + G) * B + G * B * MB) // 2) * 2          # even: 64-bit values start there
+        n_ints = self.sampling_off + 7 * B
         self.host = torch.zeros(n_ints, dtype=torch.int32, pin_memory=True)
         self.host_np = self.host.numpy()
         self.host_out = torch.zeros(B, dtype=torch.int32, pin_memory=True)     # the step's greedy tokens, copied by the graph
@@ -113,8 +115,9 @@ class StaticDecodeBatch:
             block_table=[self.dev[tables_off + g * B * MB:tables_off + (g + 1) * B * MB].view(B, MB)
                          for g in range(G)],
             err_flag=runner.err_flag, decode_only=True)
-        self.sampled = torch.zeros(B, dtype=torch.int32, device=dev)           # the last step's greedy tokens
-        self.step_graph = None
+        self.sampling = sampling_views(self.dev, self.sampling_off, B)        # device views of the sampling parameters
+        self.sampled = torch.zeros(B, dtype=torch.int32, device=dev)           # the tokens the last step chose
+        self.step_graphs = {}          # with sampling parameters or greedy -> CapturedStep
         self.follow = [None, None]     # FollowStep: the same step fed with ``sampled`` instead of host tokens
         self.in_flight = None          # an event after the last replay that reads ``host`` and writes ``host_out``
 
@@ -126,6 +129,23 @@ class StaticDecodeBatch:
     def upload(self) -> int:
         self.dev.copy_(self.host, non_blocking=True)
         return self.host.numel() * 4
+
+
+def sampling_views(buf, off: int, B: int) -> dict:
+    """The sampling parameters inside a packed decode buffer (a torch tensor or a numpy array of int32)."""
+    f32, i64 = (torch.float32, torch.int64) if isinstance(buf, torch.Tensor) else (np.float32, np.int64)
+    return dict(seed=buf[off:off + 2 * B].view(i64), counter=buf[off + 2 * B:off + 4 * B].view(i64),
+                temperature=buf[off + 4 * B:off + 5 * B].view(f32), top_k=buf[off + 5 * B:off + 6 * B],
+                top_p=buf[off + 6 * B:off + 7 * B].view(f32))
+
+
+def fill_sampling(views: dict, sampling, R: int) -> None:
+    """Write ``sampling`` (arrays of R entries by name, or None: every row greedy) into a host buffer's views;
+    rows beyond R are greedy."""
+    views["temperature"][:] = 0.0
+    if sampling is not None:
+        for name, v in views.items():
+            v[:R] = sampling[name]
 
 
 class FollowStep:
@@ -143,7 +163,7 @@ class FollowStep:
         self.host_out = torch.zeros(static.B, dtype=torch.int32, pin_memory=True)
         self.host_out_np = self.host_out.numpy()
         self.done = torch.cuda.Event()
-        self.captured = None
+        self.captured = {}             # with sampling parameters or greedy -> CapturedStep
         self.ids = None                # the requests of the launched step, in row order
 
     def tokens(self) -> np.ndarray:
@@ -320,12 +340,15 @@ class ModelRunner:
             self._static[key] = StaticDecodeBatch(self, *key)
         return self._static[key]
 
-    def _capture(self, static: StaticDecodeBatch, loop=None, follow: FollowStep | None = None) -> CapturedStep:
+    def _capture(self, static: StaticDecodeBatch, loop=None, follow: FollowStep | None = None,
+                 sampling: bool = False) -> CapturedStep:
         """Capture one decode step over the static buffers: forward, greedy
         tokens and, with ``loop`` = (out_tokens, step_counter), the feedback of
         those tokens so that the next replay is the next step.  With ``follow``
         the step takes its token ids from the step before it on the device and
-        everything else from ``follow``'s pinned buffer."""
+        everything else from ``follow``'s pinned buffer.  With ``sampling`` the
+        tokens are drawn with the rows' parameters in the static buffer
+        (temperature 0: greedy) instead of the plain argmax."""
         counter = ops.launch_counter()
         B = static.B
 
@@ -345,7 +368,12 @@ class ModelRunner:
                 ops.decode_advance(b.token_ids, sampled, b.positions, b.context_lens, b.start_pos,
                                    b.slot_mapping[0], b.block_table[0], self.page_sizes[0], loop[0], loop[1])
             else:
-                sampled = ops.argmax(logits, out=static.sampled)
+                if sampling:
+                    sp = static.sampling
+                    sampled = ops.sample(logits, sp["temperature"], sp["top_k"], sp["top_p"], sp["seed"],
+                                         sp["counter"], out=static.sampled)
+                else:
+                    sampled = ops.argmax(logits, out=static.sampled)
                 (follow or static).host_out.copy_(sampled, non_blocking=True)
             return logits, sampled
 
@@ -375,11 +403,13 @@ class ModelRunner:
             raise BatchError("a request appears twice in one step")
         return self.decode_step_flat(ids, tokens)
 
-    def decode_step_flat(self, ids: np.ndarray, tokens: np.ndarray) -> torch.Tensor:
+    def decode_step_flat(self, ids: np.ndarray, tokens: np.ndarray, sampling=None) -> torch.Tensor:
         """One decode step for requests already in the cache: ``ids`` int64
         (distinct), ``tokens`` int32, one token each, logits wanted for all.
-        Returns the logits [R, V] (a view of a static buffer); the greedy tokens
-        are in ``last_greedy``."""
+        Returns the logits [R, V] (a view of a static buffer); the tokens the
+        graph chose are in ``last_greedy``: the argmax, or, with ``sampling``
+        (arrays ``temperature``, ``top_k``, ``top_p``, ``seed``, ``counter`` of
+        one entry per request), a draw with those parameters."""
         R = len(ids)
         self.last_greedy = None
         if tokens.min() < 0 or tokens.max() >= self.model.vocab_size:
@@ -403,10 +433,12 @@ class ModelRunner:
                              f"{self.model.spec.max_position}")
         static.host_np[:R] = tokens
         static.host_np[R:B] = 0
+        fill_sampling(sampling_views(static.host_np, static.sampling_off, B), sampling, R)
         self.last_h2d_bytes = static.host.numel() * 4
-        if static.step_graph is None:
-            static.step_graph = self._capture(static)
-        cap = static.step_graph
+        key = sampling is not None
+        if key not in static.step_graphs:
+            static.step_graphs[key] = self._capture(static, sampling=key)
+        cap = static.step_graphs[key]
         cap.graph.replay()                                  # upload, the step, greedy tokens back to pinned memory
         if static.in_flight is None:
             static.in_flight = torch.cuda.Event()
@@ -427,12 +459,13 @@ class ModelRunner:
         static.in_flight.synchronize()
         return static.host_out_np[:R].copy()
 
-    def decode_follow(self, ids: np.ndarray, after) -> FollowStep | None:
+    def decode_follow(self, ids: np.ndarray, after, sampling=None) -> FollowStep | None:
         """Launch the decode step that follows a launched one for the same
         requests (``ids`` int64, in its row order) before that one's tokens are
         on the host: the token ids stay on the device.  ``after`` is what that
         step ran on: the FollowStep it was, or None for the step that
-        ``decode_step_flat`` launched last.  Nothing is committed: the caller
+        ``decode_step_flat`` launched last; ``sampling`` as there, for this
+        step's draw.  Nothing is committed: the caller
         commits the step once it knows that the requests went on.  Returns None
         if the step cannot be launched this way (no pages, a context beyond the
         static batch's tables or the model's positions)."""
@@ -459,11 +492,14 @@ class ModelRunner:
             return None
         if int(f.host_in_np[2 * B:2 * B + R].max()) > self.model.spec.max_position:
             return None
-        if f.captured is None:
-            f.captured = self._capture(static, follow=f)
-        f.captured.graph.replay()
+        fill_sampling(sampling_views(f.host_in_np, static.sampling_off, B), sampling, R)
+        key = sampling is not None
+        if key not in f.captured:
+            f.captured[key] = self._capture(static, follow=f, sampling=key)
+        cap = f.captured[key]
+        cap.graph.replay()
         f.done.record()
-        ops.launch_counter().value += f.captured.launches
+        ops.launch_counter().value += cap.launches
         self.last_h2d_bytes = (static.host.numel() - B) * 4
         f.ids = ids.copy()
         return f

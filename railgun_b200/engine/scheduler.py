@@ -148,6 +148,14 @@ class Scheduler:
             raise SchedulerError(f"unknown request {request_id}")
         return n
 
+    def num_generated_many(self, request_ids: np.ndarray) -> np.ndarray:
+        """The count of generated tokens of every request in ``request_ids`` (int64), as int64."""
+        ids = np.ascontiguousarray(request_ids, dtype=np.int64)
+        out = np.empty(ids.size, dtype=np.int64)
+        if self._lib.rg_sched_num_generated_many(self._h, ids.ctypes.data, ids.size, out.ctypes.data) != 0:
+            raise SchedulerError("num_generated_many: an unknown request")
+        return out
+
     def num_preemptions(self, request_id: int) -> int:
         return self._lib.rg_sched_num_preemptions(self._h, int(request_id))
 

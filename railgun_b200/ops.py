@@ -642,7 +642,7 @@ def argmax(logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tenso
 
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k, top_p, seed: torch.Tensor,
-           counter: torch.Tensor) -> torch.Tensor:
+           counter: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     """One token per row; rows with temperature <= 0 are greedy.  ``seed`` and
     ``counter`` are int64 tensors read as unsigned 64-bit."""
     _check(logits, "logits", torch.float32)
@@ -658,7 +658,12 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k, top_p, seed: 
                     ("top_k", top_k), ("top_p", top_p)):
         if t is not None and t.numel() != rows:
             raise KernelError(f"{name} has {t.numel()} entries for {rows} rows")
-    out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    if out is None:
+        out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    else:
+        _check(out, "out", torch.int32)
+        if out.shape != (rows,):
+            raise KernelError(f"sample: out has shape {tuple(out.shape)}, the logits have {rows} rows")
     _ok(_fn("sampling", "rg_sample")(_ptr(logits), c_int(rows), c_int(V), _ptr(temperature), _ptr(top_k),
                                      _ptr(top_p), _ptr(seed), _ptr(counter), _ptr(out), _stream()), "sample")
     return out
