@@ -319,14 +319,17 @@ def _plain_interval(logits, temperature, top_k, top_p, tok):
     return (c[tok] - p[tok]) / c[-1], c[tok] / c[-1], p
 
 
-@pytest.mark.parametrize("V", [500, 128256])
-def test_temperature_top_k_top_p_sampling(V):
+@pytest.mark.parametrize("V,scale", [(500, 2.5), (20001, 2.5), (128256, 2.5), (128256, 9.0)])
+def test_temperature_top_k_top_p_sampling(V, scale):
+    """Vocabularies that one block takes and that a cluster of blocks shares (one of them no multiple of
+    four, so the last block's part is ragged); flat and peaked rows; filters that leave a handful of
+    candidates (finished in shared memory) and filters that leave thousands (finished over the row)."""
     from railgun_b200 import ops
-    rng = np.random.default_rng(V)
+    rng = np.random.default_rng(V + int(scale))
     rows = 64
-    logits = (rng.normal(size=(rows, V)) * 2.5).astype(np.float32)
+    logits = (rng.normal(size=(rows, V)) * scale).astype(np.float32)
     temperature = rng.choice([0.0, 0.5, 0.8, 1.3], size=rows).astype(np.float32)
-    top_k = rng.choice([0, 1, 5, 50, V + 10], size=rows).astype(np.int32)
+    top_k = rng.choice([0, 1, 5, 50, 2000, V + 10], size=rows).astype(np.int32)
     top_p = rng.choice([1.0, 0.9, 0.5, 0.2], size=rows).astype(np.float32)
     seed = rng.integers(0, 2 ** 62, size=rows)
     counter = rng.integers(0, 1000, size=rows)
@@ -352,6 +355,40 @@ def test_temperature_top_k_top_p_sampling(V):
     # a batch of one gives the same token as the row in the big batch
     one = ops.sample(*(a[7:8].contiguous() for a in args)).cpu().numpy()
     assert one[0] == out[7]
+
+
+def test_sampling_with_ties_at_the_thresholds():
+    """Rows made so that the filters' thresholds fall on ties: top-k keeps every logit equal to the k-th
+    largest, top-p every probability equal to its threshold; one row is constant (everything ties: the
+    kept set is the whole vocabulary however small k is)."""
+    from railgun_b200 import ops
+    V, n = 40000, 400
+    rng = np.random.default_rng(3)
+    base = (rng.normal(size=V) * 0.5).astype(np.float32)
+    tied = base.copy()
+    top = rng.choice(V, size=30, replace=False)
+    tied[top[:10]] = 6.0
+    tied[top[10:]] = 5.0                                         # 20 logits tie for places 11..30
+    const = np.full(V, 1.25, dtype=np.float32)
+    cases = [(tied, 15, 1.0, set(top.tolist())),                 # k = 15 falls inside the tie: all 30 kept
+             (tied, 10, 1.0, set(top[:10].tolist())),
+             (tied, 0, 0.6, None), (const, 7, 1.0, None), (const, 0, 0.3, None)]
+    for row, k, p, allowed in cases:
+        logits = torch.tensor(np.tile(row, (n, 1)), device=DEV)
+        out = ops.sample(logits, torch.full((n,), 1.0, device=DEV), torch.full((n,), k, dtype=torch.int32, device=DEV),
+                         torch.full((n,), p, device=DEV), torch.full((n,), 11, dtype=torch.int64, device=DEV),
+                         torch.arange(n, dtype=torch.int64, device=DEV)).cpu().numpy()
+        probs = P.filtered_probs(row, 1.0, k, p)
+        assert (probs[out] > 0).all(), (k, p)
+        if allowed is not None:
+            assert set(out.tolist()) <= allowed and len(set(out.tolist())) > len(allowed) // 2
+        if row is const:
+            # every token is as likely as any other: the draws spread over the whole vocabulary
+            assert out.min() < V // 10 and out.max() > V - V // 10
+        for i in range(0, n, 37):
+            lo, hi, _ = _plain_interval(row, 1.0, k, p, int(out[i]))
+            u = P.uniform_from_counter(11, i)
+            assert lo - 1e-4 <= u <= hi + 1e-4
 
 
 def test_sampling_follows_the_distribution():
