@@ -295,8 +295,9 @@ sample_kernel(const float* __restrict__ logits, int V,
         if (v > best || (v == best && i < bi)) { best = v; bi = i; }
     });
     R.argmax(best, bi);
+    if (bi == 0x7fffffff) bi = 0;                                   // a row without a largest value (all NaN)
     if (!(T > 0.f)) {
-        if (tid == 0 && rank == 0) out[row_i] = bi == 0x7fffffff ? 0 : bi;
+        if (tid == 0 && rank == 0) out[row_i] = bi;
         R.sync();                                                   // nobody leaves while its shared memory is read
         return;
     }
