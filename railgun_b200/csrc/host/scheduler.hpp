@@ -188,11 +188,13 @@ public:
         return finished;
     }
 
-    // Whether the step after the one just decided is known before this one's tokens are: every entry decodes one
-    // token of a request that this step's token cannot end by length, nothing waits for admission, and nothing was
-    // preempted.  (A stop token may still end a request; the caller checks its guess against the next decision.)
+    // Whether the step after the one just decided is known before this one's tokens are: every running request
+    // decodes one token that cannot end it by length, and nothing was preempted.  A request that still waits was
+    // refused admission in this decision (no seat, no pages or no budget), and none of those comes back unless a
+    // request ends.  (A stop token may still end a request, and a request may arrive; the caller checks its guess
+    // against the next decision.)
     bool next_step_predictable() const {
-        if (entries_.empty() || !waiting_.empty() || !preempted_.empty()) return false;
+        if (entries_.empty() || !preempted_.empty()) return false;
         if (entries_.size() != running_.size()) return false;
         for (const StepEntry& e : entries_) {
             if (e.count != 1 || !e.want_last) return false;

@@ -56,7 +56,7 @@ class Engine:
         """One scheduler decision and one model step.  Returns the (request id,
         sampled token) pairs of this step, or None if nothing could be scheduled.
 
-        While every running request decodes greedily and nothing waits, the
+        While every running request decodes and none can end by length, the
         step after this one is launched before this one's tokens are read: its
         token ids stay on the device, and its positions and pages are known.
         The next call checks the guess against the scheduler's decision: the

@@ -121,8 +121,10 @@ class Scheduler:
 
     def next_step_predictable(self) -> bool:
         """Whether the decision after the one just made is known already, unless
-        a stop token ends a request: all running requests decode, none can end
-        by length at this step, nothing waits and nothing was preempted."""
+        a stop token ends a request or a request arrives: all running requests
+        decode, none can end by length at this step and nothing was preempted
+        (a request that waits was refused in this decision and stays refused
+        until a request ends)."""
         return bool(self._lib.rg_sched_next_step_predictable(self._h))
 
     def abort(self, request_id: int) -> None:
