@@ -226,3 +226,40 @@ def test_random_workloads_finish_with_undisturbed_outputs(seed):
     for rid, toks in want.items():
         assert s.finish_reason(rid) == "max_tokens" and s.outputs(rid) == toks
     assert a.free_pages() == 40 and a.free_slots() == 5
+
+
+def test_when_the_next_decision_is_known_ahead():
+    """The engine launches the next decode step early only when the scheduler says that its decision is
+    known: all running requests decode, none can end by length, nothing was preempted."""
+    a, s = make(pages=8, page=4, seats=2)
+    s.add_request(1, [1, 2, 3], 4)
+    s.add_request(2, [4, 5], 3)
+    s.add_request(3, [6, 7, 8], 5)                     # no seat: waits
+    es = s.schedule()
+    assert [e.request_id for e in es] == [1, 2] and not s.next_step_predictable()     # prompts in the step
+    s.update([1, 2], [10, 20])
+    s.schedule()
+    assert s.num_waiting == 1 and s.next_step_predictable()      # both decode; request 3 was refused a seat
+    s.update([1, 2], [11, 21])
+    s.schedule()
+    assert not s.next_step_predictable()               # request 2 generates its last token in this step
+    s.update([1, 2], [12, 22])
+    es = s.schedule()                                  # request 2 is gone, request 3 takes its seat: a prompt
+    assert sorted(e.request_id for e in es) == [1, 3] and not s.next_step_predictable()
+    assert s.num_generated_many(np.array([1, 3])).tolist() == [3, 0]
+    s.update([1, 3], [13, 30])
+    assert s.finished() == [2, 1]
+    s.schedule()
+    assert s.next_step_predictable()                   # request 3 decodes alone
+    # a preemption in the decision: nothing is launched ahead
+    a2, s2 = make(pages=3, page=4, seats=4)
+    s2.add_request(1, [1] * 4, 8)
+    s2.add_request(2, [2] * 4, 8)
+    run_step(s2)
+    while not s2.preempted():
+        assert s2.num_running == 2
+        es = s2.schedule()
+        if s2.preempted():
+            assert not s2.next_step_predictable()
+            break
+        s2.update([e.request_id for e in es], [7] * len(es))
