@@ -65,56 +65,58 @@ class Engine:
         drops them and runs the decision as usual, which recomputes the same
         cache entries."""
         ids, starts, counts, wants, tokens = self.scheduler.schedule_flat()
-        n = len(ids)
         ahead, self._ahead = self._ahead, None
-        if n == 0:
+        if len(ids) == 0:
             return None
         self.steps_run += 1
-        decode_only = self.runner.use_graphs and len(tokens) == n and bool(wants.all())
-        rows = self._rows_of_launched(ahead, ids) if decode_only and ahead is not None else None
-        logits, launched, sampling, greedy = None, None, None, True
-        if decode_only:
-            wanted = ids.tolist()
-            params = [self._params[r] for r in wanted]
-            greedy = all(p.temperature == 0.0 for p in params)
-            if not greedy:
-                sampling = self._sampling_of(ids, wanted, params)   # the graph draws with the requests' parameters
-        if rows is not None:
-            launched = ahead
-            self.steps_ahead += 1
-        elif decode_only:
-            # every request brings one token and wants its logits: straight to the decode graph
-            logits = self.runner.decode_step_flat(ids, tokens, sampling)
+        if self.runner.use_graphs and len(tokens) == len(ids) and bool(wants.all()):
+            wanted, sampled = self._decode_step(ids, tokens, ahead)
         else:
-            batch, off, wanted = [], 0, []
-            for i in range(n):
-                c = int(counts[i])
-                rid = int(ids[i])
-                batch.append(StepEntry(rid, tokens[off:off + c], [c - 1] if wants[i] else []))
-                if wants[i]:
-                    wanted.append(rid)
-                off += c
-            logits = self.runner.step(batch)
-            params = [self._params[r] for r in wanted]
-            greedy = all(p.temperature == 0.0 for p in params)
-        if logits is None and launched is None:
+            wanted, sampled = self._mixed_step(ids, counts, wants, tokens)
+        if sampled is None:
             self.scheduler.update([], [])
             return []
-        if (self.run_ahead and decode_only and (launched is None or len(launched.ids) == n)
-                and self.scheduler.next_step_predictable()):
-            after = None if sampling is None else dict(sampling, counter=sampling["counter"] + 1)
-            self._ahead = self.runner.decode_follow(ids, launched, after)
-        if launched is not None:
-            sampled = launched.tokens()[rows]
-        elif decode_only and self.runner.last_greedy is not None:
-            sampled = self.runner.greedy_tokens_host()          # the decode graph chose the tokens and copied them out
-        elif self.runner.last_greedy is not None and greedy:
-            sampled = self.runner.last_greedy.cpu().numpy()
-        else:
-            sampled = self.sampler.sample(logits, params, [self.scheduler.num_generated(r) for r in wanted])
         ops.tc_gemm_check()                 # the tokens are on the host: the step has finished
         self.scheduler.update(wanted, sampled)
         return list(zip(wanted, sampled.tolist()))
+
+    def _decode_step(self, ids, tokens, ahead):
+        """Every request brings one token and wants its logits: the step is a graph replay that chooses the
+        tokens itself, or the step launched ahead in the call before if it answers this decision."""
+        wanted = ids.tolist()
+        params = [self._params[r] for r in wanted]
+        sampling = None                                              # all greedy: the graph takes the argmax
+        if any(p.temperature != 0.0 for p in params):
+            sampling = self._sampling_of(ids, wanted, params)       # the graph draws with the requests' parameters
+        rows = self._rows_of_launched(ahead, ids) if ahead is not None else None
+        launched = ahead if rows is not None else None
+        if launched is not None:
+            self.steps_ahead += 1
+        else:
+            self.runner.decode_step_flat(ids, tokens, sampling)
+        if (self.run_ahead and (launched is None or len(launched.ids) == len(ids))
+                and self.scheduler.next_step_predictable()):
+            after = None if sampling is None else dict(sampling, counter=sampling["counter"] + 1)
+            self._ahead = self.runner.decode_follow(ids, launched, after)
+        # only now wait for this step's tokens
+        return wanted, (launched.tokens()[rows] if launched is not None else self.runner.greedy_tokens_host())
+
+    def _mixed_step(self, ids, counts, wants, tokens):
+        """Portions of prompts, maybe beside decoded tokens: one packed step; the tokens are chosen afterwards
+        at the rows that asked for logits."""
+        batch, off, wanted = [], 0, []
+        for i in range(len(ids)):
+            c = int(counts[i])
+            rid = int(ids[i])
+            batch.append(StepEntry(rid, tokens[off:off + c], [c - 1] if wants[i] else []))
+            if wants[i]:
+                wanted.append(rid)
+            off += c
+        logits = self.runner.step(batch)
+        if logits is None:
+            return wanted, None
+        params = [self._params[r] for r in wanted]
+        return wanted, self.sampler.sample(logits, params, [self.scheduler.num_generated(r) for r in wanted])
 
     def _sampling_of(self, ids, wanted, params) -> dict:
         """The requests' sampling parameters as arrays, one entry per request: the constant ones are kept while

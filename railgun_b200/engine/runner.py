@@ -450,9 +450,10 @@ class ModelRunner:
         return cap.logits[:R]
 
     def greedy_tokens_host(self):
-        """The greedy tokens of the last graph-replayed decode step as a numpy
-        array (waits for the step; the graph itself copied them to pinned
-        memory), or None if the last step was not such a step."""
+        """The tokens that the last graph-replayed decode step chose (its argmax,
+        or its draws if it was given sampling parameters) as a numpy array; waits
+        for the step, whose graph copied them to pinned memory itself.  None if
+        the last step was not such a step."""
         if self.last_greedy is None or self._greedy_host is None:
             return None
         static, R = self._greedy_host
