@@ -129,3 +129,37 @@ def test_a_step_that_runs_out_of_pages_gives_back_the_requests_it_added():
         build_step_batch([StepEntry(2, [1])], small, [16], VOCAB, MAX_POS, "cpu")
     assert small.num_requests() == 1
     small.check()
+
+
+def test_sampling_parameters_in_the_packed_decode_buffer():
+    """The decode graphs read the rows' sampling parameters from the tail of the packed buffer: 64-bit seeds
+    and draw counters first (at an even offset), then temperature, top-k, top-p; rows beyond the step's
+    requests are greedy."""
+    from railgun_b200.engine.runner import fill_sampling, sampling_views
+    B, off = 4, 38
+    buf = np.zeros(off + 7 * B, dtype=np.int32)
+    views = sampling_views(buf, off, B)
+    fill_sampling(views, dict(temperature=np.array([0.5, 0.0, 1.5], dtype=np.float32), top_k=np.array([3, 0, 40]),
+                              top_p=np.array([0.75, 1.0, 0.25], dtype=np.float32),
+                              seed=np.array([7, -1, 2 ** 62], dtype=np.int64), counter=np.array([0, 11, 12345678901])), 3)
+    assert buf[off:off + 2 * B].view(np.int64).tolist() == [7, -1, 2 ** 62, 0]
+    assert buf[off + 2 * B:off + 4 * B].view(np.int64).tolist() == [0, 11, 12345678901, 0]
+    assert buf[off + 4 * B:off + 5 * B].view(np.float32).tolist() == [0.5, 0.0, 1.5, 0.0]
+    assert buf[off + 5 * B:off + 6 * B].tolist() == [3, 0, 40, 0]
+    assert buf[off + 6 * B:off + 7 * B].view(np.float32).tolist() == [0.75, 1.0, 0.25, 0.0]
+    fill_sampling(views, None, 2)                               # a greedy step: every temperature is zero again
+    assert not buf[off + 4 * B:off + 5 * B].any()
+    assert not buf[:off].any()
+
+
+def test_rows_of_a_step_launched_ahead():
+    """Which rows of a launched step answer a decision: all of them in order, a subset (requests that ended
+    are skipped), or none if the decision names a request the step did not hold."""
+    from types import SimpleNamespace
+    from railgun_b200.engine.engine import Engine
+    launched = SimpleNamespace(ids=np.array([4, 9, 2, 7], dtype=np.int64))
+    rows = Engine._rows_of_launched(launched, np.array([4, 9, 2, 7], dtype=np.int64))
+    assert rows == slice(0, 4)
+    assert Engine._rows_of_launched(launched, np.array([4, 2, 7], dtype=np.int64)).tolist() == [0, 2, 3]
+    assert Engine._rows_of_launched(launched, np.array([7, 4], dtype=np.int64)).tolist() == [3, 0]
+    assert Engine._rows_of_launched(launched, np.array([4, 9, 2, 5], dtype=np.int64)) is None
