@@ -4,8 +4,13 @@
 (crates/vllm-cli/src/generate.rs:29-53): ``--model/-m DIR``, ``--max-tokens``
 (default 128), ``--temperature`` (default 0.0 = greedy; honoured here, the
 reference parses and ignores it), ``--cuda-device N``, ``--show-token-ids``.
-Prompts are token ids (``--prompt-ids 1,2,3;4,5``): tokenizers are out of
-scope, so ``--prompt/-p TEXT`` is replaced.  The engine options of the
+Prompts are token ids (``--prompt-ids 1,2,3;4,5``), or, as in the reference,
+text (``--prompt/-p TEXT``) when the model folder holds a ``tokenizer.json``
+(read with the ``tokenizers`` library, the one the reference's
+RailgunTokenizer wraps, crates/vllm-models/src/tokenizer.rs:29-52: encode with
+special tokens, decode skipping them; the tokenizer's end-of-sequence id, or
+the configuration's, ends generation, generate.rs:83-85; the prompt is printed
+with the generated text after it, generate.rs:99).  The engine options of the
 reference's ``serve`` (crates/vllm-cli/src/serve.rs:44-77) are accepted with
 their names and defaults.  It prints the generated ids and a ``[stats]`` line
 with tokens per second, as the reference does (generate.rs:99-111).
@@ -24,8 +29,10 @@ def make_parser() -> argparse.ArgumentParser:
 
     g = sub.add_parser("generate", help="generate tokens from prompt token ids")
     g.add_argument("-m", "--model", required=True, help="model folder (config.json + *.safetensors)")
-    g.add_argument("--prompt-ids", required=True,
-                   help="prompt token ids, comma separated; several prompts separated by ';'")
+    what = g.add_mutually_exclusive_group(required=True)
+    what.add_argument("--prompt-ids",
+                      help="prompt token ids, comma separated; several prompts separated by ';'")
+    what.add_argument("-p", "--prompt", help="prompt text (the model folder must hold a tokenizer.json)")
     g.add_argument("--max-tokens", type=int, default=128, help="maximum number of new tokens")
     g.add_argument("--temperature", type=float, default=0.0, help="sampling temperature (0.0 = greedy)")
     g.add_argument("--top-p", type=float, default=1.0)
@@ -54,13 +61,44 @@ def _ids(text: str) -> list:
     return [int(t) for t in text.replace(" ", "").split(",") if t != ""]
 
 
+def load_tokenizer(model_dir):
+    """``tokenizer.json`` of the model folder (crates/vllm-models/src/tokenizer.rs:29-31)."""
+    import os
+    path = os.path.join(str(model_dir), "tokenizer.json")
+    if not os.path.isfile(path):
+        raise OSError(f"{path} does not exist (use --prompt-ids for a model without a tokenizer)")
+    from tokenizers import Tokenizer
+    try:
+        return Tokenizer.from_file(path)
+    except Exception as e:                                  # the library raises its own exception type
+        raise ValueError(f"cannot read {path}: {e}") from e
+
+
 def run_generate(args) -> int:
     from .engine.engine import Engine
     from .engine.request import SamplingParams
 
-    prompts = [_ids(p) for p in args.prompt_ids.split(";") if p.strip()]
+    tokenizer, stop_ids = None, _ids(args.stop_token_ids)
+    if args.prompt is not None:
+        try:
+            tokenizer = load_tokenizer(args.model)
+        except (OSError, ImportError, ValueError) as e:
+            print(f"error: --prompt needs a tokenizer: {e}", file=sys.stderr)
+            return 2
+        prompts = [tokenizer.encode(args.prompt, add_special_tokens=True).ids]
+        # the end-of-sequence id: the first of these names that the tokenizer knows, else the configuration's
+        # (crates/vllm-models/src/tokenizer.rs:73-83, crates/vllm-cli/src/generate.rs:83-85)
+        eos = next((tokenizer.token_to_id(n) for n in ("<|eot_id|>", "<|end_of_text|>", "</s>")
+                    if tokenizer.token_to_id(n) is not None), None)
+        if eos is None:
+            from .config.registry import load_config
+            stop_ids += [t for t in (load_config(args.model)[1].to_dict().get("eos_token_id") or []) if t not in stop_ids]
+        elif eos not in stop_ids:
+            stop_ids.append(eos)
+    else:
+        prompts = [_ids(p) for p in args.prompt_ids.split(";") if p.strip()]
     if not prompts or any(not p for p in prompts):
-        print("error: --prompt-ids needs at least one token id per prompt", file=sys.stderr)
+        print("error: the prompt needs at least one token", file=sys.stderr)
         return 2
     t0 = time.time()
     engine = Engine(args.model, dtype=args.dtype, cuda_device=args.cuda_device, block_size=args.block_size,
@@ -69,7 +107,7 @@ def run_generate(args) -> int:
                     max_prefill_chunk=args.max_prefill_chunk)
     load_ms = (time.time() - t0) * 1e3
     params = [SamplingParams(max_new_tokens=args.max_tokens, temperature=args.temperature, top_p=args.top_p,
-                             top_k=args.top_k, stop_token_ids=_ids(args.stop_token_ids), seed=args.seed + i)
+                             top_k=args.top_k, stop_token_ids=stop_ids, seed=args.seed + i)
               for i in range(len(prompts))]
     t0 = time.time()
     outs = engine.generate(prompts, params)
@@ -77,7 +115,10 @@ def run_generate(args) -> int:
     for p, o in zip(prompts, outs):
         if args.show_token_ids:
             print(f"prompt ids: {p}")
-        print(",".join(str(t) for t in o.token_ids))
+        if tokenizer is not None:
+            print(args.prompt + tokenizer.decode(o.token_ids, skip_special_tokens=True))
+        if tokenizer is None or args.show_token_ids:
+            print(",".join(str(t) for t in o.token_ids))
         if o.error:
             print(f"[error] request {o.request_id}: {o.error}", file=sys.stderr)
     n = sum(len(o.token_ids) for o in outs)

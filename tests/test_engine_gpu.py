@@ -214,6 +214,41 @@ def test_generate_command(tmp_path):
     assert lines[-1].startswith("[stats] 12 tokens") and "tok/s" in lines[-1]
 
 
+def test_generate_command_with_a_text_prompt(tmp_path):
+    """``--prompt/-p TEXT`` with a tokenizer.json in the model folder (a word-level toy made here): the
+    same tokens as the ids path, the text printed after the prompt, generation ended by the tokenizer's
+    end-of-sequence token."""
+    import shutil
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    cfg, _, page = helpers.TINY["A"]
+    plain = P.PlainLlama(helpers.model_dir("A"))
+    mdir = tmp_path / "with_tokenizer"
+    shutil.copytree(helpers.model_dir("A"), mdir)
+    ref = plain.greedy([5, 6, 7], 6)
+    eos = ref[3]                                                 # the fourth generated token ends the text
+    vocab = {f"w{i}": i for i in range(cfg["vocab_size"])}
+    del vocab[f"w{eos}"]
+    vocab["</s>"] = eos
+    tok = Tokenizer(models.WordLevel(vocab, unk_token="w0"))
+    tok.pre_tokenizer = pre_tokenizers.Whitespace()
+    tok.save(str(mdir / "tokenizer.json"))
+    proc = subprocess.run(
+        [sys.executable, os.path.join(ROOT, "bin", "railgun"), "generate", "-m", str(mdir), "-p", "w5 w6 w7",
+         "--max-tokens", "6", "--dtype", "f32", "--show-token-ids", "--num-gpu-blocks", "32"],
+        capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    lines = proc.stdout.strip().splitlines()
+    first = ref[:ref.index(eos) + 1]                             # the stop token is kept, as in the engine path
+    assert lines[0] == "prompt ids: [5, 6, 7]"
+    assert lines[1].startswith("w5 w6 w7") and f"w{first[0]}" in lines[1]
+    assert lines[2] == ",".join(map(str, first))
+    # without a tokenizer the option is refused before anything is loaded
+    proc = subprocess.run(
+        [sys.executable, os.path.join(ROOT, "bin", "railgun"), "generate", "-m", str(helpers.model_dir("A")), "-p", "w5"],
+        capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 2 and "tokenizer.json does not exist" in proc.stderr
+
+
 def test_random_weights_command(tmp_path):
     proc = subprocess.run(
         [sys.executable, "-m", "railgun_b200", "random-weights", "--config",
