@@ -111,10 +111,9 @@ def decode_bytes(cfg, batch, context, kv_bytes_per_token):
     H, I, V, L = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"], cfg["num_hidden_layers"]
     nh, nkv, d = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
     per_layer = (nh + 2 * nkv) * d * H + nh * d * H + 3 * I * H + 2 * H
-    weights = (L * per_layer + V * H + H) * 2
-    if not cfg["tie_word_embeddings"]:
-        weights += V * H * 2
-    return weights + batch * context * kv_bytes_per_token
+    weights = (L * per_layer + V * H + H) * 2              # the head's matrix once, tied or not
+    embedding_rows = batch * H * 2                          # of the embedding table only the tokens' rows
+    return weights + embedding_rows + batch * context * kv_bytes_per_token
 
 
 def prefill_flops(cfg, T):
@@ -149,18 +148,18 @@ def run_ours(args):
     kv_per_token = runner.cache.bytes_per_token()
     launches = ops.launch_counter()
 
-    def fill_contexts(batch, first_id):
-        """Prefill ``batch`` requests of CONTEXT tokens each; returns their ids and first sampled tokens."""
+    def fill_contexts(batch, first_id, context=CONTEXT):
+        """Prefill ``batch`` requests of ``context`` tokens each; returns their ids and first sampled tokens."""
         ids = list(range(first_id, first_id + batch))
         toks = []
         for rid in ids:
-            prompt = rng.integers(0, V, size=CONTEXT).tolist()
-            lg = runner.step([StepEntry(rid, prompt, [CONTEXT - 1])])
+            prompt = rng.integers(0, V, size=context).tolist()
+            lg = runner.step([StepEntry(rid, prompt, [context - 1])])
             toks.append(int(ops.argmax(lg).item()))
         return ids, toks
 
-    def time_decode(batch, steps, warmup, first_id):
-        ids, toks = fill_contexts(batch, first_id)
+    def time_decode(batch, steps, warmup, first_id, context=CONTEXT):
+        ids, toks = fill_contexts(batch, first_id, context)
         state = runner.decode_state(ids, toks, max_steps=steps + warmup)
         for _ in range(warmup):
             runner.decode_step(state)
@@ -179,8 +178,10 @@ def run_ours(args):
         return batch / ms * 1e3, ms, n_launch
 
     if args.mode == "decode":                              # a short run of one decode batch (for profiling)
-        tok_s, ms_step, n_launch = time_decode(args.batch, args.steps, args.warmup, 1000)
-        print(json.dumps({"mode": "decode", "batch": args.batch, "tok_s": round(tok_s, 1),
+        tok_s, ms_step, n_launch = time_decode(args.batch, args.steps, args.warmup, 1000, args.context)
+        bytes_step = decode_bytes(cfg, args.batch, args.context + args.warmup + args.steps // 2, kv_per_token)
+        print(json.dumps({"mode": "decode", "batch": args.batch, "context": args.context, "tok_s": round(tok_s, 1),
+                          "hbm_frac": round(bytes_step / (ms_step * 1e-3) / 1e9 / pk["hbm_gbs"], 4),
                           "ms_per_step": round(ms_step, 4), "gpu_launches": n_launch,
                           "layers": cfg["num_hidden_layers"]}))
         return 0
@@ -389,6 +390,7 @@ def main():
                     "decode_attention, prefill_gemm, prefill_attention")
     ap.add_argument("--batch", type=int, default=8, help="--mode decode: requests in the batch")
     ap.add_argument("--tokens", type=int, default=PREFILL_TOKENS, help="--mode prefill: prompt length")
+    ap.add_argument("--context", type=int, default=CONTEXT, help="--mode decode: tokens each request holds")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
