@@ -345,6 +345,20 @@ def run_kernels(args):
             us = timed(lambda: [ops.decode_attention(q, QKV, o, kv, bt, None, B, req, pos, nh, nkv, d, 0, d ** -0.5, splits)
                                 for kv in kvs])
             out(f"decode attention B{B} ctx{ctx} splits{splits}", us, GBs=round(B * ctx * nkv * d * 4 / us / 1e3, 1))
+    if on("sampling"):
+        V = cfg["vocab_size"]
+        for rows in (8, 64):
+            logits = [torch.randn(rows, V, device=dev) * 9.0 for _ in range(L)]      # peaked rows, as a trained model's
+            seed = torch.arange(rows, dtype=torch.int64, device=dev)
+            counter = torch.zeros(rows, dtype=torch.int64, device=dev)
+            res = {"argmax": round(timed(lambda: [ops.argmax(l) for l in logits]), 1)}
+            for name, T, k, p in (("temperature", 0.8, 0, 1.0), ("top_k_50", 0.8, 50, 1.0), ("top_p_0.9", 0.8, 0, 0.9),
+                                  ("top_k_50_top_p_0.9", 0.8, 50, 0.9), ("top_k_2000", 0.8, 2000, 1.0)):
+                t = torch.full((rows,), T, device=dev)
+                kk = torch.full((rows,), k, dtype=torch.int32, device=dev)
+                pp = torch.full((rows,), p, device=dev)
+                res[name] = round(timed(lambda: [ops.sample(l, t, kk, pp, seed, counter) for l in logits]), 1)
+            out(f"sampling {rows} rows x {V} logits", res["temperature"], **res)
     if on("prefill_gemm"):
         for M in (2048, 8192):
             x = torch.randn(M, H, device=dev).to(torch.bfloat16)
@@ -386,7 +400,7 @@ def main():
     ap.add_argument("--mode", default="all", choices=["all", "decode", "prefill", "kernels"],
                     help="all: the contract's line; decode / prefill: one short measurement (for profiling); "
                          "kernels: the hot kernels one by one")
-    ap.add_argument("--cases", default="", help="--mode kernels: comma-separated subset of decode_gemm, "
+    ap.add_argument("--cases", default="", help="--mode kernels: comma-separated subset of sampling, decode_gemm, "
                     "decode_attention, prefill_gemm, prefill_attention")
     ap.add_argument("--batch", type=int, default=8, help="--mode decode: requests in the batch")
     ap.add_argument("--tokens", type=int, default=PREFILL_TOKENS, help="--mode prefill: prompt length")
