@@ -116,11 +116,13 @@ def build_step_batch(entries, alloc, page_sizes, vocab_size: int, max_position: 
             raise BatchError(f"request {e.request_id}: an entry needs at least one token")
         if toks.dtype.kind not in "iu" or toks.min() < 0 or toks.max() >= vocab_size:
             raise BatchError(f"request {e.request_id}: token ids must be in [0, {vocab_size})")
+    # small counts are Python numbers: every numpy call on an array of a few entries costs microseconds
+    count_list = [t.size for t in token_arrays]
+    want_ends = list(accumulate(len(e.want) for e in entries))
+    W = want_ends[-1]
     ids = np.fromiter((e.request_id for e in entries), dtype=np.int64, count=R)
-    counts = np.fromiter((t.size for t in token_arrays), dtype=np.int32, count=R)
-    want_offsets = np.zeros(R + 1, dtype=np.int32)
-    np.cumsum([len(e.want) for e in entries], out=want_offsets[1:])
-    W = int(want_offsets[-1])
+    counts = np.array(count_list, dtype=np.int32)
+    want_offsets = np.array([0, *want_ends], dtype=np.int32)
     want = np.fromiter(chain.from_iterable(e.want for e in entries), dtype=np.int32, count=W)
     # checked, then reserved (all or nothing new) by the cache manager
     code, bad, value, starts, max_blocks = alloc.plan_step(ids, counts, want, want_offsets, max_position)
@@ -134,12 +136,13 @@ def build_step_batch(entries, alloc, page_sizes, vocab_size: int, max_position: 
         if code == -8:
             raise BatchError(f"request {rid}: wanted place {value} is outside its {n} tokens")
         alloc._raise(code, f"reserve({rid}, {int(starts[bad]) + n})")
-    T = int(counts.sum())
-    several = counts[counts > 1]
-    n_tiles = int((-(-several // ATTENTION_TILE_ROWS)).sum())
-    n_tiles128 = int((-(-several // (2 * ATTENTION_TILE_ROWS))).sum())
-    n_dec = R - several.size
-    max_blocks_t = tuple(int(m) for m in max_blocks)
+    T = sum(count_list)
+    several = [c for c in count_list if c > 1]
+    n_tiles = sum(-(-c // ATTENTION_TILE_ROWS) for c in several)
+    n_tiles128 = sum(-(-c // (2 * ATTENTION_TILE_ROWS)) for c in several)
+    n_dec = R - len(several)
+    max_blocks_t = tuple(max_blocks.tolist())
+    start_list = starts.tolist()
     sizes = [T, T, T, W, R + 1, R, R, R]
     for g in range(G):
         sizes += [T, R * max_blocks_t[g]]
@@ -154,7 +157,7 @@ def build_step_batch(entries, alloc, page_sizes, vocab_size: int, max_position: 
     host = buf.numpy()
     cu = host[offs[4]:offs[5]].copy()
     slots = host[offs[7]:offs[8]].copy()
-    layout = (tuple(counts.tolist()), W, max_blocks_t)
+    layout = (tuple(count_list), W, max_blocks_t)
     static = into(layout) if into is not None else None
     if static is not None:
         if static.numel() != buf.numel():
@@ -166,7 +169,7 @@ def build_step_batch(entries, alloc, page_sizes, vocab_size: int, max_position: 
     d = dev.split(sizes).__getitem__                       # views, cut in one call
     return StepBatch(
         num_tokens=T, num_requests=R, num_wanted=W,
-        max_query_len=int(counts.max()), max_context_len=int((starts + counts).max()),
+        max_query_len=max(count_list), max_context_len=max(a + b for a, b in zip(start_list, count_list)),
         token_ids=d(0), positions=d(1), req_of_token=d(2), want_rows=d(3), cu_seqlens=d(4),
         context_lens=d(5), start_pos=d(6), state_slots=d(7),
         slot_mapping=[d(8 + 2 * g) for g in range(G)],
@@ -174,7 +177,7 @@ def build_step_batch(entries, alloc, page_sizes, vocab_size: int, max_position: 
         err_flag=err_flag, host_cu_seqlens=cu, host_start_pos=starts, host_state_slots=slots,
         request_ids=[e.request_id for e in entries], h2d_bytes=offs[-1] * 4, host_buffer=buf,
         layout=layout,
-        decode_only=bool(counts.max() == 1),
+        decode_only=max(count_list) == 1,
         prefill_tiles=d(8 + 2 * G).view(-1, 3) if n_tiles else None, num_prefill_tiles=n_tiles,
         decode_rows=d(9 + 2 * G) if n_dec else None, num_decode_rows=n_dec,
         prefill_tiles128=d(10 + 2 * G).view(-1, 3) if n_tiles128 else None, num_prefill_tiles128=n_tiles128,
