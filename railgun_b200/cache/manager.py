@@ -74,6 +74,7 @@ def _lib():
         lib.rg_cache_free_pages.argtypes = [c_void_p, c_int]
         lib.rg_cache_pack_decode.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int]
         lib.rg_cache_advance.argtypes = [c_void_p, c_void_p, c_int, c_int]
+        lib.rg_cache_commit_many.argtypes = [c_void_p, c_void_p, c_void_p, c_int]
         lib.rg_cache_plan_step.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p,
                                            c_void_p, c_void_p, c_void_p]
         lib.rg_cache_fill_step.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
@@ -220,6 +221,12 @@ class PageAllocator:
                                             max_blocks.ctypes.data, int(tile_rows), segments.ctypes.data, out_ptr)
         if code:
             self._raise(code, "fill_step")
+
+    def commit_many(self, ids: np.ndarray, new_lens: np.ndarray) -> None:
+        """``commit`` for several requests: ``ids`` int64, ``new_lens`` int32."""
+        code = self._lib.rg_cache_commit_many(self._h, ids.ctypes.data, new_lens.ctypes.data, ids.size)
+        if code:
+            self._raise(code, "commit_many")
 
     def advance(self, ids: np.ndarray, n: int = 1) -> None:
         code = self._lib.rg_cache_advance(self._h, ids.ctypes.data, ids.size, n)

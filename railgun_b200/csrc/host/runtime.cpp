@@ -216,6 +216,17 @@ int rg_cache_fill_step(void* h, const long long* ids, const int* counts, const i
         return CACHE_OK;
     } catch (...) { return CACHE_CORRUPT; }
 }
+// Request b now holds new_len[b] tokens (the step that was packed for them ran).
+int rg_cache_commit_many(void* h, const long long* ids, const int* new_len, int R) {
+    try {
+        CacheManager* c = (CacheManager*)h;
+        for (int b = 0; b < R; ++b) {
+            const int st = c->commit(ids[b], new_len[b]);
+            if (st != CACHE_OK) return st;
+        }
+        return CACHE_OK;
+    } catch (...) { return CACHE_CORRUPT; }
+}
 // Every listed request now holds `n` more tokens.
 int rg_cache_advance(void* h, const long long* ids, int R, int n) {
     try {

@@ -78,6 +78,8 @@ class StepBatch:
     host_cu_seqlens: np.ndarray | None = None
     host_start_pos: np.ndarray | None = None
     host_state_slots: np.ndarray | None = None
+    host_request_ids: np.ndarray | None = None   # int64
+    host_context_lens: np.ndarray | None = None  # int32: tokens each request holds once the step has run
     request_ids: list = field(default_factory=list)
     h2d_bytes: int = 0
     host_buffer: torch.Tensor | None = None      # the pinned buffer the step was packed in (alive until the copy ran)
@@ -175,6 +177,7 @@ def build_step_batch(entries, alloc, page_sizes, vocab_size: int, max_position: 
         slot_mapping=[d(8 + 2 * g) for g in range(G)],
         block_table=[d(9 + 2 * g).view(R, max_blocks_t[g]) for g in range(G)],
         err_flag=err_flag, host_cu_seqlens=cu, host_start_pos=starts, host_state_slots=slots,
+        host_request_ids=ids, host_context_lens=starts + counts,
         request_ids=[e.request_id for e in entries], h2d_bytes=offs[-1] * 4, host_buffer=buf,
         layout=layout,
         decode_only=max(count_list) == 1,

@@ -260,8 +260,7 @@ class ModelRunner:
         return logits
 
     def _commit(self, entries, batch) -> None:
-        for e, start in zip(entries, batch.host_start_pos):
-            self.alloc.commit(e.request_id, int(start) + len(e.tokens))
+        self.alloc.commit_many(batch.host_request_ids, batch.host_context_lens)
 
     def _step_shape_graph(self, entries):
         """Large steps (portions of prompts) whose packed layout was seen before

@@ -58,6 +58,7 @@ def test_fields_of_random_steps(seed):
         assert b.start_pos.tolist() == starts and b.state_slots.tolist() == exp["slots"]
         assert list(b.host_cu_seqlens) == exp["cu"] and list(b.host_start_pos) == starts
         assert list(b.host_state_slots) == exp["slots"]
+        assert b.host_request_ids.tolist() == ids and b.host_context_lens.tolist() == exp["ctx"]
         for g in range(2):
             assert b.slot_mapping[g].tolist() == exp["slot_maps"][g]
             width = b.block_table[g].shape[1]
@@ -76,8 +77,9 @@ def test_fields_of_random_steps(seed):
         assert b.decode_only == all(len(e.tokens) == 1 for e in entries)
         assert b.layout == (tuple(len(e.tokens) for e in entries), len(exp["want_rows"]),
                             tuple(t.shape[1] for t in b.block_table))
+        alloc.commit_many(b.host_request_ids, b.host_context_lens)
         for e, s in zip(entries, starts):
-            alloc.commit(e.request_id, s + len(e.tokens))
+            assert alloc.num_computed(e.request_id) == s + len(e.tokens)
             live[e.request_id] = s + len(e.tokens)
         for rid in ids:
             if live[rid] > 300 or rng.random() < 0.2:
