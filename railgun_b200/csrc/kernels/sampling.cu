@@ -1,4 +1,5 @@
-// Sampling over 32-bit logits, one thread block per row.
+// Sampling over 32-bit logits: one thread block per row for short rows and for the greedy kernels, a cluster of
+// eight blocks per row when a token is drawn from a long row.
 //
 // Greedy: argmax, ties to the lowest index (crates/vllm-models/src/llama/model.rs:210-218).
 // Temperature: p = softmax(logits / T); top-k keeps logits >= the k-th largest,
