@@ -15,7 +15,7 @@ import numpy as np
 from .. import ops
 from ..sampling.sampler import Sampler, _as_i64
 from .batch import StepEntry
-from .request import RequestOutput, SamplingParams
+from .request import RequestOutput, SamplingParams, StepResponse
 from .runner import ModelRunner
 from .scheduler import Scheduler, SchedulerConfig
 
@@ -159,6 +159,36 @@ class Engine:
     def stats(self) -> dict:
         return dict(num_waiting=self.scheduler.num_waiting, num_running=self.scheduler.num_running,
                     num_free_blocks=self.runner.alloc.free_pages(0), steps=self.steps_run)
+
+    def stream(self, prompt_ids, params=None):
+        """Generate for every prompt and yield a StepResponse for every token as
+        the step that made it ends (the reference's receiver of
+        EngineStepResponse, crates/vllm-engine/src/engine.rs:64-76); the last
+        response of a request has ``is_finished`` and its finish reason.  A
+        request that ends without a token (an error, an abort) gets one
+        response without a token."""
+        if prompt_ids and isinstance(prompt_ids[0], (int, np.integer)):
+            prompt_ids = [prompt_ids]
+        if params is None or isinstance(params, SamplingParams):
+            params = [params or SamplingParams()] * len(prompt_ids)
+        if len(params) != len(prompt_ids):
+            raise ValueError(f"{len(prompt_ids)} prompts but {len(params)} parameter sets")
+        open_ids = {self.add_request(list(p), sp) for p, sp in zip(prompt_ids, params)}
+        while open_ids:
+            made = self.step()
+            done = [r for r in self.scheduler.finished() if r in open_ids]
+            if made is None and not done and not self.scheduler.preempted():
+                raise RuntimeError("the scheduler can make no progress: no request fits the cache")
+            for rid, token in made or ():
+                if rid in open_ids:
+                    ended = rid in done
+                    yield StepResponse(rid, token, ended, self.scheduler.finish_reason(rid) if ended else None)
+                    if ended:
+                        open_ids.discard(rid)
+            for rid in done:
+                if rid in open_ids:                                  # ended in this step without a token
+                    open_ids.discard(rid)
+                    yield StepResponse(rid, None, True, self.scheduler.finish_reason(rid))
 
     # ---- the call a user makes --------------------------------------------------------------
     def generate(self, prompt_ids, params=None) -> list:

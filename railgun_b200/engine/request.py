@@ -42,3 +42,15 @@ class RequestOutput:
     finish_reason: str | None
     error: str | None = None
     num_preemptions: int = 0
+
+
+@dataclass
+class StepResponse:
+    """One generated token of one request, as the reference sends one
+    EngineStepResponse per token to the request's receiver
+    (crates/vllm-engine/src/engine.rs:27-33); ``token_id`` stands where the
+    reference has the decoded text (tokenizers are outside this engine)."""
+    request_id: int
+    token_id: int | None
+    is_finished: bool
+    finish_reason: str | None = None

@@ -167,3 +167,24 @@ def test_nothing_is_launched_ahead_of_a_last_token():
     assert eng._ahead is None and not eng.has_unfinished()
     assert eng.collect(a).token_ids == expected_output(a, [5, 6, 7], 3)
     assert [e[0] for e in eng.runner.log] == ["mixed", "step", "ahead"]
+
+
+def test_stream_yields_every_token_as_its_step_ends():
+    """``Engine.stream``: one response per generated token, in step order, the last one of a request
+    marked finished with its reason; the finished requests stay collectable."""
+    eng = make_engine(True)
+    prompts = [[3, 4, 5], [9] * 7, [1]]
+    stop = expected_output(2, prompts[1], 9)[4]
+    params = [SamplingParams(max_new_tokens=6), SamplingParams(max_new_tokens=9, stop_token_ids=[stop]),
+              SamplingParams(max_new_tokens=2)]
+    got, last = {}, {}
+    for r in eng.stream(prompts, params):
+        assert r.request_id not in last, "a response after the finishing one"
+        got.setdefault(r.request_id, []).append(r.token_id)
+        if r.is_finished:
+            last[r.request_id] = r.finish_reason
+    assert got[1] == expected_output(1, prompts[0], 6) and last[1] == "max_tokens"
+    assert got[2] == expected_output(2, prompts[1], 9, [stop]) and last[2] == "stop_token" and got[2][-1] == stop
+    assert got[3] == expected_output(3, prompts[2], 2) and last[3] == "max_tokens"
+    assert eng.collect(2).token_ids == got[2] and not eng.has_unfinished()
+    eng.runner.alloc.check()
