@@ -186,6 +186,23 @@ def test_steps_launched_ahead_change_nothing(dtype, sampled):
     assert sampled or dtype == "bfloat16" or base[0].token_ids == plain.greedy(prompts[0], 30)
 
 
+def test_stream_gives_the_tokens_of_generate():
+    from railgun_b200.engine.engine import Engine
+    from railgun_b200.engine.request import SamplingParams
+    cfg, _, page = helpers.TINY["A"]
+    prompts = helpers.prompts(cfg["vocab_size"], [5, 17, 33], seed=1)
+    params = [SamplingParams(max_new_tokens=n, temperature=t, seed=2) for n, t in ((8, 0.0), (3, 0.9), (12, 0.0))]
+    kw = dict(dtype="float32", block_size=page, num_gpu_blocks=64, max_num_seqs=8)
+    outs = Engine(helpers.model_dir("A"), **kw).generate(prompts, params)
+    got, reasons = {}, {}
+    for r in Engine(helpers.model_dir("A"), **kw).stream(prompts, params):
+        got.setdefault(r.request_id, []).append(r.token_id)
+        if r.is_finished:
+            reasons[r.request_id] = r.finish_reason
+    assert [got[o.request_id] for o in outs] == [o.token_ids for o in outs]
+    assert [reasons[o.request_id] for o in outs] == [o.finish_reason for o in outs] == ["max_tokens"] * 3
+
+
 def test_engine_refuses_bad_requests():
     from railgun_b200.engine.engine import Engine
     from railgun_b200.engine.request import SamplingParams
