@@ -6,6 +6,15 @@ wanted places.  Generation, the scheduler and trace replay all go through it.
 The reference's counterpart is execute_model_step -> forward_packed
 (crates/vllm-engine/src/engine.rs:175-286,
 crates/vllm-models/src/llama/architecture.rs:141-156).
+
+How a step reaches the GPU: steps of single tokens replay a CUDA graph over a
+static batch (``decode_step_flat``; the graph copies its inputs in, chooses
+the tokens and copies them out), and the step after such a step can be
+launched before its tokens are known (``decode_follow``); large steps whose
+packed layout repeats replay a graph captured for that layout
+(``_step_shape_graph``); everything else launches its kernels one by one.
+``decode_state`` / ``decode_step`` run several decode steps without the host
+in between (what the benchmark's device-side number times).
 """
 from __future__ import annotations
 
