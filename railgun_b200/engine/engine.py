@@ -14,7 +14,7 @@ import numpy as np
 
 from .. import ops
 from ..sampling.sampler import Sampler, _as_i64
-from .batch import StepEntry
+from .batch import StepEntry, _token_array
 from .request import RequestOutput, SamplingParams, StepResponse
 from .runner import ModelRunner
 from .scheduler import Scheduler, SchedulerConfig
@@ -44,11 +44,12 @@ class Engine:
         params = params or SamplingParams()
         params.validate()
         vocab = self.runner.model.vocab_size
-        if any((t < 0 or t >= vocab) for t in prompt_ids):
-            raise ValueError(f"prompt token ids must be in [0, {vocab})")
+        prompt = _token_array(prompt_ids)
+        if prompt.size and (prompt.dtype.kind not in "iu" or prompt.min() < 0 or prompt.max() >= vocab):
+            raise ValueError(f"prompt token ids must be integers in [0, {vocab})")
         rid = self._next_id
         self._next_id += 1
-        self.scheduler.add_request(rid, prompt_ids, params.max_new_tokens, params.stop_token_ids)
+        self.scheduler.add_request(rid, prompt, params.max_new_tokens, params.stop_token_ids)
         self._params[rid] = params
         return rid
 

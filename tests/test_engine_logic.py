@@ -188,3 +188,22 @@ def test_stream_yields_every_token_as_its_step_ends():
     assert got[3] == expected_output(3, prompts[2], 2) and last[3] == "max_tokens"
     assert eng.collect(2).token_ids == got[2] and not eng.has_unfinished()
     eng.runner.alloc.check()
+
+
+def test_requests_are_checked_when_they_are_added():
+    from railgun_b200.engine.scheduler import SchedulerError
+    eng = make_engine(False)
+    for bad in ([1, 97], [-1, 2], [1.5, 2.0]):                       # outside the vocabulary of 97, or no integers
+        with pytest.raises(ValueError, match="prompt token ids"):
+            eng.add_request(bad)
+    with pytest.raises(SchedulerError, match="empty"):
+        eng.add_request([])
+    with pytest.raises(SchedulerError, match="max_model_len"):
+        eng.add_request([1] * 500, SamplingParams(max_new_tokens=100))
+    with pytest.raises(ValueError):
+        eng.add_request([1], SamplingParams(top_p=0.0))
+    assert not eng.has_unfinished() and eng._params == {}
+    rid = eng.add_request(np.array([3, 4, 5]), SamplingParams(max_new_tokens=2))      # arrays are taken as lists are
+    while eng.has_unfinished():
+        eng.step()
+    assert eng.collect(rid).token_ids == expected_output(rid, [3, 4, 5], 2)
