@@ -29,7 +29,7 @@ LLAMA_3_2_1B = dict(
     head_dim=64, num_hidden_layers=16, intermediate_size=8192, vocab_size=128256, rope_theta=500000.0,
     rope_scaling=dict(rope_type="llama3", factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0,
                       original_max_position_embeddings=8192),
-    tie_word_embeddings=True, rms_norm_eps=1e-5, max_position_embeddings=8192, torch_dtype="bfloat16")
+    tie_word_embeddings=True, rms_norm_eps=1e-5, max_position_embeddings=131072, torch_dtype="bfloat16")
 CONTEXT = 1024            # tokens each decoding request holds
 PREFILL_TOKENS = 2048
 FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0)     # used only if MEASURED_PEAKS.json is absent
@@ -156,32 +156,123 @@ def run_ours(args):
             prompt = rng.integers(0, V, size=context).tolist()
             lg = runner.step([StepEntry(rid, prompt, [context - 1])])
             toks.append(int(ops.argmax(lg).item()))
-        return ids, toks
+        return np.asarray(ids, dtype=np.int64), np.asarray(toks, dtype=np.int32)
 
-    def time_decode(batch, steps, warmup, first_id, context=CONTEXT):
+    class DecodeLoop:
+        """Decode steps for requests in the cache, launched as generation launches them (``Engine.step``): the
+        first from host tokens, every later one while the one before it runs, its token ids staying on the
+        device; but no step's tokens are read here.  ``log`` [n, rows] receives every step's tokens."""
+
+        def __init__(self, ids, toks, log=None):
+            self.ids, self.log, self.done, self.follow = ids, log, 0, None
+            runner.decode_step_flat(ids, toks)
+            self._note(runner.last_greedy)
+
+        def _note(self, sampled):
+            if self.log is not None:
+                self.log[self.done, :len(self.ids)].copy_(sampled[:len(self.ids)])
+            self.done += 1
+
+        def run(self, n):
+            for _ in range(n):
+                nxt = runner.decode_follow(self.ids, self.follow)
+                if nxt is None:
+                    raise RuntimeError("the cache has no room for the timed decode steps")
+                if self.follow is not None:
+                    runner.alloc.advance(self.ids, 1)      # the step before is committed once its successor is packed
+                self.follow = nxt
+                self._note(nxt.static.sampled)
+
+        def close(self):
+            if self.follow is not None:
+                runner.alloc.advance(self.ids, 1)
+            torch.cuda.synchronize()
+
+    def time_decode(batch, steps, warmup, first_id, context=CONTEXT, min_seconds=0.3):
+        """Windows of exactly ``steps`` decode steps each, timed with CUDA events, until ``min_seconds`` are
+        covered (three windows at least); before each window the requests go back to ``context`` tokens, so every
+        window reads the same amount of cache.  Returns the median window."""
         ids, toks = fill_contexts(batch, first_id, context)
-        state = runner.decode_state(ids, toks, max_steps=steps + warmup)
+        back = np.full(batch, context, dtype=np.int32)
+        windows, n_launch, total = [], 0, 0.0
+        while len(windows) < 3 or (total < min_seconds and len(windows) < 200):
+            runner.alloc.commit_many(ids, back)
+            loop = DecodeLoop(ids, toks)
+            loop.run(warmup - 1)
+            torch.cuda.synchronize()
+            n0 = launches.value
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            loop.run(steps)
+            t1.record()
+            torch.cuda.synchronize()
+            loop.close()
+            n_launch = launches.value - n0
+            ms = t0.elapsed_time(t1)
+            windows.append(ms / steps)
+            total += ms * 1e-3
+        runner.check_device_errors()
+        runner.end(ids.tolist())
+        ms = sorted(windows)[len(windows) // 2]
+        return batch / ms * 1e3, ms, n_launch, len(windows)
+
+    def hbm_frac(batch, ms, steps, warmup, context=CONTEXT):
+        bytes_step = decode_bytes(cfg, batch, context + warmup + steps // 2, kv_per_token)
+        achieved = bytes_step / (ms * 1e-3) / 1e9
+        return achieved, achieved / pk["hbm_gbs"]
+
+    def e2e_window(prompts, steps, warmup):
+        """``steps`` calls of Engine.step with every request decoding: host tokens in, host tokens out."""
+        rids = [eng.add_request(p, SamplingParams(max_new_tokens=steps + warmup + 2)) for p in prompts]
+        tokens = {r: [] for r in rids}
+        while True:                                        # until all prompts are in the cache
+            out = eng.step()
+            for r, t in out or ():
+                tokens[r].append(t)
+            if out is not None and len(out) == len(prompts):
+                break
         for _ in range(warmup):
-            runner.decode_step(state)
+            for r, t in eng.step():
+                tokens[r].append(t)
         torch.cuda.synchronize()
-        n0 = launches.value
-        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        t0.record()
+        w0 = time.perf_counter()
         for _ in range(steps):
-            runner.decode_step(state)
-        t1.record()
+            for r, t in eng.step():
+                tokens[r].append(t)
         torch.cuda.synchronize()
-        ms = t0.elapsed_time(t1) / steps
-        n_launch = launches.value - n0
-        runner.decode_finish(state)
-        runner.end(ids)
-        return batch / ms * 1e3, ms, n_launch
+        seconds = time.perf_counter() - w0
+        h2d = eng.runner.last_h2d_bytes
+        for r in rids:
+            eng.abort(r)
+            eng.collect(r)
+        return seconds * 1e3 / steps, h2d, [tokens[r] for r in rids]
+
+    def check_tokens(prompts, n=24):
+        """The timed loop against the entry point: the same prompts through Engine.step, token by token on the
+        host, and through ``DecodeLoop`` after the same prefill; every token of every step must be equal."""
+        _, _, by_engine = e2e_window(prompts, n - 1, 1)
+        rids = [eng.add_request(p, SamplingParams(max_new_tokens=n + 2)) for p in prompts]
+        while True:
+            out = eng.step()
+            if out is not None and len(out) == len(prompts):
+                break
+        first = dict(out)
+        ids = np.asarray(rids, dtype=np.int64)
+        log = torch.zeros((n, len(rids)), dtype=torch.int32, device=runner.device)
+        loop = DecodeLoop(ids, np.asarray([first[r] for r in rids], dtype=np.int32), log)
+        loop.run(n - 1)
+        loop.close()
+        by_loop = log.cpu().numpy()
+        for r in rids:
+            eng.abort(r)
+            eng.collect(r)
+        return all([first[r]] + by_loop[:, i].tolist() == by_engine[i][:n + 1] for i, r in enumerate(rids))
 
     if args.mode == "decode":                              # a short run of one decode batch (for profiling)
-        tok_s, ms_step, n_launch = time_decode(args.batch, args.steps, args.warmup, 1000, args.context)
-        bytes_step = decode_bytes(cfg, args.batch, args.context + args.warmup + args.steps // 2, kv_per_token)
+        tok_s, ms_step, n_launch, _ = time_decode(args.batch, args.steps, args.warmup, 1000, args.context,
+                                                  min_seconds=0.0 if args.windows == 1 else 0.3)
         print(json.dumps({"mode": "decode", "batch": args.batch, "context": args.context, "tok_s": round(tok_s, 1),
-                          "hbm_frac": round(bytes_step / (ms_step * 1e-3) / 1e9 / pk["hbm_gbs"], 4),
+                          "hbm_frac": round(hbm_frac(args.batch, ms_step, args.steps, args.warmup, args.context)[1], 4),
                           "ms_per_step": round(ms_step, 4), "gpu_launches": n_launch,
                           "layers": cfg["num_hidden_layers"]}))
         return 0
@@ -202,17 +293,23 @@ def run_ours(args):
                           "tok_s": round(args.tokens / ms * 1e3, 1), "layers": cfg["num_hidden_layers"],
                           "frac": round(prefill_flops(cfg, args.tokens) / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}))
         return 0
+
+    prompts = [rng.integers(0, V, size=CONTEXT).tolist() for _ in range(8)]
+    checked = bool(check_tokens(prompts))
     with ClockSampler() as clocks:
-        tok_s, ms_step, n_launch = time_decode(8, args.steps, args.warmup, 1000)
+        tok_s, ms_step, n_launch, n_windows = time_decode(8, args.steps, args.warmup, 1000)
     clock_summary = clocks.summary()
     points = {}
     for b in (1, 64):
-        points[f"decode_b{b}"] = round(time_decode(b, max(10, args.steps // 2), args.warmup, 2000 + 100 * b)[0], 1)
+        b_tok_s, b_ms, _, _ = time_decode(b, args.steps, args.warmup, 2000 + 100 * b)
+        points[f"decode_b{b}"] = round(b_tok_s, 1)
+        points[f"decode_b{b}_ms_per_step"] = round(b_ms, 4)
+        points[f"decode_b{b}_frac"] = round(hbm_frac(b, b_ms, args.steps, args.warmup)[1], 4)
 
     # prefill of 2,048 tokens, logits at the last position
     prompt = rng.integers(0, V, size=PREFILL_TOKENS).tolist()
     pf_ms = []
-    for i in range(args.warmup + 5):
+    for i in range(args.warmup + 9):
         torch.cuda.synchronize()
         t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         t0.record()
@@ -222,36 +319,26 @@ def run_ours(args):
         runner.end([5000 + i])
         if i >= args.warmup:
             pf_ms.append(t0.elapsed_time(t1))
+    runner.check_device_errors()
     pf = sorted(pf_ms)[len(pf_ms) // 2]
     flops = prefill_flops(cfg, PREFILL_TOKENS)
 
-    # end to end through the entry point: host tokens in, host tokens out, every step
-    prompts = [rng.integers(0, V, size=CONTEXT).tolist() for _ in range(8)]
-    e2e_steps = args.steps
-    for p in prompts:
-        eng.add_request(p, SamplingParams(max_new_tokens=e2e_steps + args.warmup + 1))
-    while True:                                            # until all eight prompts are in the cache
-        out = eng.step()
-        if out is not None and len(out) == 8:
-            break
-    for _ in range(args.warmup):
-        eng.step()
-    torch.cuda.synchronize()
-    w0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        eng.step()
-    torch.cuda.synchronize()
-    e2e_ms = (time.perf_counter() - w0) * 1e3 / e2e_steps
-    h2d, d2h = eng.runner.last_h2d_bytes, 8 * 4
+    # end to end through the entry point: host tokens in, host tokens out, every step; the median window
+    e2e, seconds = [], 0.0
+    while len(e2e) < 3 or (seconds < 0.3 and len(e2e) < 200):
+        ms, h2d, _ = e2e_window(prompts, args.steps, args.warmup)
+        e2e.append(ms)
+        seconds += ms * args.steps * 1e-3
+    e2e_ms = sorted(e2e)[len(e2e) // 2]
+    d2h = 8 * 4
 
-    bytes_step = decode_bytes(cfg, 8, CONTEXT + args.warmup + args.steps // 2, kv_per_token)
-    achieved = bytes_step / (ms_step * 1e-3) / 1e9
+    achieved, frac = hbm_frac(8, ms_step, args.steps, args.warmup)
     line = {
         "metric": "decode tok/s at batch 8 (Llama 3.2 1B sizes, 1,024-token contexts)",
         "value": round(tok_s, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: seeded random weights and uniform random token ids",
-        "impl": "ours",
+        "impl": "ours", "checked": checked,
         "config": {
             "model": "Llama-3.2-1B sizes, random weights", "layers": cfg["num_hidden_layers"],
             "layers_of_named_config": full_layers, "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
@@ -259,14 +346,16 @@ def run_ours(args):
             "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "global_batch": 8,
             "seq_len": CONTEXT, "block_size": page, "kv_pool_tokens": pool_tokens, "parallelism": "none (1 GPU)",
             "l2": "inputs larger than L2 (2.5 GB of weights per step)", "peaks": pk_src,
+            "timing": f"median of {n_windows} windows of {args.steps} steps",
         },
         "e2e": {"value": round(8 / e2e_ms * 1e3, 1), "unit": "tok/s", "ms_per_step": round(e2e_ms, 4),
-                "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
+                "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
+                "frac": round(hbm_frac(8, e2e_ms, args.steps, args.warmup)[1], 4), "windows": len(e2e)},
         "gpu_launches": int(n_launch),
         "prefill": {"value": round(PREFILL_TOKENS / pf * 1e3, 1), "tokens": PREFILL_TOKENS, "ms": round(pf, 3),
                     "frac": round(flops / (pf * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
-                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+                     "frac": round(frac, 4)},
         "points": points,
         "clocks": clock_summary,
     }
@@ -405,6 +494,7 @@ def main():
     ap.add_argument("--batch", type=int, default=8, help="--mode decode: requests in the batch")
     ap.add_argument("--tokens", type=int, default=PREFILL_TOKENS, help="--mode prefill: prompt length")
     ap.add_argument("--context", type=int, default=CONTEXT, help="--mode decode: tokens each request holds")
+    ap.add_argument("--windows", type=int, default=0, help="--mode decode: 1 times three windows only (for profiling)")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":

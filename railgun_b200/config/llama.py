@@ -7,7 +7,10 @@ defaults max_position_embeddings 4096, rope_theta 10000.0, rms_norm_eps 1e-5,
 num_key_value_heads = num_attention_heads.  Keys the reference cannot read but
 the architecture needs are added: head_dim, tie_word_embeddings, rope_scaling
 (crates/vllm-models/src/llama/model.rs:49 hard-sets it to None), and
-eos_token_id as an integer or a list.
+eos_token_id as an integer or a list.  ``hidden_act``, ``attention_bias`` and
+``mlp_bias`` are read so that a checkpoint the parts cannot run is refused
+here: the feed-forward computes SiLU and nothing else
+(crates/vllm-models/src/llama/architecture.rs:82), and no projection adds a bias.
 """
 from __future__ import annotations
 
@@ -75,6 +78,12 @@ class LlamaConfig:
         nh = r.integer("num_attention_heads", minimum=1)
         nkv = r.integer("num_key_value_heads", nh, minimum=1)
         head_dim = r.integer("head_dim", None, minimum=1)
+        act = r.string("hidden_act", "silu")
+        if act not in ("silu", "swish"):
+            raise ConfigError(f"{where}: hidden_act {act!r} is not supported: the feed-forward computes 'silu'")
+        for key in ("attention_bias", "mlp_bias"):
+            if r.boolean(key, False):
+                raise ConfigError(f"{where}: {key} is true, but the projections here add no bias")
         if head_dim is None:
             if hidden % nh:
                 raise ConfigError(

@@ -85,7 +85,7 @@ extern "C" int rg_paged_attention_general(
         const int* block_table, int max_blocks, const int* req_of_token, const int* positions,
         int T, int nh, int nkv, int d, int page_size, int window, float scale, void* stream) {
     if (T <= 0) return 0;
-    if (d > 2 * ATT_THREADS || d < 1 || nh % nkv) return RG_ERR_UNSUPPORTED;
+    if (d > 2 * ATT_THREADS || d < 1 || nkv < 1 || nh < nkv || nh % nkv) return RG_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(T, nh);
     const size_t smem = (size_t)(d + ATT_THREADS + 33) * sizeof(float);

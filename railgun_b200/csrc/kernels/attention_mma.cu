@@ -669,7 +669,8 @@ extern "C" int rg_prefill_attention(const void* q, int q_stride, void* out, cons
                                     const int* positions, int nh, int nkv, int d, int page_size, int window,
                                     float scale, void* stream) {
     if (n_tiles <= 0) return 0;
-    if (d % 16 || d < 16 || d > 256 || nh % nkv || (long long)n_tiles * nh > 0x7fffffffll) return RG_ERR_UNSUPPORTED;
+    if (d % 16 || d < 16 || d > 256 || nkv < 1 || nh < nkv || nh % nkv || (long long)n_tiles * nh > 0x7fffffffll)
+        return RG_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     const float scale_log2 = scale * 1.4426950408889634f;
     const size_t smem = prefill_smem(d);
@@ -694,7 +695,7 @@ extern "C" int rg_decode_attention(const void* q, int q_stride, void* out, const
                                    int* counters, int nh, int nkv, int d, int page_size, int window, float scale,
                                    int num_splits, void* stream) {
     if (n_tokens <= 0) return 0;
-    if (d % 16 || d < 16 || d > 256 || nh % nkv || num_splits < 1) return RG_ERR_UNSUPPORTED;
+    if (d % 16 || d < 16 || d > 256 || nkv < 1 || nh < nkv || nh % nkv || num_splits < 1) return RG_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     const float scale_log2 = scale * 1.4426950408889634f;
     const size_t smem = decode_smem(d);
@@ -745,23 +746,24 @@ extern "C" int rg_decode_attention_static_scratch(
         int num_heads, int num_kv_heads, int head_dim, int page_size, int window, float scale, int num_splits,
         void* stream, char* error_text, int error_cap) {
     if (n_tokens <= 0) return 0;
-    if (num_splits < 1 || num_heads < 1 || head_dim < 1) {
-        rg_set_error(error_text, error_cap, "num_splits, num_heads and head_dim must be positive");
+    if (num_splits < 1 || num_heads < 1 || num_kv_heads < 1 || head_dim < 1) {
+        rg_set_error(error_text, error_cap, "num_splits, num_heads, num_kv_heads and head_dim must be positive");
         return RG_ERR_UNSUPPORTED;
     }
-    // part_o floats, rounded up to 64 floats (256 bytes), then part_ml
+    // part_o floats, rounded up to 64 floats (256 bytes), then part_ml likewise, then the counters
     const unsigned long long slots = (unsigned long long)n_tokens * num_heads * num_splits;
     const unsigned long long o_floats = (slots * head_dim + 63ull) / 64ull * 64ull;
     const unsigned long long ml_floats = (slots * 2ull + 63ull) / 64ull * 64ull;
     const unsigned long long n_counters = (unsigned long long)n_tokens * num_kv_heads *
-                                          ((num_heads / (num_kv_heads > 0 ? num_kv_heads : 1) + 7) / 8);
+                                          ((num_heads / num_kv_heads + 7) / 8);
     const unsigned long long need = (o_floats + ml_floats + n_counters) * sizeof(float);
     if (need > RG_STATIC_SCRATCH_BYTES) {
-        char msg[256];
+        char msg[320];
         snprintf(msg, sizeof msg,
-                 "scratch of %llu bytes needed (n_tokens %d x heads %d x splits %d x (head_dim %d + 2) floats) "
-                 "but the fixed array holds %u: use fewer splits or tokens per call",
-                 need, n_tokens, num_heads, num_splits, head_dim, (unsigned)RG_STATIC_SCRATCH_BYTES);
+                 "scratch of %llu bytes needed (n_tokens %d x heads %d x splits %d x (head_dim %d + 2) floats, each "
+                 "part rounded up to 256 bytes, and %llu counters) but the fixed array holds %u: use fewer splits "
+                 "or tokens per call",
+                 need, n_tokens, num_heads, num_splits, head_dim, n_counters, (unsigned)RG_STATIC_SCRATCH_BYTES);
         rg_set_error(error_text, error_cap, msg);
         return RG_ERR_SCRATCH_TOO_LARGE;
     }
@@ -785,16 +787,12 @@ extern "C" int rg_decode_attention_static_scratch(
         }
         base = rg_static_scratch_ptr[dev];
     }
-    // The counters start at zero (a __device__ array is zeroed when the library is loaded) and every launch
-    // leaves them at zero; they sit behind this call's partial results, which is why a call must not overlap
-    // another one.  The counters' place depends on the sizes, so they are cleared when the sizes change.
-    static unsigned long long last_counter_offset[RG_MAX_DEVICES];
+    // The counters sit behind this call's partial results, at a place that depends on the sizes, and an earlier
+    // call of other sizes may have left partial results there: every call clears its own counters first, on the
+    // caller's stream (a memset node, no allocation).  That is also why calls must not overlap on the GPU.
     int* counters = reinterpret_cast<int*>(base + o_floats + ml_floats);
-    if (last_counter_offset[dev] != o_floats + ml_floats + 1) {
-        cudaError_t ce = cudaMemsetAsync(counters, 0, n_counters * sizeof(int), (cudaStream_t)stream);
-        if (ce != cudaSuccess) { rg_set_error(error_text, error_cap, cudaGetErrorString(ce)); return (int)ce; }
-        last_counter_offset[dev] = o_floats + ml_floats + 1;
-    }
+    cudaError_t ce = cudaMemsetAsync(counters, 0, n_counters * sizeof(int), (cudaStream_t)stream);
+    if (ce != cudaSuccess) { rg_set_error(error_text, error_cap, cudaGetErrorString(ce)); return (int)ce; }
     const int code = rg_decode_attention(q, q_stride, out, kv_cache, block_table, max_blocks, rows, n_tokens,
                                          req_of_token, positions, base, base + o_floats, counters, num_heads,
                                          num_kv_heads, head_dim, page_size, window, scale, num_splits, stream);

@@ -14,9 +14,12 @@
 //
 // The scratch is a file-scope __device__ array of RG_STATIC_SCRATCH_BYTES
 // (4 MiB).  Every GPU that loads the library holds those 4 MiB until the
-// process exits.  A call needs
-//     n_tokens * num_heads * num_splits * (head_dim + 2) * 4 bytes
-// (plus up to 252 bytes of alignment); a call that needs more is refused with
+// process exits.  With S = n_tokens * num_heads * num_splits, a call needs
+//     4 * (round64(S * head_dim) + round64(S * 2)
+//          + n_tokens * num_kv_heads * ceil(num_heads / num_kv_heads / 8)) bytes,
+// round64 rounding up to a multiple of 64 (the partial outputs, the partial
+// maxima and sums, and one counter per token, key/value head and tile of 8
+// query heads).  A call that needs more is refused with
 // RG_ERR_SCRATCH_TOO_LARGE and a message, and nothing is launched.
 //
 // The first call on a device looks up the array's device address
@@ -25,13 +28,12 @@
 // capture begins.  Later calls do no set-up.
 //
 // All calls share the one array and it keeps the last call's contents.  The
-// kernels write every partial result they later read; the per-token counters
-// that tell the last block to reduce must be zero on entry, are left at zero by
-// every launch, and are cleared by the call itself (cudaMemsetAsync on the
-// caller's stream, no allocation) whenever the sizes, and with them the
-// counters' place in the array, change.  Two calls whose kernels overlap on the
-// GPU (different streams, no ordering between them) race on the array.  Order
-// them.
+// kernels write every partial result they later read; the counters that tell
+// the last block of a token to reduce must be zero on entry, and since their
+// place in the array depends on the sizes and may hold an earlier call's partial
+// results, every call clears its own counters first (cudaMemsetAsync on the
+// caller's stream, no allocation).  Two calls whose kernels overlap on the GPU
+// (different streams, no ordering between them) race on the array.  Order them.
 //
 // It calls no cudaMalloc, cudaFree or allocating library routine.
 #pragma once

@@ -355,7 +355,7 @@ extern "C" int rg_prefill_attention_tc(const void* q, int q_stride, int n_rows_t
                                        int n_tiles, const int* positions, int nh, int nkv, int d, int page_size,
                                        int window, float scale, int* err, void* stream) {
     if (n_tiles <= 0) return 0;
-    if (d != FA_D || nh % nkv || page_size % 8 || page_size > 128 || 128 % page_size || q_stride % 8 ||
+    if (d != FA_D || nkv < 1 || nh < nkv || nh % nkv || page_size % 8 || page_size > 128 || 128 % page_size || q_stride % 8 ||
         ((uintptr_t)q & 15) || ((uintptr_t)kv_cache & 15) || (long long)n_tiles * nh > 0x7fffffffll)
         return RG_ERR_UNSUPPORTED;
     CUtensorMap qm, kvm;

@@ -77,7 +77,9 @@ class Engine:
         if sampled is None:
             self.scheduler.update([], [])
             return []
-        ops.tc_gemm_check()                 # the tokens are on the host: the step has finished
+        # the tokens are on the host, so the step has finished: did a kernel give up a wait or meet a bad position?
+        # (decode graphs bring their flag back with the tokens, see _decode_step)
+        ops.tc_gemm_check()
         self.scheduler.update(wanted, sampled)
         return list(zip(wanted, sampled.tolist()))
 
@@ -117,7 +119,9 @@ class Engine:
         if logits is None:
             return wanted, None
         params = [self._params[r] for r in wanted]
-        return wanted, self.sampler.sample(logits, params, [self.scheduler.num_generated(r) for r in wanted])
+        sampled = self.sampler.sample(logits, params, [self.scheduler.num_generated(r) for r in wanted])
+        self.runner.check_device_errors()
+        return wanted, sampled
 
     def _sampling_of(self, ids, wanted, params) -> dict:
         """The requests' sampling parameters as arrays, one entry per request: the constant ones are kept while
@@ -167,7 +171,8 @@ class Engine:
         EngineStepResponse, crates/vllm-engine/src/engine.rs:64-76); the last
         response of a request has ``is_finished`` and its finish reason.  A
         request that ends without a token (an error, an abort) gets one
-        response without a token."""
+        response without a token.  The engine forgets a request once its last
+        response has been made."""
         if prompt_ids and isinstance(prompt_ids[0], (int, np.integer)):
             prompt_ids = [prompt_ids]
         if params is None or isinstance(params, SamplingParams):
@@ -180,16 +185,22 @@ class Engine:
             done = [r for r in self.scheduler.finished() if r in open_ids]
             if made is None and not done and not self.scheduler.preempted():
                 raise RuntimeError("the scheduler can make no progress: no request fits the cache")
+            out = []
             for rid, token in made or ():
                 if rid in open_ids:
                     ended = rid in done
-                    yield StepResponse(rid, token, ended, self.scheduler.finish_reason(rid) if ended else None)
+                    out.append(StepResponse(rid, token, ended, self.scheduler.finish_reason(rid) if ended else None))
                     if ended:
                         open_ids.discard(rid)
             for rid in done:
                 if rid in open_ids:                                  # ended in this step without a token
                     open_ids.discard(rid)
-                    yield StepResponse(rid, None, True, self.scheduler.finish_reason(rid))
+                    out.append(StepResponse(rid, None, True, self.scheduler.finish_reason(rid)))
+            for r in out:
+                if r.is_finished:
+                    self.scheduler.forget(r.request_id)
+                    self._params.pop(r.request_id, None)
+            yield from out
 
     # ---- the call a user makes --------------------------------------------------------------
     def generate(self, prompt_ids, params=None) -> list:

@@ -13,8 +13,6 @@ the tokens and copies them out), and the step after such a step can be
 launched before its tokens are known (``decode_follow``); large steps whose
 packed layout repeats replay a graph captured for that layout
 (``_step_shape_graph``); everything else launches its kernels one by one.
-``decode_state`` / ``decode_step`` run several decode steps without the host
-in between (what the benchmark's device-side number times).
 """
 from __future__ import annotations
 
@@ -109,8 +107,11 @@ class StaticDecodeBatch:
         n_ints = self.sampling_off + 7 * B
         self.host = torch.zeros(n_ints, dtype=torch.int32, pin_memory=True)
         self.host_np = self.host.numpy()
-        self.host_out = torch.zeros(B, dtype=torch.int32, pin_memory=True)     # the step's greedy tokens, copied by the graph
+        # the step's tokens and, behind them, the flag that a kernel raises for a position outside its table:
+        # one copy by the graph brings both to the host
+        self.host_out = torch.zeros(B + 1, dtype=torch.int32, pin_memory=True)
         self.host_out_np = self.host_out.numpy()
+        self.out_dev = torch.zeros(B + 1, dtype=torch.int32, device=dev)
         self.dev = torch.zeros(n_ints, dtype=torch.int32, device=dev)
         seg = lambda i: self.dev[i * B:(i + 1) * B]
         ar = torch.arange(B + 1, dtype=torch.int32, device=dev)
@@ -123,12 +124,18 @@ class StaticDecodeBatch:
             slot_mapping=[seg(5 + g) for g in range(G)],
             block_table=[self.dev[tables_off + g * B * MB:tables_off + (g + 1) * B * MB].view(B, MB)
                          for g in range(G)],
-            err_flag=runner.err_flag, decode_only=True)
+            err_flag=self.out_dev[B:], decode_only=True)
         self.sampling = sampling_views(self.dev, self.sampling_off, B)        # device views of the sampling parameters
-        self.sampled = torch.zeros(B, dtype=torch.int32, device=dev)           # the tokens the last step chose
+        self.sampled = self.out_dev[:B]                                         # the tokens the last step chose
         self.step_graphs = {}          # with sampling parameters or greedy -> CapturedStep
         self.follow = [None, None]     # FollowStep: the same step fed with ``sampled`` instead of host tokens
         self.in_flight = None          # an event after the last replay that reads ``host`` and writes ``host_out``
+
+    def raise_if_flagged(self, host_out_np) -> None:
+        if host_out_np[self.B]:
+            self.out_dev[self.B:].zero_()
+            host_out_np[self.B] = 0
+            raise RuntimeError("a kernel met a position outside its table")
 
     def wait_until_reusable(self) -> None:
         """The pinned buffers may be written again once the last replay that copies them has run."""
@@ -169,16 +176,17 @@ class FollowStep:
         self.static = static
         self.host_in = torch.zeros(static.host.numel(), dtype=torch.int32, pin_memory=True)
         self.host_in_np = self.host_in.numpy()
-        self.host_out = torch.zeros(static.B, dtype=torch.int32, pin_memory=True)
+        self.host_out = torch.zeros(static.B + 1, dtype=torch.int32, pin_memory=True)
         self.host_out_np = self.host_out.numpy()
         self.done = torch.cuda.Event()
         self.captured = {}             # with sampling parameters or greedy -> CapturedStep
         self.ids = None                # the requests of the launched step, in row order
 
     def tokens(self) -> np.ndarray:
-        """The launched step's greedy tokens, one per row (waits for the step)."""
+        """The launched step's tokens, one per row (waits for the step; raises if a kernel of it flagged an error)."""
         self.done.synchronize()
-        return self.host_out_np
+        self.static.raise_if_flagged(self.host_out_np)
+        return self.host_out_np[:self.static.B]
 
 
 class ShapeGraph:
@@ -194,15 +202,6 @@ class ShapeGraph:
 class CapturedStep:
     def __init__(self, graph, logits, sampled, launches):
         self.graph, self.logits, self.sampled, self.launches = graph, logits, sampled, launches
-
-
-class DecodeState:
-    """Several decode steps in a row on the device for a fixed set of requests."""
-
-    def __init__(self, ids, static, captured, out_tokens, step_counter, max_steps):
-        self.ids, self.static, self.captured = ids, static, captured
-        self.out_tokens, self.step_counter, self.max_steps = out_tokens, step_counter, max_steps
-        self.steps_done = 0
 
 
 class ModelRunner:
@@ -331,9 +330,14 @@ class ModelRunner:
                 self.alloc.release(rid)
 
     def check_device_errors(self) -> None:
+        """Raise if a kernel gave up a bounded wait or met a position outside its table since the last check
+        (synchronises).  Steps replayed from decode graphs carry their own flag, which also travels to the host
+        with their tokens."""
         ops.tc_gemm_check()
-        if int(self.err_flag.item()):
-            self.err_flag.zero_()
+        flags = [self.err_flag] + [st.out_dev[st.B:] for st in self._static.values()]
+        if int(torch.cat(flags).sum().item()):
+            for f in flags:
+                f.zero_()
             raise RuntimeError("a kernel met a position outside its table")
 
     # ---- decode steps from captured graphs -----------------------------------------------------------
@@ -348,41 +352,34 @@ class ModelRunner:
             self._static[key] = StaticDecodeBatch(self, *key)
         return self._static[key]
 
-    def _capture(self, static: StaticDecodeBatch, loop=None, follow: FollowStep | None = None,
+    def _capture(self, static: StaticDecodeBatch, follow: FollowStep | None = None,
                  sampling: bool = False) -> CapturedStep:
-        """Capture one decode step over the static buffers: forward, greedy
-        tokens and, with ``loop`` = (out_tokens, step_counter), the feedback of
-        those tokens so that the next replay is the next step.  With ``follow``
-        the step takes its token ids from the step before it on the device and
-        everything else from ``follow``'s pinned buffer.  With ``sampling`` the
-        tokens are drawn with the rows' parameters in the static buffer
-        (temperature 0: greedy) instead of the plain argmax."""
+        """Capture one decode step over the static buffers: the copy of its
+        packed inputs from pinned memory, the forward pass, the choice of the
+        tokens and their copy to pinned memory, so that one graph launch and one
+        wait are all the host does.  With ``follow`` the step takes its token
+        ids from the step before it on the device and everything else from
+        ``follow``'s pinned buffer.  With ``sampling`` the tokens are drawn with
+        the rows' parameters in the static buffer (temperature 0: greedy)
+        instead of the plain argmax."""
         counter = ops.launch_counter()
         B = static.B
 
         def body():
             if follow is not None:
                 static.dev[B:].copy_(follow.host_in[B:], non_blocking=True)
-            elif loop is None:
-                # a single step carries its own transfers: the packed inputs from pinned memory first, the greedy
-                # tokens to pinned memory last, so that one graph launch and one wait are all the host does
+            else:
                 static.dev.copy_(static.host, non_blocking=True)
             # a following step reads its token ids where the step before left its greedy tokens
             batch = static.batch if follow is None else dataclasses.replace(static.batch, token_ids=static.sampled)
             logits = self.model.forward(batch, self.views)
-            if loop is not None:
-                sampled = ops.argmax(logits)
-                b = static.batch
-                ops.decode_advance(b.token_ids, sampled, b.positions, b.context_lens, b.start_pos,
-                                   b.slot_mapping[0], b.block_table[0], self.page_sizes[0], loop[0], loop[1])
+            if sampling:
+                sp = static.sampling
+                sampled = ops.sample(logits, sp["temperature"], sp["top_k"], sp["top_p"], sp["seed"],
+                                     sp["counter"], out=static.sampled)
             else:
-                if sampling:
-                    sp = static.sampling
-                    sampled = ops.sample(logits, sp["temperature"], sp["top_k"], sp["top_p"], sp["seed"],
-                                         sp["counter"], out=static.sampled)
-                else:
-                    sampled = ops.argmax(logits, out=static.sampled)
-                (follow or static).host_out.copy_(sampled, non_blocking=True)
+                sampled = ops.argmax(logits, out=static.sampled)
+            (follow or static).host_out.copy_(static.out_dev, non_blocking=True)
             return logits, sampled
 
         # a first run outside capture, so that libraries set themselves up before it
@@ -466,6 +463,7 @@ class ModelRunner:
             return None
         static, R = self._greedy_host
         static.in_flight.synchronize()
+        static.raise_if_flagged(static.host_out_np)
         return static.host_out_np[:R].copy()
 
     def decode_follow(self, ids: np.ndarray, after, sampling=None) -> FollowStep | None:
@@ -512,38 +510,3 @@ class ModelRunner:
         self.last_h2d_bytes = (static.host.numel() - B) * 4
         f.ids = ids.copy()
         return f
-
-    def decode_state(self, request_ids, first_tokens, max_steps: int) -> DecodeState:
-        """Prepare ``max_steps`` decode steps that run on the device without
-        the host in between, for requests already in the cache; their pages
-        are reserved now.  Greedy sampling."""
-        ids = np.asarray(request_ids, dtype=np.int64)
-        R = len(ids)
-        ctx = [self.alloc.num_computed(int(r)) for r in ids]
-        if max(ctx) + max_steps > self.model.spec.max_position:
-            raise BatchError("decode_state: the steps would run beyond max_position_embeddings")
-        for r, c in zip(ids, ctx):
-            self.alloc.reserve(int(r), c + max_steps)
-        static = self._static_for(R, max(ctx) + max_steps)
-        self.alloc.pack_decode(ids, static.B, static.MB, static.host_np[static.B:])
-        static.host_np[:R] = np.asarray(first_tokens, dtype=np.int32)
-        static.host_np[R:static.B] = 0
-        static.upload()
-        out_tokens = torch.zeros((max_steps, static.B), dtype=torch.int32, device=self.device)
-        step_counter = torch.zeros(1, dtype=torch.int32, device=self.device)
-        cap = self._capture(static, loop=(out_tokens, step_counter))
-        step_counter.zero_()
-        return DecodeState(ids, static, cap, out_tokens, step_counter, max_steps)
-
-    def decode_step(self, state: DecodeState) -> None:
-        if state.steps_done >= state.max_steps:
-            raise RuntimeError("decode_state: no reserved steps are left")
-        state.captured.graph.replay()
-        ops.launch_counter().value += state.captured.launches
-        state.steps_done += 1
-
-    def decode_finish(self, state: DecodeState) -> np.ndarray:
-        """Tell the cache what the device did; returns the generated tokens [steps, requests]."""
-        self.alloc.advance(state.ids, state.steps_done)
-        done, state.steps_done, state.max_steps = state.steps_done, 0, 0
-        return state.out_tokens[:done, :len(state.ids)].cpu().numpy()

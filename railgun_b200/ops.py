@@ -70,7 +70,6 @@ class LaunchCounter:
 
 
 _COUNTER = LaunchCounter()
-_LAUNCHES_PER_CALL = {"rg_decode_advance": 2}
 _fn_cache: dict = {}
 
 
@@ -95,7 +94,7 @@ def _fn(lib_name: str, fn_name: str):
         fn = getattr(lib, fn_name)
         fn.restype = c_int
         _fn_cache[fn_name] = fn
-    _COUNTER.value += _LAUNCHES_PER_CALL.get(fn_name, 1)
+    _COUNTER.value += 1
     return fn
 
 
@@ -667,21 +666,6 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k, top_p, seed: 
     _ok(_fn("sampling", "rg_sample")(_ptr(logits), c_int(rows), c_int(V), _ptr(temperature), _ptr(top_k),
                                      _ptr(top_p), _ptr(seed), _ptr(counter), _ptr(out), _stream()), "sample")
     return out
-
-
-def decode_advance(token_ids, sampled, positions, context_lens, start_pos, slots, block_table, page_size: int,
-                   out_tokens, step_counter) -> None:
-    """After a decode step on the device: feed the sampled tokens back, move
-    every request one position on and look up the new slots."""
-    for name, t in (("token_ids", token_ids), ("sampled", sampled), ("positions", positions),
-                    ("context_lens", context_lens), ("start_pos", start_pos), ("slots", slots),
-                    ("block_table", block_table), ("out_tokens", out_tokens), ("step_counter", step_counter)):
-        _check(t, name, torch.int32)
-    B = token_ids.numel()
-    _ok(_fn("decode_advance", "rg_decode_advance")(
-        _ptr(token_ids), _ptr(sampled), _ptr(positions), _ptr(context_lens), _ptr(start_pos), _ptr(slots),
-        _ptr(block_table), c_int(block_table.shape[1]), c_int(page_size), c_int(B), _ptr(out_tokens),
-        _ptr(step_counter), c_int(out_tokens.shape[0]), _stream()), "decode_advance")
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype=None) -> torch.Tensor:

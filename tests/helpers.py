@@ -7,7 +7,9 @@ from pathlib import Path
 
 import numpy as np
 
-# Two tiny configurations that differ in every size and option.
+# Tiny configurations that differ in every size and option.  A and B have head sizes 16 and 32; C has the head
+# size 64 (with more query features than the hidden size) that selects the tcgen05 attention kernel and the exact
+# head-size specialisations of the other kernels.
 TINY_A = dict(
     architectures=["LlamaForCausalLM"], hidden_size=64, num_attention_heads=4, num_key_value_heads=2,
     head_dim=16, num_hidden_layers=2, intermediate_size=176, vocab_size=256, rope_theta=10000.0,
@@ -18,7 +20,13 @@ TINY_B = dict(
     rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
                       original_max_position_embeddings=64),
     tie_word_embeddings=False, rms_norm_eps=1e-6, max_position_embeddings=512)
-TINY = {"A": (TINY_A, 0, 16), "B": (TINY_B, 2, 8)}      # config, weight seed, page size
+TINY_C = dict(
+    architectures=["LlamaForCausalLM"], hidden_size=192, num_attention_heads=4, num_key_value_heads=2,
+    head_dim=64, num_hidden_layers=2, intermediate_size=320, vocab_size=384, rope_theta=50000.0,
+    rope_scaling=dict(rope_type="llama3", factor=4.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                      original_max_position_embeddings=128),
+    tie_word_embeddings=True, rms_norm_eps=2e-5, max_position_embeddings=1024)
+TINY = {"A": (TINY_A, 0, 16), "B": (TINY_B, 2, 8), "C": (TINY_C, 4, 16)}      # config, weight seed, page size
 
 _made: dict = {}
 

@@ -49,6 +49,9 @@ def test_head_dim_key_wins_over_quotient():
     ({"rms_norm_eps": -1.0}, "rms_norm_eps"),
     ({"tie_word_embeddings": "yes"}, "tie_word_embeddings"),
     ({"head_dim": 15}, "even"),
+    ({"hidden_act": "gelu"}, "hidden_act"),
+    ({"attention_bias": True}, "attention_bias"),
+    ({"mlp_bias": True}, "mlp_bias"),
 ])
 def test_bad_configs_are_refused(patch, word):
     data = dict(helpers.TINY_A)
@@ -59,7 +62,7 @@ def test_bad_configs_are_refused(patch, word):
 
 
 def test_round_trip_through_config_json(tmp_path):
-    for name in ("A", "B"):
+    for name in ("A", "B", "C"):
         cfg = LlamaConfig.from_dict(helpers.TINY[name][0])
         (tmp_path / "config.json").write_text(json.dumps(cfg.to_dict()))
         arch, back = load_config(tmp_path)
@@ -95,7 +98,7 @@ def test_registering_another_architecture(tmp_path):
 def test_spec_holds_only_config_numbers():
     """Every size in the model description comes from the configuration."""
     from railgun_b200.models.llama import llama_model_spec
-    for name in ("A", "B"):
+    for name in ("A", "B", "C"):
         raw = helpers.TINY[name][0]
         spec = llama_model_spec(LlamaConfig.from_dict(raw))
         assert len(spec.layers) == raw["num_hidden_layers"]

@@ -186,6 +186,68 @@ def test_steps_launched_ahead_change_nothing(dtype, sampled):
     assert sampled or dtype == "bfloat16" or base[0].token_ids == plain.greedy(prompts[0], 30)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_many_live_requests(name, dtype):
+    """Forty-eight requests, up to 64 seats (the reference's default is 256,
+    crates/vllm-scheduler/src/scheduler.rs:47-58): decode steps of 17 to 48 rows
+    take the library products, SiLU-mul on interleaved storage, the larger batch
+    buckets and steps launched ahead at those sizes.  Greedy and sampled
+    requests, prompts of mixed length cut into portions beside decoding
+    requests, and a pool small enough that requests are preempted.  Every token
+    is checked against the plain implementation, teacher-forced; in 32-bit the
+    outputs also equal those of the same requests run one at a time."""
+    from railgun_b200.engine.engine import Engine
+    from railgun_b200.engine.request import SamplingParams
+    cfg, _, page = helpers.TINY[name]
+    rng = np.random.default_rng(31)
+    lengths = [int(n) for n in rng.integers(2, 70, size=48)]
+    prompts = helpers.prompts(cfg["vocab_size"], lengths, seed=32)
+    params = []
+    for i in range(48):
+        n_new = int(rng.integers(6, 24))
+        if i % 3 == 1:
+            params.append(SamplingParams(max_new_tokens=n_new, temperature=0.8, seed=1000 + i))
+        elif i % 3 == 2:
+            params.append(SamplingParams(max_new_tokens=n_new, temperature=1.0, top_k=12, top_p=0.9, seed=2000 + i))
+        else:
+            params.append(SamplingParams(max_new_tokens=n_new))
+    blocks = 1400 // page
+    eng = Engine(helpers.model_dir(name), dtype=dtype, block_size=page, num_gpu_blocks=blocks, max_num_seqs=64,
+                 max_num_batched_tokens=256, max_model_len=128)
+    widest = 0
+    rids = [eng.add_request(p, sp) for p, sp in zip(prompts, params)]
+    while eng.has_unfinished():
+        made = eng.step()
+        widest = max(widest, len(made or ()))
+    outs = [eng.collect(r) for r in rids]
+    assert widest > 32, f"at most {widest} requests were live in a step"
+    assert sum(o.num_preemptions for o in outs) >= 1
+    eng.runner.alloc.check()
+    assert eng.stats()["num_free_blocks"] == blocks
+    plain = P.PlainLlama(helpers.model_dir(name))
+    tol = 1e-4 if dtype == "float32" else 6e-2
+    for p, sp, o in zip(prompts, params, outs):
+        assert o.finish_reason == "max_tokens" and len(o.token_ids) == sp.max_new_tokens
+        logits = plain.forward(list(p) + o.token_ids)
+        for k, t in enumerate(o.token_ids):
+            row = logits[len(p) - 1 + k]
+            if sp.temperature == 0.0:
+                assert row[t] >= row.max() - tol * np.abs(logits).max(), f"token {k} ({t}) is not the argmax"
+            else:
+                # the drawn token's interval of the plain distribution holds the draw's uniform number
+                pr = P.filtered_probs(row, sp.temperature, sp.top_k, sp.top_p)
+                c = np.cumsum(pr)
+                u = P.uniform_from_counter(sp.seed, k)
+                slack = 1e-4 if dtype == "float32" else 5e-2
+                assert c[t] - pr[t] - slack <= u <= c[t] + slack, f"token {k} ({t}) is not the plain draw"
+    if dtype == "float32":
+        one = Engine(helpers.model_dir(name), dtype=dtype, block_size=page, num_gpu_blocks=64, max_num_seqs=1,
+                     max_model_len=128)
+        for p, sp, o in list(zip(prompts, params, outs))[::5]:
+            assert one.generate([p], sp)[0].token_ids == o.token_ids
+
+
 def test_stream_gives_the_tokens_of_generate():
     from railgun_b200.engine.engine import Engine
     from railgun_b200.engine.request import SamplingParams

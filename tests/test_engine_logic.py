@@ -12,7 +12,7 @@ import pytest
 from railgun_b200.cache.manager import PageAllocator
 from railgun_b200.engine.engine import Engine
 from railgun_b200.engine.request import SamplingParams
-from railgun_b200.engine.scheduler import Scheduler, SchedulerConfig
+from railgun_b200.engine.scheduler import Scheduler, SchedulerConfig, SchedulerError
 
 
 def answer(rid: int, position: int) -> int:
@@ -41,6 +41,9 @@ class StandInRunner:
 
     def greedy_tokens_host(self):
         return self._host
+
+    def check_device_errors(self):
+        pass
 
     def decode_follow(self, ids, after, sampling=None):
         ahead = 0 if after is None else 1
@@ -171,7 +174,7 @@ def test_nothing_is_launched_ahead_of_a_last_token():
 
 def test_stream_yields_every_token_as_its_step_ends():
     """``Engine.stream``: one response per generated token, in step order, the last one of a request
-    marked finished with its reason; the finished requests stay collectable."""
+    marked finished with its reason; afterwards the engine has forgotten the requests."""
     eng = make_engine(True)
     prompts = [[3, 4, 5], [9] * 7, [1]]
     stop = expected_output(2, prompts[1], 9)[4]
@@ -186,7 +189,10 @@ def test_stream_yields_every_token_as_its_step_ends():
     assert got[1] == expected_output(1, prompts[0], 6) and last[1] == "max_tokens"
     assert got[2] == expected_output(2, prompts[1], 9, [stop]) and last[2] == "stop_token" and got[2][-1] == stop
     assert got[3] == expected_output(3, prompts[2], 2) and last[3] == "max_tokens"
-    assert eng.collect(2).token_ids == got[2] and not eng.has_unfinished()
+    # the engine keeps nothing of a streamed request once its last response is out
+    assert not eng.has_unfinished() and list(eng.scheduler.finished()) == [] and eng._params == {}
+    with pytest.raises(SchedulerError):
+        eng.collect(2)
     eng.runner.alloc.check()
 
 

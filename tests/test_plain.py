@@ -69,7 +69,7 @@ def test_attention_against_loops_with_groups_and_window():
 
 
 def test_model_is_causal_and_tied_or_untied():
-    for name in ("A", "B"):
+    for name in ("A", "B", "C"):
         cfg = helpers.TINY[name][0]
         m = P.PlainLlama(helpers.model_dir(name))
         ids = helpers.prompts(cfg["vocab_size"], [12], seed=4)[0]

@@ -1,7 +1,9 @@
 """Trace replay on the GPU against the plain implementation: every request
 whole, with the last 32 tokens decoded one by one, in portions of changing
 size, and mixed with other requests in a pool so small that pages are used
-again; in 32-bit and in bfloat16, for both tiny configurations."""
+again; in 32-bit and in bfloat16, for every tiny configuration (the third has
+head size 64 and prompts of several hundred tokens, which the tcgen05
+attention kernel with its 128-row tiles takes)."""
 import json
 import os
 import subprocess
@@ -15,7 +17,11 @@ from plain_llama import PlainLlama
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"A": [5, 17, 33, 70, 100, 131, 64, 48], "B": [1, 9, 40, 63, 100, 200, 77, 129]}
+LENGTHS = {"A": [5, 17, 33, 70, 100, 131, 64, 48], "B": [1, 9, 40, 63, 100, 200, 77, 129],
+           "C": [300, 392, 400, 129, 257, 64, 395, 390]}
+# portion sizes of the "portions" and "mixed" cuts; C's cross the 64- and 128-row tiles of the attention kernels
+PORTIONS = {"C": (130, 2, 64, 7, 128, 3, 65, 2, 33, 129)}
+MIXED = {"C": (5, 1, 2, 70, 1, 1, 3, 140, 1, 2, 128, 17)}
 # Largest absolute logit difference allowed, as a fraction of the largest
 # absolute logit of the row's sequence.  32-bit differs from the 64-bit plain
 # implementation by accumulated rounding only; bfloat16 rounds activations to
@@ -34,15 +40,15 @@ def oracle(name):
     return _oracle_cache[name]
 
 
-def make_trace(mode, reqs):
+def make_trace(mode, reqs, name="A"):
     if mode == "whole":
         return helpers.trace_whole(reqs)
     if mode == "tail":
         return helpers.trace_tail_decode(reqs, 32)
     if mode == "portions":
-        return helpers.trace_portions(reqs)
+        return helpers.trace_portions(reqs, **({"sizes": PORTIONS[name]} if name in PORTIONS else {}))
     if mode == "mixed":
-        return helpers.trace_mixed(reqs, max_live=4, seed=5)
+        return helpers.trace_mixed(reqs, max_live=4, seed=5, **({"sizes": MIXED[name]} if name in MIXED else {}))
     raise ValueError(mode)
 
 
@@ -63,19 +69,20 @@ def compare(rows, reqs, logits, dtype, what):
 
 @pytest.mark.parametrize("mode", ["whole", "tail", "portions", "mixed"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_replay_matches_plain(name, dtype, mode, tmp_path):
     from railgun_b200.engine.runner import ModelRunner
     from railgun_b200.replay import Replayer
     cfg, _, page = helpers.TINY[name]
     reqs, logits = oracle(name)
-    steps = make_trace(mode, reqs)
+    steps = make_trace(mode, reqs, name)
     max_tokens = helpers.peak_tokens(steps, 64)
     runner = ModelRunner(helpers.model_dir(name), dtype=dtype, page_size=page, max_tokens=max_tokens,
                          max_requests=4)
     rp = Replayer(runner, tmp_path)
     for s in steps:
         rp.feed(s)
+    runner.check_device_errors()
     runner.alloc.check()
     assert runner.alloc.num_requests() == 0
     rows = helpers.collect(steps, tmp_path, cfg["vocab_size"])
@@ -84,7 +91,7 @@ def test_replay_matches_plain(name, dtype, mode, tmp_path):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_steps_of_a_repeated_layout_replay_a_graph(name, dtype, tmp_path):
     """Large steps whose packed layout repeats are captured the second time and replayed from then on.  With
     the threshold lowered to two tokens, equal portions of several requests (alone, and beside single tokens of
@@ -94,7 +101,8 @@ def test_steps_of_a_repeated_layout_replay_a_graph(name, dtype, tmp_path):
     from railgun_b200.replay import Replayer
     cfg, _, page = helpers.TINY[name]
     reqs, logits = oracle(name)
-    names = [k for k, v in reqs.items() if len(v) >= 63][:4]
+    P = 130 if name == "C" else 21                               # C: a tile of 128 rows and one of 2 in every portion
+    names = [k for k, v in reqs.items() if len(v) >= 3 * P][:4]
     decoder = next(k for k, v in reqs.items() if len(v) >= 40 and k not in names)
     steps, n = [], 0
     # the decoder's prompt but for its last 12 tokens, then it decodes beside the others' portions
@@ -104,9 +112,9 @@ def test_steps_of_a_repeated_layout_replay_a_graph(name, dtype, tmp_path):
     n += 1
     fed = len(dt) - 12
     for r in names:
-        toks = reqs[r][:63]                                      # three portions of 21 tokens: the same layout 12 times
+        toks = reqs[r][:3 * P]                                   # three portions of P tokens: the same layout 12 times
         for p in range(3):
-            entries = [{"id": r, "tokens": toks[21 * p:21 * p + 21], "want": list(range(21))}]
+            entries = [{"id": r, "tokens": toks[P * p:P * p + P], "want": list(range(P))}]
             if fed < len(dt):
                 entries.append({"id": decoder, "tokens": [dt[fed]], "want": [0]})
                 fed += 1
@@ -124,7 +132,7 @@ def test_steps_of_a_repeated_layout_replay_a_graph(name, dtype, tmp_path):
     runner.check_device_errors()
     runner.alloc.check()
     rows = helpers.collect(steps, tmp_path, cfg["vocab_size"])
-    some = {r: reqs[r][:63] for r in names}
+    some = {r: reqs[r][:3 * P] for r in names}
     some[decoder] = dt
     ref = {r: logits[r][:len(t)] for r, t in some.items()}
     # rows of a prefix do not depend on what follows it, so the prefix's reference rows are the request's own
@@ -143,17 +151,17 @@ def test_pages_are_used_again(tmp_path):
     runner = ModelRunner(helpers.model_dir("B"), dtype="float32", page_size=page, max_tokens=max_tokens,
                          max_requests=4)
     rp = Replayer(runner, tmp_path)
-    seen_pages, reused = set(), False
+    held, freed, reused = {}, set(), set()
     for s in steps:
         rp.feed(s)
-        for rid in list(rp._ids.values()):
-            for p in runner.alloc.block_table(rid, 0):
-                pass
-        live = {int(p) for rid in rp._ids.values() for p in runner.alloc.block_table(rid, 0)}
-        ended_pages = seen_pages - live
-        seen_pages |= live
-        reused = reused or bool(ended_pages)
-    assert reused
+        now = {rid: {int(p) for p in runner.alloc.block_table(rid, 0)} for rid in rp._ids.values()}
+        for rid, pages in now.items():
+            reused |= (pages - held.get(rid, set())) & freed     # a page handed out now that an ended request gave back
+        for rid, pages in held.items():
+            if rid not in now:
+                freed |= pages
+        held = now
+    assert reused, "no page that an ended request gave back was handed to a later request"
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

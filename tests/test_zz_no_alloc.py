@@ -7,7 +7,9 @@ allocation could stall the device.  For them the library exports
 inside the library.  This test calls it through its exported C symbol, the
 way such a caller would, twice in a row with different inputs, and checks it
 against the ordinary entry point (``ops.decode_attention``, which allocates
-its scratch); then that it refuses work that would not fit the array.
+its scratch) and against a 64-bit restatement of the attention formula; then
+a sequence of calls whose counters land where an earlier, larger call left
+partial results; then that it refuses work that would not fit the array.
 
 The file's name makes pytest collect it last, so a run that stops at the first
 failure has already run every other test.
@@ -69,6 +71,49 @@ def test_static_scratch_entry_point_matches_the_allocating_one():
         assert torch.cuda.memory_allocated() == before
         err = (got.double() - want.double()).abs().max() / want.double().abs().max()
         assert err < 1e-2, f"call {seed}: relative error {err:.3e}"      # the tolerance of the kernel tests
+        ref = _reference(q, kv, bt, pos, nh, nkv, d, page)
+        err = (got.double().cpu() - ref).abs().max() / ref.abs().max()
+        assert err < 1e-2, f"call {seed}: relative error {err:.3e} against the 64-bit formula"
+
+
+def _reference(q, kv, bt, pos, nh, nkv, d, page):
+    """softmax(q . k / sqrt(d)) v over each request's keys, in 64-bit, from the paged cache."""
+    q, kv = q.double().cpu(), kv.double().cpu()
+    out = torch.zeros(q.shape[0], nh, d, dtype=torch.float64)
+    for r in range(q.shape[0]):
+        idx = torch.arange(int(pos[r]) + 1)
+        pages = bt[r].cpu().long()[idx // page]
+        K, V = kv[pages, 0, :, idx % page, :], kv[pages, 1, :, idx % page, :]
+        for h in range(nh):
+            kh = h // (nh // nkv)
+            p = torch.softmax((K[:, kh, :] @ q[r, h * d:(h + 1) * d]) * d ** -0.5, dim=0)
+            out[r, h] = p @ V[:, kh, :]
+    return out.reshape(q.shape[0], nh * d)
+
+
+def test_static_scratch_counters_do_not_inherit_an_earlier_calls_results():
+    """A large call fills the array with partial results; the calls after it are small, need the same number of
+    partial results as one another but different numbers of counters (8 key/value heads, then 32; one token with
+    4 splits, then two tokens with 2 splits), so their counters lie where the large call wrote.  Every output row
+    must be written (they start as NaN) and match the 64-bit formula."""
+    from railgun_b200 import native
+    lib = native.load("attention_mma")
+    cases = [(40, [300] * 40, 32, 8, 64, 16, 7),                  # large: 40 x 32 x 7 x 66 floats = 2.4 MB
+             (2, [500, 90], 32, 8, 64, 16, 2),
+             (2, [260, 41], 32, 32, 64, 16, 2),                   # as many partial results, four times the counters
+             (1, [700], 32, 8, 64, 16, 4),
+             (2, [130, 700], 32, 8, 64, 16, 2)]
+    for seed, (n_req, ctx, nh, nkv, d, page, splits) in enumerate(cases):
+        q, kv, bt, req, pos = _case(40 + seed, n_req, ctx, nh, nkv, d, page)
+        got = torch.full((n_req, nh * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+        code, msg = _call_static(lib, q, got, kv, bt, req, pos, nh, nkv, d, page, splits)
+        torch.cuda.synchronize()
+        assert code == 0, msg
+        assert not torch.isnan(got).any(), f"call {seed}: rows were left unwritten"
+        if n_req <= 2:
+            want = _reference(q, kv, bt, pos, nh, nkv, d, page)
+            err = (got.double().cpu() - want).abs().max() / want.abs().max()
+            assert err < 1e-2, f"call {seed}: relative error {err:.3e}"
 
 
 def test_static_scratch_entry_point_refuses_what_does_not_fit():
@@ -81,3 +126,5 @@ def test_static_scratch_entry_point_refuses_what_does_not_fit():
     torch.cuda.synchronize()
     assert code == 10002 and "fixed array holds 4194304" in msg
     assert not out.any()                                                # nothing was launched
+    code, msg = _call_static(lib, q, out, kv, bt, req, pos, nh, 0, d, page, 2)     # no key/value heads: refused
+    assert code == 10001 and "num_kv_heads" in msg
