@@ -16,7 +16,9 @@ packed layout repeats replay a graph captured for that layout
 """
 from __future__ import annotations
 
+import contextlib
 import dataclasses
+import gc
 
 import numpy as np
 import torch
@@ -39,6 +41,21 @@ _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.
 # (below it the launches are few and short; single tokens have their own graphs), and so many layouts are kept.
 SHAPE_GRAPH_MIN_TOKENS = 256
 SHAPE_GRAPHS_KEPT = 4
+
+
+@contextlib.contextmanager
+def capture(graph):
+    """``torch.cuda.graph(graph)`` with Python's cyclic garbage collector held off: a collection in the middle of
+    a capture may free a page-locked host buffer of an earlier step, and freeing one records an event on the
+    stream that used it, which is not allowed on a capturing stream and invalidates the capture."""
+    was_enabled = gc.isenabled()
+    gc.disable()
+    try:
+        with torch.cuda.graph(graph):
+            yield
+    finally:
+        if was_enabled:
+            gc.enable()
 
 
 def parse_dtype(name):
@@ -315,7 +332,7 @@ class ModelRunner:
         counter = ops.launch_counter()
         n0 = counter.value
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
+        with capture(graph):
             logits = self.model.forward(batch, self.views)
         launches = counter.value - n0
         counter.value = n0
@@ -394,7 +411,7 @@ class ModelRunner:
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         n0 = counter.value
-        with torch.cuda.graph(graph):
+        with capture(graph):
             logits, sampled = body()
         launches = counter.value - n0
         counter.value = n0

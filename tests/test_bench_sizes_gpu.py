@@ -27,10 +27,12 @@ BENCH_SIZES = dict(
     tie_word_embeddings=True, rms_norm_eps=1e-5, max_position_embeddings=131072, torch_dtype="bfloat16")
 PAGE = 16
 LENGTHS = [2200, 300, 150, 40, 1100, 77]
-# bfloat16 against the 32-bit path, as a fraction of the largest absolute logit of the request.  Measured on a
-# B200 over every cut below: the worst row differs by 5.6e-3 (bfloat16 rounds activations to 8 bits of mantissa
-# between kernels; two layers); the bound leaves a factor of about two.
-BF16_VS_F32 = 1.2e-2
+# bfloat16 against the 32-bit path: the largest difference in a row as a fraction of the largest absolute logit
+# of the request, and the row's root-mean-square difference as a fraction of its root-mean-square logit.
+# Measured on a B200 over every cut below (bfloat16 rounds activations to 8 bits of mantissa between kernels;
+# two layers; 128,256 logits a row): worst rows 1.3e-2 and 1.1e-2; the bounds leave a factor of two.
+BF16_VS_F32 = 2.6e-2
+BF16_VS_F32_RMS = 2.2e-2
 F32_VS_PLAIN = 2e-5
 
 _made: dict = {}
@@ -113,9 +115,13 @@ def reference_rows(tmp_path):
     return _made["f32"]
 
 
-def compare(rows, ref, what, tol):
+def rms_error(got, want):
+    return float(np.sqrt(np.mean((got - want) ** 2)) / np.sqrt(np.mean(want ** 2)))
+
+
+def compare(rows, ref, what, tol, tol_rms=None):
     reqs, keep = requests()
-    worst, flips = 0.0, 0
+    worst, worst_rms, flips = 0.0, 0.0, 0
     for name in reqs:
         places = sorted(p for p in keep[name] if (name, p) in rows)
         assert places, f"{what}: no rows of request {name}"
@@ -127,12 +133,17 @@ def compare(rows, ref, what, tol):
                 raise AssertionError(f"{what}: request {name} (length {len(reqs[name])}) first differs at position "
                                      f"{p}: relative error {err:.3e} > {tol:.1e}")
             worst = max(worst, err)
+            if tol_rms is not None:
+                rms = rms_error(got, want)
+                assert rms < tol_rms, f"{what}: request {name} position {p}: rms error {rms:.3e} > {tol_rms:.1e}"
+                worst_rms = max(worst_rms, rms)
             top2 = np.sort(want)[-2:]
             if top2[1] - top2[0] > 2 * tol * scale:                  # a clear winner stays the winner
                 assert int(np.argmax(got)) == int(np.argmax(want)), f"{what}: {name} position {p}: another argmax"
             else:
                 flips += 1
-    print(f"{what}: worst relative error {worst:.3e} ({flips} rows without a clear winner)")
+    print(f"{what}: worst relative error {worst:.3e}, worst rms error {worst_rms:.3e} "
+          f"({flips} rows without a clear winner)")
     return worst
 
 
@@ -180,7 +191,7 @@ def cut_steps(mode):
 def test_bfloat16_matches_the_float32_path_at_bench_sizes(mode, tmp_path):
     ref = reference_rows(tmp_path)
     rows = replay("bfloat16", cut_steps(mode), tmp_path)
-    compare(rows, ref, f"bench sizes bfloat16 {mode}", BF16_VS_F32)
+    compare(rows, ref, f"bench sizes bfloat16 {mode}", BF16_VS_F32, BF16_VS_F32_RMS)
 
 
 def test_float32_path_is_the_same_in_every_cut_at_bench_sizes(tmp_path):
@@ -206,6 +217,7 @@ def test_repeated_large_layouts_replay_graphs_at_bench_sizes(tmp_path):
     for (name, p), row in rows.items():
         scale = np.abs(ref[(name, p)]).max()
         assert np.abs(row - ref[(name, p)]).max() / scale < BF16_VS_F32, (name, p)
+        assert rms_error(row, ref[(name, p)]) < BF16_VS_F32_RMS, (name, p)
     assert len(rows) > 40
 
 
@@ -237,9 +249,11 @@ def test_forty_requests_decode_together_at_bench_sizes(tmp_path):
         runner.check_device_errors()
         got[dtype] = helpers.collect(steps, tmp_path / dtype, V)
         del rp, runner
-    worst = 0.0
+    worst, worst_rms = 0.0, 0.0
     for key, want in got["float32"].items():
         err = np.abs(got["bfloat16"][key] - want).max() / np.abs(want).max()
-        worst = max(worst, err)
+        rms = rms_error(got["bfloat16"][key], want)
+        worst, worst_rms = max(worst, err), max(worst_rms, rms)
         assert err < BF16_VS_F32, f"request {key[0]} position {key[1]}: relative error {err:.3e}"
-    print(f"forty requests: worst relative error {worst:.3e}")
+        assert rms < BF16_VS_F32_RMS, f"request {key[0]} position {key[1]}: rms error {rms:.3e}"
+    print(f"forty requests: worst relative error {worst:.3e}, worst rms error {worst_rms:.3e}")
