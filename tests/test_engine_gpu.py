@@ -212,7 +212,7 @@ def test_many_live_requests(name, dtype):
             params.append(SamplingParams(max_new_tokens=n_new, temperature=1.0, top_k=12, top_p=0.9, seed=2000 + i))
         else:
             params.append(SamplingParams(max_new_tokens=n_new))
-    blocks = 2000 // page
+    blocks = int(0.8 * sum(-(-n // page) for n in lengths))        # four fifths of what the prompts alone need
     eng = Engine(helpers.model_dir(name), dtype=dtype, block_size=page, num_gpu_blocks=blocks, max_num_seqs=64,
                  max_num_batched_tokens=256, max_model_len=128)
     widest = 0
