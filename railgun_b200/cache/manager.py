@@ -15,7 +15,7 @@ its own tensor ``[pages, 2, kv_heads, page_size, head_dim]``.
 from __future__ import annotations
 
 import ctypes
-from ctypes import c_int, c_longlong, c_void_p, POINTER
+from ctypes import c_float, c_int, c_longlong, c_ulonglong, c_void_p, POINTER
 from dataclasses import dataclass
 
 import numpy as np
@@ -33,10 +33,24 @@ class OutOfPages(CacheError):
 
 @dataclass(frozen=True)
 class PagedKVNeed:
-    """Keys and values in pages: what an attention-like mixer asks for."""
+    """Pages that grow with the request: what an attention-like mixer asks for.  By default a page holds keys and
+    values, ``[2, num_kv_heads, page_size, head_dim]`` in the model's precision, with the page size and the pool
+    the engine was given.  A mixer that wants something else says so: ``page_size`` and ``pool_tokens`` (tokens
+    the group's pool holds; a windowed group can do with fewer), ``dtype`` (a torch dtype name) and
+    ``page_shape`` (what one page is, as a tuple in which the string "page" stands for the page size, for
+    instance ``("page", 96)`` for one compressed vector per token)."""
     num_kv_heads: int
     head_dim: int
     window: int = 0            # 0: all keys are kept
+    page_size: int = 0         # 0: the engine's
+    pool_tokens: int = 0       # 0: the engine's
+    dtype: str | None = None   # None: the model's
+    page_shape: tuple | None = None
+
+    def shape_of_page(self, page_size: int) -> tuple:
+        if self.page_shape is None:
+            return (2, self.num_kv_heads, page_size, self.head_dim)
+        return tuple(page_size if x == "page" else int(x) for x in self.page_shape)
 
 
 @dataclass(frozen=True)
@@ -72,7 +86,12 @@ def _lib():
         lib.rg_cache_can_reserve.argtypes = [c_void_p, c_longlong, c_int, c_int]
         lib.rg_cache_table.argtypes = [c_void_p, c_longlong, c_int, c_void_p, c_int]
         lib.rg_cache_free_pages.argtypes = [c_void_p, c_int]
-        lib.rg_cache_pack_decode.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int]
+        lib.rg_cache_pack_decode.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int,
+                                             c_void_p]
+        lib.rg_cache_records.argtypes = [c_void_p]
+        lib.rg_cache_records.restype = c_void_p
+        lib.rg_cache_set_request.argtypes = [c_void_p, c_longlong, c_int, c_int, c_int, c_float, c_int, c_float,
+                                             c_ulonglong]
         lib.rg_cache_advance.argtypes = [c_void_p, c_void_p, c_int, c_int]
         lib.rg_cache_commit_many.argtypes = [c_void_p, c_void_p, c_void_p, c_int]
         lib.rg_cache_plan_step.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p,
@@ -85,7 +104,10 @@ def _lib():
         lib.rg_sched_create.argtypes = [c_void_p, c_int, c_int, c_int, c_int]
         lib.rg_sched_destroy.argtypes = [c_void_p]
         lib.rg_sched_destroy.restype = None
-        lib.rg_sched_add_request.argtypes = [c_void_p, c_longlong, c_void_p, c_int, c_int, c_void_p, c_int]
+        lib.rg_sched_add_request.argtypes = [c_void_p, c_longlong, c_void_p, c_int, c_int, c_void_p, c_int, c_float,
+                                             c_int, c_float, c_ulonglong]
+        lib.rg_sched_sampling_many.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                               c_void_p]
         for name in ("schedule", "fetch"):
             getattr(lib, f"rg_sched_{name}").argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                                          c_void_p, c_int]
@@ -105,8 +127,16 @@ def _lib():
     return lib
 
 
+# A live request's record, one per state slot (csrc/host/cache_manager.hpp, RequestRecord): 64 bytes.
+REQUEST_RECORD = np.dtype([
+    ("request_id", "<i8"), ("num_computed", "<i4"), ("prompt_len", "<i4"), ("num_generated", "<i4"),
+    ("max_new_tokens", "<i4"), ("last_token", "<i4"), ("top_k", "<i4"), ("temperature", "<f4"), ("top_p", "<f4"),
+    ("seed", "<u8"), ("flags", "<i4"), ("reserved", "<i4", (3,))])
+
+
 class PageAllocator:
-    """The C++ cache manager: page groups, block tables, state slots.  No device memory."""
+    """The C++ cache manager: page groups, block tables, state slots and the slots' request records.  No
+    device memory."""
 
     def __init__(self, page_sizes, num_pages, windows, max_requests: int):
         self._lib = _lib()
@@ -123,6 +153,30 @@ class PageAllocator:
         self.windows = [int(x) for x in windows]
         self.max_requests = int(max_requests)
         self._buf = np.empty(64, dtype=np.int32)
+        self._any_sampled = c_int(0)
+        if self._lib.rg_cache_record_bytes() != REQUEST_RECORD.itemsize:
+            raise CacheError("the request record of the native library is not the one this module describes")
+
+    @property
+    def records(self) -> np.ndarray:
+        """The request records of all state slots, in place (a view of the C++ array, valid while this object
+        lives): record s describes the request in slot s; ``request_id`` -1 marks a free slot."""
+        n = max(1, self.max_requests)
+        raw = (ctypes.c_char * (n * REQUEST_RECORD.itemsize)).from_address(self._lib.rg_cache_records(self._h))
+        return np.frombuffer(raw, dtype=REQUEST_RECORD, count=n)
+
+    def record(self, req_id: int):
+        """A copy of a live request's record."""
+        return self.records[self.slot(req_id)].copy()
+
+    def set_request(self, req_id: int, prompt_len: int = 0, num_generated: int = 0, max_new_tokens: int = 0,
+                    temperature: float = 0.0, top_k: int = 0, top_p: float = 1.0, seed: int = 0) -> None:
+        """Fill in what the cache manager does not work out itself in a live request's record (the scheduler does
+        this in C++ when it admits a request)."""
+        code = self._lib.rg_cache_set_request(self._h, req_id, int(prompt_len), int(num_generated), int(max_new_tokens),
+                                              float(temperature), int(top_k), float(top_p), int(seed) & ((1 << 64) - 1))
+        if code:
+            self._raise(code, f"set_request({req_id})")
 
     def __del__(self):
         h, self._h = getattr(self, "_h", None), None
@@ -187,15 +241,21 @@ class PageAllocator:
             n = self._lib.rg_cache_table(self._h, req_id, group, self._buf.ctypes.data, self._buf.size)
         return self._buf[:n].copy()
 
-    def pack_decode(self, ids: np.ndarray, B: int, MB: int, out: np.ndarray, ahead: int = 0) -> None:
+    def pack_decode(self, ids: np.ndarray, B: int, MB: int, out: np.ndarray, ahead: int = 0,
+                    sampling: np.ndarray | None = None, draw_ahead: int = 0) -> bool:
         """Reserve one more token for each request in ``ids`` (int64) and write
         the decode step's positions, slots and block tables into ``out``
         (int32; layout in csrc/host/runtime.cpp, rg_cache_pack_decode).
         ``ahead`` = 1 packs the step after a step that is launched but not yet
-        committed."""
-        code = self._lib.rg_cache_pack_decode(self._h, ids.ctypes.data, ids.size, B, MB, out.ctypes.data, int(ahead))
+        committed.  ``sampling`` (int32 [7 B]) receives the rows' sampling
+        parameters from the requests' records, the draw numbered
+        num_generated + ``draw_ahead``; returns whether any row samples."""
+        code = self._lib.rg_cache_pack_decode(self._h, ids.ctypes.data, ids.size, B, MB, out.ctypes.data, int(ahead),
+                                              sampling.ctypes.data if sampling is not None else None, int(draw_ahead),
+                                              ctypes.byref(self._any_sampled))
         if code:
             self._raise(code, "pack_decode")
+        return bool(self._any_sampled.value)
 
     def plan_step(self, ids: np.ndarray, counts: np.ndarray, want: np.ndarray, want_offsets: np.ndarray,
                   max_position: int):
@@ -280,29 +340,38 @@ def group_needs(needs: dict) -> tuple[list, dict, dict]:
 class CacheManager:
     """Pages and state slots of one model on one device.
 
-    ``max_tokens``: tokens the pool of every group holds (rounded up to whole
-    pages); ``max_requests``: state slots, the most requests live at a time."""
+    ``page_size`` and ``max_tokens`` (tokens a group's pool holds, rounded up
+    to whole pages) are what a group gets whose need does not ask for its own;
+    ``dtype`` likewise.  ``max_requests``: state slots, the most requests live
+    at a time."""
 
     def __init__(self, needs: dict, page_size: int, max_tokens: int, max_requests: int, dtype, device):
         import torch
         groups, self.group_of, self.state_needs = group_needs(needs)
-        self.page_size = int(page_size)
-        num_pages = (int(max_tokens) + self.page_size - 1) // self.page_size
-        self.groups = [GroupInfo(need, self.page_size, num_pages, cids) for need, cids in groups]
-        self.alloc = PageAllocator([self.page_size] * len(groups), [num_pages] * len(groups),
+        self.groups = []
+        for need, cids in groups:
+            ps = int(need.page_size or page_size)
+            if ps < 1:
+                raise CacheError(f"a page must hold at least one token, not {ps}")
+            self.groups.append(GroupInfo(need, ps, (int(need.pool_tokens or max_tokens) + ps - 1) // ps, cids))
+        self.alloc = PageAllocator([g.page_size for g in self.groups], [g.num_pages for g in self.groups],
                                    [g.need.window for g in self.groups], max_requests)
         self.max_requests = int(max_requests)
         self.dtype = dtype
         self.device = device
         self.kv: dict = {}
         for g in self.groups:
+            page_dtype = getattr(torch, g.need.dtype) if g.need.dtype else dtype
             for cid in g.cache_ids:
-                self.kv[cid] = torch.zeros((num_pages, 2, g.need.num_kv_heads, self.page_size, g.need.head_dim),
-                                           dtype=dtype, device=device)
+                self.kv[cid] = torch.zeros((g.num_pages, *g.need.shape_of_page(g.page_size)), dtype=page_dtype,
+                                           device=device)
         self.state: dict = {}
         for cid, need in self.state_needs.items():
             self.state[cid] = torch.zeros((self.max_requests, *need.shape), dtype=getattr(torch, need.dtype),
                                           device=device)
 
+    def page_size_of(self, cache_id) -> int:
+        return self.groups[self.group_of[cache_id]].page_size
+
     def bytes_per_token(self) -> int:
-        return sum(t.element_size() * t[0].numel() // self.page_size for t in self.kv.values())
+        return sum(t.element_size() * t[0].numel() // self.page_size_of(cid) for cid, t in self.kv.items())

@@ -5,7 +5,11 @@
 // table.  A group with a window w only needs the keys of the last w positions:
 // pages that every future query has passed are given back at commit time and
 // their block-table entries become -1.  Beside the pages, every live request
-// holds one state slot, an index into fixed-size per-request buffers.
+// holds one state slot: an index into fixed-size per-request buffers, and the
+// place of its RequestRecord, the one fixed-size description of a live request
+// (position, lengths, sampling parameters, seed) that decode steps are packed
+// from.  The reference spreads the same over Request and SamplingParams
+// (crates/vllm-scheduler/src/request.rs:37-76,95-193).
 //
 // Policy as in the reference's BlockAllocator
 // (crates/vllm-paged-attention/src/allocator.rs:57-86): FIFO free list
@@ -39,9 +43,25 @@ struct CacheGroup {
     std::vector<int> refcount;
 };
 
+// One per state slot, 64 bytes, plain data: Python reads the array in place and may copy it to the device.
+struct RequestRecord {
+    int64_t request_id = -1;        // -1: the slot is free
+    int32_t num_computed = 0;       // the request's position: tokens whose keys/state are in the cache
+    int32_t prompt_len = 0;
+    int32_t num_generated = 0;      // also the number of the request's next random draw
+    int32_t max_new_tokens = 0;
+    int32_t last_token = -1;
+    int32_t top_k = 0;              // 0: no top-k filter
+    float temperature = 0.f;        // 0: greedy
+    float top_p = 1.f;
+    uint64_t seed = 0;
+    int32_t flags = 0;
+    int32_t reserved[3] = {0, 0, 0};
+};
+static_assert(sizeof(RequestRecord) == 64, "RequestRecord is read as 16 32-bit words");
+
 struct CacheRequest {
     int slot = -1;
-    int num_computed = 0;           // tokens whose keys/state are in the cache
     std::vector<std::vector<int>> tables;   // per group: logical page -> page id, -1 once released
 };
 
@@ -59,6 +79,7 @@ public:
         }
         max_slots_ = max_slots;
         for (int s = 0; s < max_slots; ++s) free_slots_.push_back(s);
+        records_.assign((size_t)(max_slots > 0 ? max_slots : 1), RequestRecord());
     }
 
     int num_groups() const { return (int)groups_.size(); }
@@ -77,8 +98,25 @@ public:
         r.slot = free_slots_.front();
         free_slots_.pop_front();
         r.tables.resize(groups_.size());
+        records_[r.slot] = RequestRecord();
+        records_[r.slot].request_id = id;
         reqs_.emplace(id, std::move(r));
         return reqs_[id].slot;
+    }
+
+    // The record of a live request (nullptr if unknown), and all of them by slot.
+    RequestRecord* record(int64_t id) {
+        auto it = reqs_.find(id);
+        return it == reqs_.end() ? nullptr : &records_[it->second.slot];
+    }
+    const RequestRecord* record(int64_t id) const {
+        auto it = reqs_.find(id);
+        return it == reqs_.end() ? nullptr : &records_[it->second.slot];
+    }
+    const RequestRecord* records() const { return records_.data(); }
+    int num_computed(int64_t id) const {
+        const RequestRecord* r = record(id);
+        return r ? r->num_computed : 0;
     }
 
     // Pages each group would have to add so that the request can hold new_len tokens.
@@ -129,7 +167,7 @@ public:
         CacheRequest& r = it->second;
         for (size_t g = 0; g < groups_.size(); ++g)
             if (new_len > (int)r.tables[g].size() * groups_[g].page_size) return CACHE_BAD_ARGUMENT;
-        r.num_computed = new_len;
+        records_[r.slot].num_computed = new_len;
         for (size_t g = 0; g < groups_.size(); ++g) {
             CacheGroup& G = groups_[g];
             if (G.window <= 0) continue;
@@ -158,6 +196,7 @@ public:
                     if (st != CACHE_OK) status = st;
                 }
         free_slots_.push_back(it->second.slot);
+        records_[it->second.slot] = RequestRecord();
         reqs_.erase(it);
         return status;
     }
@@ -188,8 +227,12 @@ public:
         std::vector<int> slot_seen(max_slots_, 0);
         for (int s : free_slots_)
             if (s < 0 || s >= max_slots_ || slot_seen[s]++) return CACHE_CORRUPT;
-        for (const auto& kv : reqs_)
+        for (const auto& kv : reqs_) {
             if (kv.second.slot < 0 || kv.second.slot >= max_slots_ || slot_seen[kv.second.slot]++) return CACHE_CORRUPT;
+            if (records_[kv.second.slot].request_id != kv.first) return CACHE_CORRUPT;
+        }
+        for (int s : free_slots_)
+            if (records_[s].request_id != -1) return CACHE_CORRUPT;
         for (int s = 0; s < max_slots_; ++s)
             if (slot_seen[s] != 1) return CACHE_CORRUPT;
         return CACHE_OK;
@@ -205,6 +248,7 @@ private:
     std::vector<CacheGroup> groups_;
     std::unordered_map<int64_t, CacheRequest> reqs_;
     std::deque<int> free_slots_;
+    std::vector<RequestRecord> records_;
     int max_slots_ = 0;
 };
 

@@ -30,8 +30,23 @@ int rg_cache_commit(void* h, long long id, int new_len) { RG_GUARD(return ((Cach
 int rg_cache_release(void* h, long long id) { RG_GUARD(return ((CacheManager*)h)->release(id)) }
 int rg_cache_has(void* h, long long id) { return ((CacheManager*)h)->has(id) ? 1 : 0; }
 int rg_cache_num_computed(void* h, long long id) {
-    const CacheRequest* r = ((CacheManager*)h)->find(id);
+    const RequestRecord* r = ((CacheManager*)h)->record(id);
     return r ? r->num_computed : CACHE_UNKNOWN_REQUEST;
+}
+// The records of all state slots, in place: max_slots records of rg_cache_record_bytes() bytes, record s for
+// slot s (request_id -1: free).  The memory lives as long as the cache manager.
+const void* rg_cache_records(void* h) { return ((CacheManager*)h)->records(); }
+int rg_cache_record_bytes() { return (int)sizeof(RequestRecord); }
+// Sets what the cache manager does not work out itself in a live request's record (a scheduler does this at
+// admission; callers without one, to have decode steps sample).
+int rg_cache_set_request(void* h, long long id, int prompt_len, int num_generated, int max_new_tokens,
+                         float temperature, int top_k, float top_p, unsigned long long seed) {
+    RequestRecord* r = ((CacheManager*)h)->record(id);
+    if (!r) return CACHE_UNKNOWN_REQUEST;
+    if (!(temperature >= 0.f) || top_k < 0 || !(top_p > 0.f && top_p <= 1.f) || num_generated < 0) return CACHE_BAD_ARGUMENT;
+    r->prompt_len = prompt_len; r->num_generated = num_generated; r->max_new_tokens = max_new_tokens;
+    r->temperature = temperature; r->top_k = top_k; r->top_p = top_p; r->seed = seed;
+    return CACHE_OK;
 }
 int rg_cache_slot(void* h, long long id) {
     const CacheRequest* r = ((CacheManager*)h)->find(id);
@@ -51,14 +66,25 @@ int rg_cache_table(void* h, long long id, int group, int* out, int cap) {
 // Packs a pure-decode step (one new token per request) for `R` requests into `out`, laid out for a static
 // batch of `B` rows and block tables `MB` wide:
 //   positions[B] | context_lens[B] | start_pos[B] | state_slots[B] | per group: slots[B] | per group: table[B*MB]
-// Rows R..B-1 are padding: position 0, context 1, slot -1 (nothing is written), table of zeros.
+// Rows R..B-1 are padding: position 0, context 1, cache slot -1 (nothing is written), state slot -1 (no
+// request: a part with per-request state leaves such rows alone), table of zeros.
 // Pages for the new token are reserved here.  `ahead` > 0 packs the step that many steps after the next one (for a
-// step launched before the one before it has been committed): its position is num_computed + ahead.  Returns 0, or
+// step launched before the one before it has been committed): its position is num_computed + ahead.
+// `sampling` (may be null): the rows' sampling parameters from the requests' records, as 7 B 32-bit words:
+//   seed[B] (64-bit) | draw counter[B] (64-bit) = num_generated + draw_ahead | temperature[B] | top_k[B] | top_p[B]
+// with padding rows greedy; *any_sampled says whether a row has a temperature above zero.  Returns 0, or
 // a negative status (nothing half-reserved matters: a failed request keeps what it had).
-int rg_cache_pack_decode(void* h, const long long* ids, int R, int B, int MB, int* out, int ahead) {
+int rg_cache_pack_decode(void* h, const long long* ids, int R, int B, int MB, int* out, int ahead, int* sampling,
+                         int draw_ahead, int* any_sampled) {
     try {
         CacheManager* c = (CacheManager*)h;
-        if (ahead < 0) return CACHE_BAD_ARGUMENT;
+        if (ahead < 0 || draw_ahead < 0) return CACHE_BAD_ARGUMENT;
+        if (any_sampled) *any_sampled = 0;
+        if (sampling) {
+            std::memset(sampling, 0, sizeof(int) * (size_t)7 * B);
+            float* top_p = reinterpret_cast<float*>(sampling + 6 * B);
+            for (int b = 0; b < B; ++b) top_p[b] = 1.f;
+        }
         const int G = c->num_groups();
         int* positions = out;
         int* context = out + B;
@@ -69,15 +95,25 @@ int rg_cache_pack_decode(void* h, const long long* ids, int R, int B, int MB, in
         std::memset(out, 0, sizeof(int) * ((size_t)(4 + G) * B + (size_t)G * B * MB));
         for (int b = R; b < B; ++b) {
             context[b] = 1;
+            slots_state[b] = -1;
             for (int g = 0; g < G; ++g) slot_map[g * B + b] = -1;
         }
         for (int b = 0; b < R; ++b) {
             const CacheRequest* r = c->find(ids[b]);
             if (!r) return CACHE_UNKNOWN_REQUEST;
-            const int pos = r->num_computed + ahead;
+            const RequestRecord* rec = c->record(ids[b]);
+            const int pos = rec->num_computed + ahead;
             const int st = c->reserve(ids[b], pos + 1);
             if (st != CACHE_OK) return st;
             r = c->find(ids[b]);
+            if (sampling) {
+                reinterpret_cast<unsigned long long*>(sampling)[b] = rec->seed;
+                reinterpret_cast<long long*>(sampling + 2 * B)[b] = (long long)rec->num_generated + draw_ahead;
+                reinterpret_cast<float*>(sampling + 4 * B)[b] = rec->temperature;
+                sampling[5 * B + b] = rec->top_k;
+                reinterpret_cast<float*>(sampling + 6 * B)[b] = rec->top_p;
+                if (any_sampled && rec->temperature > 0.f) *any_sampled = 1;
+            }
             positions[b] = pos;
             context[b] = pos + 1;
             start[b] = pos;
@@ -115,8 +151,7 @@ int rg_cache_plan_step(void* h, const long long* ids, const int* counts, int R, 
             *bad = b;
             if (!seen.emplace(ids[b], b).second) return CACHE_DUPLICATE;
             if (counts[b] < 1) return CACHE_BAD_ARGUMENT;
-            const CacheRequest* r = c->find(ids[b]);
-            starts[b] = r ? r->num_computed : 0;
+            starts[b] = c->num_computed(ids[b]);
             if ((long long)starts[b] + counts[b] > max_position) return STEP_BEYOND_MAX_POSITION;
             for (int w = want_offsets[b]; w < want_offsets[b + 1]; ++w)
                 if (want[w] < 0 || want[w] >= counts[b]) { *bad_value = want[w]; return STEP_BAD_WANT; }
@@ -232,9 +267,8 @@ int rg_cache_advance(void* h, const long long* ids, int R, int n) {
     try {
         CacheManager* c = (CacheManager*)h;
         for (int b = 0; b < R; ++b) {
-            const CacheRequest* r = c->find(ids[b]);
-            if (!r) return CACHE_UNKNOWN_REQUEST;
-            const int st = c->commit(ids[b], r->num_computed + n);
+            if (!c->has(ids[b])) return CACHE_UNKNOWN_REQUEST;
+            const int st = c->commit(ids[b], c->num_computed(ids[b]) + n);
             if (st != CACHE_OK) return st;
         }
         return CACHE_OK;
@@ -258,8 +292,22 @@ void* rg_sched_create(void* cache, int max_num_batched_tokens, int max_num_seqs,
 }
 void rg_sched_destroy(void* h) { delete (Scheduler*)h; }
 int rg_sched_add_request(void* h, long long id, const int* prompt, int n, int max_new_tokens, const int* stop,
-                         int n_stop) {
-    RG_GUARD(return ((Scheduler*)h)->add_request(id, prompt, n, max_new_tokens, stop, n_stop))
+                         int n_stop, float temperature, int top_k, float top_p, unsigned long long seed) {
+    RG_GUARD(return ((Scheduler*)h)->add_request(id, prompt, n, max_new_tokens, stop, n_stop, temperature, top_k,
+                                                 top_p, seed))
+}
+// The sampling parameters of n requests (waiting, running or finished), and the number of each one's next draw.
+int rg_sched_sampling_many(void* h, const long long* ids, int n, float* temperature, int* top_k, float* top_p,
+                           long long* seed, long long* counter) {
+    try {
+        for (int i = 0; i < n; ++i) {
+            const SchedRequest* r = ((Scheduler*)h)->find(ids[i]);
+            if (!r) return SCHED_UNKNOWN;
+            temperature[i] = r->temperature; top_k[i] = r->top_k; top_p[i] = r->top_p;
+            seed[i] = (long long)r->seed; counter[i] = r->num_generated();
+        }
+        return 0;
+    } catch (...) { return SCHED_BAD_ARGUMENT; }
 }
 // Decides the next step and writes it flat: per entry id/start/count/want_last, and all entries' tokens
 // one after the other.  Returns the number of entries, or -(needed token capacity) - 1000000 if a buffer is

@@ -64,6 +64,10 @@ struct SchedRequest {
     int prompt_len = 0;
     int max_new_tokens = 0;
     std::vector<int> stop_ids;
+    float temperature = 0.f;             // sampling parameters: they outlive a preemption, the slot's record does not
+    float top_p = 1.f;
+    int top_k = 0;
+    uint64_t seed = 0;
     int finish = FINISH_NONE;
     int num_preemptions = 0;
     uint64_t arrival = 0;
@@ -81,9 +85,11 @@ class Scheduler {
 public:
     Scheduler(CacheManager* cache, const SchedConfig& cfg) : cache_(cache), cfg_(cfg) {}
 
-    int add_request(int64_t id, const int* prompt, int n, int max_new_tokens, const int* stop, int n_stop) {
+    int add_request(int64_t id, const int* prompt, int n, int max_new_tokens, const int* stop, int n_stop,
+                    float temperature = 0.f, int top_k = 0, float top_p = 1.f, uint64_t seed = 0) {
         if (n <= 0) return SCHED_EMPTY_PROMPT;              // request.rs:143 asserts a non-empty prompt
-        if (max_new_tokens < 1) return SCHED_BAD_ARGUMENT;
+        if (max_new_tokens < 1 || !(temperature >= 0.f) || top_k < 0 || !(top_p > 0.f && top_p <= 1.f))
+            return SCHED_BAD_ARGUMENT;
         if (all_.count(id)) return SCHED_DUPLICATE;
         if (n + max_new_tokens > cfg_.max_model_len) return SCHED_TOO_LONG;
         SchedRequest r;
@@ -92,6 +98,7 @@ public:
         r.prompt_len = n;
         r.max_new_tokens = max_new_tokens;
         r.stop_ids.assign(stop, stop + n_stop);
+        r.temperature = temperature; r.top_k = top_k; r.top_p = top_p; r.seed = seed;
         r.arrival = next_arrival_++;
         all_.emplace(id, std::move(r));
         waiting_.push_back(id);
@@ -112,7 +119,7 @@ public:
             if (budget <= 0) break;
             if (std::find(running_.begin(), running_.end(), id) == running_.end()) continue;   // preempted meanwhile
             SchedRequest& r = all_[id];
-            const int computed = cache_->find(id)->num_computed;
+            const int computed = cache_->num_computed(id);
             int n = portion((int)r.tokens.size() - computed, budget);
             bool placed = false;
             while (true) {
@@ -157,6 +164,7 @@ public:
                 break;
             }
             running_.push_back(id);
+            write_record(r);
             entries_.push_back({id, 0, n, n == (int)r.tokens.size() ? 1 : 0});
             budget -= n;
         }
@@ -174,6 +182,10 @@ public:
             if (it == all_.end() || it->second.finish != FINISH_NONE) continue;
             SchedRequest& r = it->second;
             r.tokens.push_back(tokens[i]);
+            if (RequestRecord* rec = cache_->record(ids[i])) {
+                rec->num_generated = r.num_generated();
+                rec->last_token = tokens[i];
+            }
             int reason = FINISH_NONE;
             if (std::find(r.stop_ids.begin(), r.stop_ids.end(), tokens[i]) != r.stop_ids.end())
                 reason = FINISH_STOP_TOKEN;
@@ -245,9 +257,19 @@ public:
     CacheManager* cache() const { return cache_; }
 
 private:
+    // The slot's record of a request that has just been given a slot (admitted, maybe after a preemption).
+    void write_record(const SchedRequest& r) {
+        RequestRecord* rec = cache_->record(r.id);
+        if (!rec) return;
+        rec->prompt_len = r.prompt_len;
+        rec->num_generated = r.num_generated();
+        rec->max_new_tokens = r.max_new_tokens;
+        rec->last_token = r.tokens.back();
+        rec->temperature = r.temperature; rec->top_k = r.top_k; rec->top_p = r.top_p; rec->seed = r.seed;
+    }
     int remaining(int64_t id) const {
         const SchedRequest& r = all_.at(id);
-        return (int)r.tokens.size() - cache_->find(id)->num_computed;
+        return (int)r.tokens.size() - cache_->num_computed(id);
     }
     int portion(int remaining_tokens, int budget) const {
         int n = std::min(remaining_tokens, budget);

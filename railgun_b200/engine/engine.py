@@ -13,7 +13,7 @@ from __future__ import annotations
 import numpy as np
 
 from .. import ops
-from ..sampling.sampler import Sampler, _as_i64
+from ..sampling.sampler import Sampler
 from .batch import StepEntry, _token_array
 from .request import RequestOutput, SamplingParams, StepResponse
 from .runner import ModelRunner
@@ -31,12 +31,12 @@ class Engine:
             max_num_batched_tokens=max_num_batched_tokens, max_num_seqs=max_num_seqs,
             max_prefill_chunk=max_prefill_chunk, max_model_len=max_model_len))
         self.sampler = Sampler(self.runner.device)
-        self._params: dict = {}
         self._next_id = 1
         self.steps_run = 0
-        self.run_ahead = True          # launch the next decode step before this one's tokens are on the host
+        # launch the next decode step before this one's tokens are on the host; not for a model whose parts keep
+        # state of their own: a launched step that is then dropped would have advanced it
+        self.run_ahead = not self.runner.cache.state
         self._ahead = None             # the step launched that way, if any (runner.FollowStep)
-        self._sampling = None          # the sampling parameters of the requests of the last sampled decode step
         self.steps_ahead = 0           # how many steps were taken from a launch made ahead
 
     # ---- low level --------------------------------------------------------------------------
@@ -49,8 +49,10 @@ class Engine:
             raise ValueError(f"prompt token ids must be integers in [0, {vocab})")
         rid = self._next_id
         self._next_id += 1
-        self.scheduler.add_request(rid, prompt, params.max_new_tokens, params.stop_token_ids)
-        self._params[rid] = params
+        # the scheduler keeps the parameters and writes them into the request's slot record, from which decode
+        # steps are packed: the request has no second home here
+        self.scheduler.add_request(rid, prompt, params.max_new_tokens, params.stop_token_ids, params.temperature,
+                                   params.top_k, params.top_p, params.seed)
         return rid
 
     def step(self) -> list:
@@ -87,20 +89,15 @@ class Engine:
         """Every request brings one token and wants its logits: the step is a graph replay that chooses the
         tokens itself, or the step launched ahead in the call before if it answers this decision."""
         wanted = ids.tolist()
-        params = [self._params[r] for r in wanted]
-        sampling = None                                              # all greedy: the graph takes the argmax
-        if any(p.temperature != 0.0 for p in params):
-            sampling = self._sampling_of(ids, wanted, params)       # the graph draws with the requests' parameters
         rows = self._rows_of_launched(ahead, ids) if ahead is not None else None
         launched = ahead if rows is not None else None
         if launched is not None:
             self.steps_ahead += 1
         else:
-            self.runner.decode_step_flat(ids, tokens, sampling)
+            self.runner.decode_step_flat(ids, tokens)   # draws or takes the argmax as the requests' records say
         if (self.run_ahead and (launched is None or len(launched.ids) == len(ids))
                 and self.scheduler.next_step_predictable()):
-            after = None if sampling is None else dict(sampling, counter=sampling["counter"] + 1)
-            self._ahead = self.runner.decode_follow(ids, launched, after)
+            self._ahead = self.runner.decode_follow(ids, launched)
         # only now wait for this step's tokens
         return wanted, (launched.tokens()[rows] if launched is not None else self.runner.greedy_tokens_host())
 
@@ -118,24 +115,9 @@ class Engine:
         logits = self.runner.step(batch)
         if logits is None:
             return wanted, None
-        params = [self._params[r] for r in wanted]
-        sampled = self.sampler.sample(logits, params, [self.scheduler.num_generated(r) for r in wanted])
+        sampled = self.sampler.sample_arrays(logits, self.scheduler.sampling_many(wanted))
         self.runner.check_device_errors()
         return wanted, sampled
-
-    def _sampling_of(self, ids, wanted, params) -> dict:
-        """The requests' sampling parameters as arrays, one entry per request: the constant ones are kept while
-        the same requests decode; the count of generated tokens, which numbers the draw, is read every step."""
-        kept = self._sampling
-        if kept is None or len(kept["ids"]) != len(ids) or not (kept["ids"] == ids).all():
-            kept = self._sampling = dict(
-                ids=ids.copy(),
-                temperature=np.array([p.temperature for p in params], dtype=np.float32),
-                top_k=np.array([p.top_k for p in params], dtype=np.int32),
-                top_p=np.array([p.top_p for p in params], dtype=np.float32),
-                seed=np.array([_as_i64(p.seed) for p in params], dtype=np.int64))
-        return dict(temperature=kept["temperature"], top_k=kept["top_k"], top_p=kept["top_p"], seed=kept["seed"],
-                    counter=self.scheduler.num_generated_many(ids))
 
     @staticmethod
     def _rows_of_launched(launched, ids):
@@ -155,7 +137,6 @@ class Engine:
                             self.scheduler.finish_reason(request_id), self.scheduler.error(request_id),
                             self.scheduler.num_preemptions(request_id))
         self.scheduler.forget(request_id)
-        self._params.pop(request_id, None)
         return out
 
     def has_unfinished(self) -> bool:
@@ -199,7 +180,6 @@ class Engine:
             for r in out:
                 if r.is_finished:
                     self.scheduler.forget(r.request_id)
-                    self._params.pop(r.request_id, None)
             yield from out
 
     # ---- the call a user makes --------------------------------------------------------------

@@ -58,6 +58,13 @@ def capture(graph):
             gc.enable()
 
 
+def raise_device_error(code: int):
+    """What a kernel left in an error flag: 1 for a position outside its table."""
+    if code == 1:
+        raise RuntimeError("a kernel met a position outside its table")
+    raise RuntimeError(f"a kernel flagged error {code}; the step's result is invalid")
+
+
 def parse_dtype(name):
     if isinstance(name, torch.dtype):
         if name not in (torch.bfloat16, torch.float32):
@@ -73,7 +80,7 @@ class _CacheViews:
     def __init__(self, cache: CacheManager):
         self._views = {}
         for cid, t in cache.kv.items():
-            self._views[cid] = CacheView(cid, group=cache.group_of[cid], kv=t, page_size=cache.page_size)
+            self._views[cid] = CacheView(cid, group=cache.group_of[cid], kv=t, page_size=cache.page_size_of(cid))
         for cid, t in cache.state.items():
             self._views[cid] = CacheView(cid, state=t)
         self._none = {}
@@ -135,7 +142,7 @@ class StaticDecodeBatch:
         tables_off = (5 + G) * B
         self.batch = StepBatch(
             num_tokens=B, num_requests=B, num_wanted=B, max_query_len=1,
-            max_context_len=MB * (runner.page_sizes[0] if G else 1),
+            max_context_len=MB * (min(runner.page_sizes) if G else 1),
             token_ids=seg(0), positions=seg(1), req_of_token=ar[:B], want_rows=ar[:B], cu_seqlens=ar,
             context_lens=seg(2), start_pos=seg(3), state_slots=seg(4),
             slot_mapping=[seg(5 + g) for g in range(G)],
@@ -149,10 +156,11 @@ class StaticDecodeBatch:
         self.in_flight = None          # an event after the last replay that reads ``host`` and writes ``host_out``
 
     def raise_if_flagged(self, host_out_np) -> None:
-        if host_out_np[self.B]:
+        code = int(host_out_np[self.B])
+        if code:
             self.out_dev[self.B:].zero_()
             host_out_np[self.B] = 0
-            raise RuntimeError("a kernel met a position outside its table")
+            raise_device_error(code)
 
     def wait_until_reusable(self) -> None:
         """The pinned buffers may be written again once the last replay that copies them has run."""
@@ -170,15 +178,6 @@ def sampling_views(buf, off: int, B: int) -> dict:
     return dict(seed=buf[off:off + 2 * B].view(i64), counter=buf[off + 2 * B:off + 4 * B].view(i64),
                 temperature=buf[off + 4 * B:off + 5 * B].view(f32), top_k=buf[off + 5 * B:off + 6 * B],
                 top_p=buf[off + 6 * B:off + 7 * B].view(f32))
-
-
-def fill_sampling(views: dict, sampling, R: int) -> None:
-    """Write ``sampling`` (arrays of R entries by name, or None: every row greedy) into a host buffer's views;
-    rows beyond R are greedy."""
-    views["temperature"][:] = 0.0
-    if sampling is not None:
-        for name, v in views.items():
-            v[:R] = sampling[name]
 
 
 class FollowStep:
@@ -247,10 +246,10 @@ class ModelRunner:
         self.views = _CacheViews(self.cache)
         self.page_sizes = [g.page_size for g in self.cache.groups]
         self.err_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
-        # graphs need every part to work from device-side descriptions only; parts with state of their own
-        # and parts that say they plan on the host (none of the built-in ones) switch them off
-        self.use_graphs = (bool(use_graphs) and not self.cache.state and len(self.page_sizes) >= 1
-                           and self.model.graph_safe)
+        # graphs need every part to work from device-side descriptions only; a part that says it plans on the
+        # host (none of the built-in ones) switches them off.  Per-request state is no obstacle: its buffers are
+        # static and the rows' slots are data of the step (-1 in a padding row).
+        self.use_graphs = bool(use_graphs) and self.model.graph_safe
         self._static: dict = {}
         self._shape_steps: dict = {}       # layout -> ShapeGraph: steps of a layout seen before replay a captured graph
         self._shape_seen: dict = {}
@@ -352,15 +351,17 @@ class ModelRunner:
         with their tokens."""
         ops.tc_gemm_check()
         flags = [self.err_flag] + [st.out_dev[st.B:] for st in self._static.values()]
-        if int(torch.cat(flags).sum().item()):
+        code = int(torch.cat(flags).max().item())
+        if code:
             for f in flags:
                 f.zero_()
-            raise RuntimeError("a kernel met a position outside its table")
+            raise_device_error(code)
 
     # ---- decode steps from captured graphs -----------------------------------------------------------
     def _static_for(self, n_requests: int, max_context: int) -> StaticDecodeBatch:
         B = _bucket(n_requests, _BATCH_BUCKETS)
-        page = self.page_sizes[0]
+        # block tables are as wide as the group with the smallest pages needs
+        page = min(self.page_sizes) if self.page_sizes else 16
         ctx_bucket = 1024
         while ctx_bucket < max_context:
             ctx_bucket *= 2
@@ -378,7 +379,14 @@ class ModelRunner:
         ids from the step before it on the device and everything else from
         ``follow``'s pinned buffer.  With ``sampling`` the tokens are drawn with
         the rows' parameters in the static buffer (temperature 0: greedy)
-        instead of the plain argmax."""
+        instead of the plain argmax.
+
+        The step whose arrival makes the capture necessary runs here, once,
+        outside the capture (libraries set themselves up in that run); the
+        graph serves the steps after it.  So a step is executed exactly once,
+        which a part with state of its own needs (rewriting a cache entry is
+        harmless, advancing a state twice is not).  Returns the captured step
+        and that first run's logits."""
         counter = ops.launch_counter()
         B = static.B
 
@@ -399,14 +407,10 @@ class ModelRunner:
             (follow or static).host_out.copy_(static.out_dev, non_blocking=True)
             return logits, sampled
 
-        # a first run outside capture, so that libraries set themselves up before it
         side = torch.cuda.Stream(device=self.device)
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
-            saved, saved_sampled = static.dev.clone(), static.sampled.clone()
-            body()
-            static.dev.copy_(saved)
-            static.sampled.copy_(saved_sampled)             # a following step is fed with the tokens before this run
+            first_logits, _ = body()                        # this step itself
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
@@ -415,7 +419,7 @@ class ModelRunner:
             logits, sampled = body()
         launches = counter.value - n0
         counter.value = n0
-        return CapturedStep(graph, logits, sampled, launches)
+        return CapturedStep(graph, logits, sampled, launches), first_logits
 
     def _step_decode_graph(self, entries) -> torch.Tensor:
         R = len(entries)
@@ -425,13 +429,13 @@ class ModelRunner:
             raise BatchError("a request appears twice in one step")
         return self.decode_step_flat(ids, tokens)
 
-    def decode_step_flat(self, ids: np.ndarray, tokens: np.ndarray, sampling=None) -> torch.Tensor:
+    def decode_step_flat(self, ids: np.ndarray, tokens: np.ndarray) -> torch.Tensor:
         """One decode step for requests already in the cache: ``ids`` int64
         (distinct), ``tokens`` int32, one token each, logits wanted for all.
         Returns the logits [R, V] (a view of a static buffer); the tokens the
-        graph chose are in ``last_greedy``: the argmax, or, with ``sampling``
-        (arrays ``temperature``, ``top_k``, ``top_p``, ``seed``, ``counter`` of
-        one entry per request), a draw with those parameters."""
+        graph chose are in ``last_greedy``: for a request whose slot record has
+        a temperature above zero a draw with the record's parameters (numbered
+        by its count of generated tokens), else the argmax."""
         R = len(ids)
         self.last_greedy = None
         if tokens.min() < 0 or tokens.max() >= self.model.vocab_size:
@@ -441,7 +445,8 @@ class ModelRunner:
             static = self._static_for(R, ctx)
             static.wait_until_reusable()
             try:
-                self.alloc.pack_decode(ids, static.B, static.MB, static.host_np[static.B:])
+                sampled = self.alloc.pack_decode(ids, static.B, static.MB, static.host_np[static.B:],
+                                                 sampling=static.host_np[static.sampling_off:])
                 break
             except CacheError as e:
                 if "bad argument" in str(e) and ctx < self.model.spec.max_position:
@@ -455,21 +460,23 @@ class ModelRunner:
                              f"{self.model.spec.max_position}")
         static.host_np[:R] = tokens
         static.host_np[R:B] = 0
-        fill_sampling(sampling_views(static.host_np, static.sampling_off, B), sampling, R)
         self.last_h2d_bytes = static.host.numel() * 4
-        key = sampling is not None
+        key = sampled
+        logits = None
         if key not in static.step_graphs:
-            static.step_graphs[key] = self._capture(static, sampling=key)
+            static.step_graphs[key], logits = self._capture(static, sampling=key)   # runs this step and captures it
         cap = static.step_graphs[key]
-        cap.graph.replay()                                  # upload, the step, greedy tokens back to pinned memory
+        if logits is None:
+            cap.graph.replay()                              # upload, the step, greedy tokens back to pinned memory
+            ops.launch_counter().value += cap.launches
+            logits = cap.logits
         if static.in_flight is None:
             static.in_flight = torch.cuda.Event()
         static.in_flight.record()
-        ops.launch_counter().value += cap.launches
         self.alloc.advance(ids, 1)
         self.last_greedy = cap.sampled[:R]
         self._greedy_host = (static, R)
-        return cap.logits[:R]
+        return logits[:R]
 
     def greedy_tokens_host(self):
         """The tokens that the last graph-replayed decode step chose (its argmax,
@@ -483,13 +490,13 @@ class ModelRunner:
         static.raise_if_flagged(static.host_out_np)
         return static.host_out_np[:R].copy()
 
-    def decode_follow(self, ids: np.ndarray, after, sampling=None) -> FollowStep | None:
+    def decode_follow(self, ids: np.ndarray, after) -> FollowStep | None:
         """Launch the decode step that follows a launched one for the same
         requests (``ids`` int64, in its row order) before that one's tokens are
         on the host: the token ids stay on the device.  ``after`` is what that
         step ran on: the FollowStep it was, or None for the step that
-        ``decode_step_flat`` launched last; ``sampling`` as there, for this
-        step's draw.  Nothing is committed: the caller
+        ``decode_step_flat`` launched last.  Its draws are numbered one after
+        those of that step.  Nothing is committed: the caller
         commits the step once it knows that the requests went on.  Returns None
         if the step cannot be launched this way (no pages, a context beyond the
         static batch's tables or the model's positions)."""
@@ -511,19 +518,18 @@ class ModelRunner:
         B = static.B
         ahead = 0 if after is None else 1                   # decode_step_flat has advanced its requests already
         try:
-            self.alloc.pack_decode(ids, B, static.MB, f.host_in_np[B:], ahead=ahead)
+            key = self.alloc.pack_decode(ids, B, static.MB, f.host_in_np[B:], ahead=ahead,
+                                         sampling=f.host_in_np[static.sampling_off:], draw_ahead=1)
         except CacheError:
             return None
         if int(f.host_in_np[2 * B:2 * B + R].max()) > self.model.spec.max_position:
             return None
-        fill_sampling(sampling_views(f.host_in_np, static.sampling_off, B), sampling, R)
-        key = sampling is not None
         if key not in f.captured:
-            f.captured[key] = self._capture(static, follow=f, sampling=key)
-        cap = f.captured[key]
-        cap.graph.replay()
+            f.captured[key], _ = self._capture(static, follow=f, sampling=key)       # runs this step and captures it
+        else:
+            f.captured[key].graph.replay()
+            ops.launch_counter().value += f.captured[key].launches
         f.done.record()
-        ops.launch_counter().value += cap.launches
         self.last_h2d_bytes = (static.host.numel() - B) * 4
         f.ids = ids.copy()
         return f

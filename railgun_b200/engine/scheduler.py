@@ -36,7 +36,8 @@ class ScheduledEntry:
 
 
 _ADD_ERRORS = {-1: "the prompt is empty", -2: "prompt + max_new_tokens exceeds max_model_len",
-               -3: "a request with this id exists", -5: "max_new_tokens must be >= 1"}
+               -3: "a request with this id exists",
+               -5: "max_new_tokens must be >= 1, temperature >= 0, top_k >= 0 and top_p in (0, 1]"}
 
 
 class Scheduler:
@@ -62,11 +63,16 @@ class Scheduler:
         if h:
             self._lib.rg_sched_destroy(h)
 
-    def add_request(self, request_id: int, prompt, max_new_tokens: int, stop_token_ids=()) -> None:
+    def add_request(self, request_id: int, prompt, max_new_tokens: int, stop_token_ids=(), temperature: float = 0.0,
+                    top_k: int = 0, top_p: float = 1.0, seed: int = 0) -> None:
+        """The request with its sampling parameters (the reference's SamplingParams,
+        crates/vllm-scheduler/src/request.rs:37-76, and a seed): the scheduler keeps them and writes them
+        into the request's slot record whenever it gives the request a slot."""
         p = np.ascontiguousarray(prompt, dtype=np.int32)
         s = np.ascontiguousarray(list(stop_token_ids), dtype=np.int32)
         code = self._lib.rg_sched_add_request(self._h, int(request_id), p.ctypes.data, p.size,
-                                              int(max_new_tokens), s.ctypes.data, s.size)
+                                              int(max_new_tokens), s.ctypes.data, s.size, float(temperature),
+                                              int(top_k), float(top_p), int(seed) & ((1 << 64) - 1))
         if code:
             raise SchedulerError(f"request {request_id}: {_ADD_ERRORS.get(code, code)}")
 
@@ -156,6 +162,19 @@ class Scheduler:
         out = np.empty(ids.size, dtype=np.int64)
         if self._lib.rg_sched_num_generated_many(self._h, ids.ctypes.data, ids.size, out.ctypes.data) != 0:
             raise SchedulerError("num_generated_many: an unknown request")
+        return out
+
+    def sampling_many(self, request_ids) -> dict:
+        """The sampling parameters of the requests as arrays (``temperature``, ``top_k``, ``top_p``, ``seed``) and
+        the number of each one's next draw (``counter`` = tokens generated so far)."""
+        ids = np.ascontiguousarray(request_ids, dtype=np.int64)
+        n = ids.size
+        out = dict(temperature=np.empty(n, np.float32), top_k=np.empty(n, np.int32), top_p=np.empty(n, np.float32),
+                   seed=np.empty(n, np.int64), counter=np.empty(n, np.int64))
+        if self._lib.rg_sched_sampling_many(self._h, ids.ctypes.data, n, out["temperature"].ctypes.data,
+                                            out["top_k"].ctypes.data, out["top_p"].ctypes.data, out["seed"].ctypes.data,
+                                            out["counter"].ctypes.data) != 0:
+            raise SchedulerError("sampling_many: an unknown request")
         return out
 
     def num_preemptions(self, request_id: int) -> int:

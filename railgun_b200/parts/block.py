@@ -1,6 +1,7 @@
 """Block arrangements: how a layer's parts sit around the residual stream.
 
-"prenorm": x = x + mixer(norm(x)); x = x + ffn(norm(x))
+"prenorm": for every branch of the layer in turn, x = x + part(norm(x)); the
+usual block is x = x + mixer(norm(x)); x = x + ffn(norm(x))
 (crates/vllm-models/src/llama/architecture.rs:47-58).  Each addition is done
 inside the next norm's kernel, in 32-bit; at small decode batches the
 addition moves into the kernel of the product before it and the norm into the
@@ -14,16 +15,13 @@ from .registry import register_arrangement
 
 class PreNorm(Arrangement):
     def run(self, layer, stream, batch, cache, writes):
-        h = normed_input(layer.mixer_norm, layer.mixer, stream)
-        if getattr(layer.mixer, "defers_output", False):
-            stream.pending = layer.mixer.forward(h, batch, cache, writes, defer=True)
-        else:
-            stream.pending = layer.mixer.forward(h, batch, cache, writes)
-        h = normed_input(layer.ffn_norm, layer.ffn, stream)
-        if getattr(layer.ffn, "defers_output", False):
-            stream.pending = layer.ffn.forward(h, batch, defer=True)
-        else:
-            stream.pending = layer.ffn.forward(h, batch)
+        for b in layer.branches:
+            h = normed_input(b.norm, b.part, stream)
+            more = dict(defer=True) if getattr(b.part, "defers_output", False) else {}
+            if b.role == "mixer":
+                stream.pending = b.part.forward(h, batch, cache, writes, **more)
+            else:
+                stream.pending = b.part.forward(h, batch, **more)
 
 
 register_arrangement("prenorm", PreNorm)

@@ -19,14 +19,18 @@ from . import attention as _attention, block as _block, embedding as _embedding 
 from . import mlp as _mlp, norm as _norm, rope as _rope  # noqa: F401
 
 
+def _part_registry(role: str):
+    return MIXERS if role == "mixer" else FEED_FORWARDS
+
+
 def expected_tensors(spec: ModelSpec) -> dict:
     """Every tensor the model reads: name -> TensorSpec."""
     out = {}
     out.update(EMBEDDINGS.get(spec.embedding.kind).tensor_specs(spec.embedding.params, ""))
     for layer in spec.layers:
-        for reg, part in ((NORMS, layer.mixer_norm), (MIXERS, layer.mixer),
-                          (NORMS, layer.ffn_norm), (FEED_FORWARDS, layer.ffn)):
-            out.update(reg.get(part.kind).tensor_specs(part.params, layer.prefix))
+        for b in layer.branches():
+            out.update(NORMS.get(b.norm.kind).tensor_specs(b.norm.params, layer.prefix))
+            out.update(_part_registry(b.role).get(b.part.kind).tensor_specs(b.part.params, layer.prefix))
     out.update(NORMS.get(spec.final_norm.kind).tensor_specs(spec.final_norm.params, ""))
     out.update(HEADS.get(spec.head.kind).tensor_specs(spec.head.params, ""))
     return out
@@ -66,12 +70,29 @@ class TensorBank:
 
 
 @dataclass
+class Branch:
+    norm: object
+    part: object
+    role: str                       # "mixer" or "ffn"
+
+
+@dataclass
 class Layer:
-    mixer_norm: object
-    mixer: object
-    ffn_norm: object
-    ffn: object
+    """A built block: its branches in order, and how they are wired."""
+    branches: list
     arrangement: object
+
+    def _first(self, role, what):
+        for b in self.branches:
+            if b.role == role:
+                return getattr(b, what)
+        return None
+
+    # the usual block's parts by name
+    mixer = property(lambda self: self._first("mixer", "part"))
+    mixer_norm = property(lambda self: self._first("mixer", "norm"))
+    ffn = property(lambda self: self._first("ffn", "part"))
+    ffn_norm = property(lambda self: self._first("ffn", "norm"))
 
 
 class DecoderModel:
@@ -82,10 +103,9 @@ class DecoderModel:
         self.layers = []
         for ls in spec.layers:
             self.layers.append(Layer(
-                mixer_norm=NORMS.get(ls.mixer_norm.kind)(ls.mixer_norm.params, ls.prefix, env, tensors),
-                mixer=MIXERS.get(ls.mixer.kind)(ls.mixer.params, ls.prefix, env, tensors),
-                ffn_norm=NORMS.get(ls.ffn_norm.kind)(ls.ffn_norm.params, ls.prefix, env, tensors),
-                ffn=FEED_FORWARDS.get(ls.ffn.kind)(ls.ffn.params, ls.prefix, env, tensors),
+                branches=[Branch(NORMS.get(b.norm.kind)(b.norm.params, ls.prefix, env, tensors),
+                                 _part_registry(b.role).get(b.part.kind)(b.part.params, ls.prefix, env, tensors),
+                                 b.role) for b in ls.branches()],
                 arrangement=ARRANGEMENTS.get(ls.arrangement)(),
             ))
         self.final_norm = NORMS.get(spec.final_norm.kind)(spec.final_norm.params, "", env, tensors)
@@ -109,7 +129,9 @@ class DecoderModel:
     def parts(self):
         yield self.embedding
         for layer in self.layers:
-            yield from (layer.mixer_norm, layer.mixer, layer.ffn_norm, layer.ffn)
+            for b in layer.branches:
+                yield b.norm
+                yield b.part
         yield self.final_norm
         yield self.head
 
@@ -120,15 +142,22 @@ class DecoderModel:
 
     def cache_needs(self) -> dict:
         """cache id -> what the writing layer's mixer keeps between steps."""
+        def need_of(layer_index):
+            """What the layer's mixers keep between steps: a schedule entry names one cache, so one of them at most."""
+            found = [n for n in (MIXERS.get(b.part.kind).cache_need(b.part.params)
+                                 for b in self.spec.layers[layer_index].branches() if b.role == "mixer") if n is not None]
+            if len(found) > 1:
+                raise ValueError(f"layer {layer_index} has {len(found)} mixers that keep something between steps; "
+                                 "a layer's schedule entry names one cache")
+            return found[0] if found else None
+
         needs = {}
         for e in self.order:
             if e.writes:
-                ls = self.spec.layers[e.layer]
-                needs[e.cache] = MIXERS.get(ls.mixer.kind).cache_need(ls.mixer.params)
+                needs[e.cache] = need_of(e.layer)
         for e in self.order:
             if not e.writes:
-                ls = self.spec.layers[e.layer]
-                need = MIXERS.get(ls.mixer.kind).cache_need(ls.mixer.params)
+                need = need_of(e.layer)
                 if need != needs[e.cache]:
                     raise ValueError(f"layer {e.layer} reads cache {e.cache} whose geometry {needs[e.cache]} "
                                      f"differs from its own {need}")

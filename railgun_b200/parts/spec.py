@@ -22,14 +22,52 @@ class PartSpec:
 
 
 @dataclass(frozen=True)
+class SubLayer:
+    """One branch of a block around the residual stream: ``part`` (a mixer or a
+    feed-forward; ``role`` says which interface it has) behind ``norm``."""
+    norm: PartSpec
+    part: PartSpec
+    role: str                       # "mixer" or "ffn"
+
+    def __post_init__(self):
+        if self.role not in ("mixer", "ffn"):
+            raise ValueError(f"a sub-layer's role is 'mixer' or 'ffn', not {self.role!r}")
+
+
+@dataclass(frozen=True)
 class LayerSpec:
-    """One block: a mixer and a feed-forward, each behind its norm."""
+    """One block: a list of branches (norm, part) that its arrangement wires
+    around the residual stream.  The usual block, a mixer and a feed-forward
+    each behind its norm, can be given by the four fields of those names;
+    ``sublayers`` gives any other list: a single mixer, two feed-forwards,
+    three norms."""
     prefix: str                     # tensor-name prefix, e.g. "model.layers.3."
-    mixer: PartSpec
-    mixer_norm: PartSpec
-    ffn: PartSpec
-    ffn_norm: PartSpec
+    mixer: PartSpec | None = None
+    mixer_norm: PartSpec | None = None
+    ffn: PartSpec | None = None
+    ffn_norm: PartSpec | None = None
     arrangement: str = "prenorm"
+    sublayers: tuple = ()
+
+    def __post_init__(self):
+        if self.sublayers and (self.mixer or self.ffn or self.mixer_norm or self.ffn_norm):
+            raise ValueError("a LayerSpec is given by `sublayers` or by mixer / ffn with their norms, not both")
+        if not self.sublayers and ((self.mixer is None) != (self.mixer_norm is None)
+                                   or (self.ffn is None) != (self.ffn_norm is None)):
+            raise ValueError("a part and its norm are given together")
+        if not self.branches():
+            raise ValueError("a layer needs at least one branch")
+
+    def branches(self) -> tuple:
+        """The block's branches in the order they run."""
+        if self.sublayers:
+            return tuple(self.sublayers)
+        out = []
+        if self.mixer is not None:
+            out.append(SubLayer(self.mixer_norm, self.mixer, "mixer"))
+        if self.ffn is not None:
+            out.append(SubLayer(self.ffn_norm, self.ffn, "ffn"))
+        return tuple(out)
 
 
 @dataclass(frozen=True)

@@ -27,15 +27,24 @@ class Sampler:
         rows = logits.shape[0]
         if rows != len(params) or rows != len(counters):
             raise ValueError(f"{rows} rows of logits for {len(params)} parameter sets")
-        if all(p.temperature == 0.0 for p in params):
+        return self.sample_arrays(logits, dict(
+            temperature=np.array([p.temperature for p in params], dtype=np.float32),
+            top_k=np.array([p.top_k for p in params], dtype=np.int32),
+            top_p=np.array([p.top_p for p in params], dtype=np.float32),
+            seed=np.array([_as_i64(p.seed) for p in params], dtype=np.int64),
+            counter=np.array([int(c) for c in counters], dtype=np.int64)))
+
+    def sample_arrays(self, logits: torch.Tensor, sp: dict) -> np.ndarray:
+        """The same from arrays of one entry per row: ``temperature`` float32, ``top_k`` int32, ``top_p``
+        float32, ``seed`` int64 (the bits of an unsigned seed), ``counter`` int64 (the number of the draw)."""
+        rows = logits.shape[0]
+        if any(len(sp[k]) != rows for k in ("temperature", "top_k", "top_p", "seed", "counter")):
+            raise ValueError(f"{rows} rows of logits, but the parameter arrays have other lengths")
+        if not (sp["temperature"] != 0.0).any():
             return ops.argmax(logits).cpu().numpy()
-        temperature = torch.tensor([p.temperature for p in params], dtype=torch.float32)
-        top_k = torch.tensor([p.top_k for p in params], dtype=torch.int32)
-        top_p = torch.tensor([p.top_p for p in params], dtype=torch.float32)
-        seed = torch.tensor([_as_i64(p.seed) for p in params], dtype=torch.int64)
-        counter = torch.tensor([int(c) for c in counters], dtype=torch.int64)
-        dev = lambda t: t.to(self.device, non_blocking=True)
-        out = ops.sample(logits, dev(temperature), dev(top_k), dev(top_p), dev(seed), dev(counter))
+        dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(self.device, non_blocking=True)
+        out = ops.sample(logits, dev(sp["temperature"]), dev(sp["top_k"]), dev(sp["top_p"]), dev(sp["seed"]),
+                         dev(sp["counter"]))
         return out.cpu().numpy()
 
 

@@ -127,3 +127,27 @@ def test_needs_are_sorted_into_groups():
         0: full, 1: PagedKVNeed(2, 16, 8), 2: full, 3: StateNeed((4, 4)), 4: None, 5: PagedKVNeed(1, 16, 0)})
     assert [(n, c) for n, c in groups] == [(full, [0, 2]), (PagedKVNeed(2, 16, 8), [1]), (PagedKVNeed(1, 16, 0), [5])]
     assert group_of == {0: 0, 2: 0, 1: 1, 5: 2} and list(states) == [3]
+
+
+def test_groups_get_the_page_geometry_they_ask_for():
+    """Needs that say nothing get the engine's page size, pool and precision; a need may ask for its own page
+    size, a smaller pool (a windowed group), another precision and another shape of page."""
+    import torch
+    from railgun_b200.cache.manager import CacheManager, PagedKVNeed, StateNeed
+    needs = {0: PagedKVNeed(2, 16), 1: PagedKVNeed(2, 16),                       # one group, two cache ids
+             2: PagedKVNeed(1, 32, window=24, page_size=8, pool_tokens=96),      # windowed: small pages, small pool
+             3: PagedKVNeed(0, 0, dtype="float32", page_shape=("page", 40)),     # one compressed vector per token
+             4: StateNeed((5, 3), "float32"), 5: None}
+    cm = CacheManager(needs, page_size=16, max_tokens=256, max_requests=4, dtype=torch.bfloat16, device="cpu")
+    assert [(g.page_size, g.num_pages, g.cache_ids) for g in cm.groups] == [(16, 16, [0, 1]), (8, 12, [2]), (16, 16, [3])]
+    assert cm.kv[0].shape == (16, 2, 2, 16, 16) and cm.kv[0].dtype == torch.bfloat16
+    assert cm.kv[2].shape == (12, 2, 1, 8, 32) and cm.page_size_of(2) == 8
+    assert cm.kv[3].shape == (16, 16, 40) and cm.kv[3].dtype == torch.float32
+    assert cm.state[4].shape == (4, 5, 3) and 5 not in cm.kv and 5 not in cm.state
+    assert cm.bytes_per_token() == 2 * (2 * 2 * 16 * 2) + 2 * 1 * 32 * 2 + 40 * 4
+    # the allocator has the groups' own page sizes and pools: 20 tokens take 2, 3 and 2 pages
+    cm.alloc.add_request(1)
+    cm.alloc.reserve(1, 20)
+    assert [len(cm.alloc.block_table(1, g)) for g in range(3)] == [2, 3, 2]
+    assert [cm.alloc.free_pages(g) for g in range(3)] == [14, 9, 14]
+    cm.alloc.check()

@@ -30,7 +30,7 @@ class StandInRunner:
         self.last_greedy = None
         self.log = []
 
-    def decode_step_flat(self, ids, tokens, sampling=None):
+    def decode_step_flat(self, ids, tokens):
         pos = [self.alloc.num_computed(int(r)) for r in ids]
         for r, p in zip(ids, pos):
             self.alloc.reserve(int(r), p + 1)
@@ -45,7 +45,7 @@ class StandInRunner:
     def check_device_errors(self):
         pass
 
-    def decode_follow(self, ids, after, sampling=None):
+    def decode_follow(self, ids, after):
         ahead = 0 if after is None else 1
         pos = [self.alloc.num_computed(int(r)) + ahead for r in ids]
         for r, p in zip(ids, pos):
@@ -75,9 +75,9 @@ def make_engine(run_ahead, pages=64, page=4, seats=3, budget=32):
     alloc = PageAllocator([page], [pages], [0], seats)
     eng.runner = StandInRunner(alloc)
     eng.scheduler = Scheduler(alloc, SchedulerConfig(budget, seats, 0, 512))
-    eng.sampler = SimpleNamespace(sample=lambda logits, params, counters: logits)     # the stand-in's logits are tokens
-    eng._params, eng._next_id, eng.steps_run = {}, 1, 0
-    eng.run_ahead, eng._ahead, eng._sampling, eng.steps_ahead = run_ahead, None, None, 0
+    eng.sampler = SimpleNamespace(sample_arrays=lambda logits, sp: logits)             # the stand-in's logits are tokens
+    eng._next_id, eng.steps_run = 1, 0
+    eng.run_ahead, eng._ahead, eng.steps_ahead = run_ahead, None, 0
     eng.runner.model = SimpleNamespace(vocab_size=97)
     return eng
 
@@ -190,7 +190,7 @@ def test_stream_yields_every_token_as_its_step_ends():
     assert got[2] == expected_output(2, prompts[1], 9, [stop]) and last[2] == "stop_token" and got[2][-1] == stop
     assert got[3] == expected_output(3, prompts[2], 2) and last[3] == "max_tokens"
     # the engine keeps nothing of a streamed request once its last response is out
-    assert not eng.has_unfinished() and list(eng.scheduler.finished()) == [] and eng._params == {}
+    assert not eng.has_unfinished() and list(eng.scheduler.finished()) == []
     with pytest.raises(SchedulerError):
         eng.collect(2)
     eng.runner.alloc.check()
@@ -208,7 +208,7 @@ def test_requests_are_checked_when_they_are_added():
         eng.add_request([1] * 500, SamplingParams(max_new_tokens=100))
     with pytest.raises(ValueError):
         eng.add_request([1], SamplingParams(top_p=0.0))
-    assert not eng.has_unfinished() and eng._params == {}
+    assert not eng.has_unfinished()
     rid = eng.add_request(np.array([3, 4, 5]), SamplingParams(max_new_tokens=2))      # arrays are taken as lists are
     while eng.has_unfinished():
         eng.step()

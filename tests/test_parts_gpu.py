@@ -77,7 +77,7 @@ def test_prenorm_block_hands_unfinished_values_only_to_parts_that_take_them(rows
     from railgun_b200 import ops
     from railgun_b200.parts.base import Mixer, Norm, Stream
     from railgun_b200.parts.block import PreNorm
-    from railgun_b200.parts.model import Layer
+    from railgun_b200.parts.model import Branch, Layer
     from railgun_b200.parts.registry import FEED_FORWARDS, NORMS
     dtype, H, I, eps = torch.bfloat16, 72, 200, 1e-5
     rng = np.random.default_rng(rows)
@@ -122,9 +122,10 @@ def test_prenorm_block_hands_unfinished_values_only_to_parts_that_take_them(rows
         for l in ("a.", "b."):
             norm = lambda name: (NORMS.get("rmsnorm")(dict(size=H, eps=eps, name=name), l, env, tensors) if lazy
                                  else PlainNorm(tensors.get(l + name, torch.float32)))
-            layers.append(Layer(mixer_norm=norm("n1"), mixer=TwoLinears(l, tensors, lazy), ffn_norm=norm("n2"),
-                                ffn=FEED_FORWARDS.get("swiglu")(dict(hidden_size=H, intermediate_size=I), l, env, tensors),
-                                arrangement=PreNorm()))
+            layers.append(Layer(branches=[
+                Branch(norm("n1"), TwoLinears(l, tensors, lazy), "mixer"),
+                Branch(norm("n2"), FEED_FORWARDS.get("swiglu")(dict(hidden_size=H, intermediate_size=I), l, env, tensors),
+                       "ffn")], arrangement=PreNorm()))
         stream = Stream(torch.tensor(x0, dtype=torch.float32, device=DEV))
         for layer in layers:
             layer.arrangement.run(layer, stream, None, None, True)

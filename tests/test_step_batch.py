@@ -134,24 +134,70 @@ def test_a_step_that_runs_out_of_pages_gives_back_the_requests_it_added():
 
 
 def test_sampling_parameters_in_the_packed_decode_buffer():
-    """The decode graphs read the rows' sampling parameters from the tail of the packed buffer: 64-bit seeds
-    and draw counters first (at an even offset), then temperature, top-k, top-p; rows beyond the step's
-    requests are greedy."""
-    from railgun_b200.engine.runner import fill_sampling, sampling_views
-    B, off = 4, 38
-    buf = np.zeros(off + 7 * B, dtype=np.int32)
-    views = sampling_views(buf, off, B)
-    fill_sampling(views, dict(temperature=np.array([0.5, 0.0, 1.5], dtype=np.float32), top_k=np.array([3, 0, 40]),
-                              top_p=np.array([0.75, 1.0, 0.25], dtype=np.float32),
-                              seed=np.array([7, -1, 2 ** 62], dtype=np.int64), counter=np.array([0, 11, 12345678901])), 3)
-    assert buf[off:off + 2 * B].view(np.int64).tolist() == [7, -1, 2 ** 62, 0]
-    assert buf[off + 2 * B:off + 4 * B].view(np.int64).tolist() == [0, 11, 12345678901, 0]
-    assert buf[off + 4 * B:off + 5 * B].view(np.float32).tolist() == [0.5, 0.0, 1.5, 0.0]
-    assert buf[off + 5 * B:off + 6 * B].tolist() == [3, 0, 40, 0]
-    assert buf[off + 6 * B:off + 7 * B].view(np.float32).tolist() == [0.75, 1.0, 0.25, 0.0]
-    fill_sampling(views, None, 2)                               # a greedy step: every temperature is zero again
-    assert not buf[off + 4 * B:off + 5 * B].any()
-    assert not buf[:off].any()
+    """The decode graphs read the rows' sampling parameters from the tail of the packed buffer, where the
+    cache manager writes them from the requests' slot records: 64-bit seeds and draw counters first, then
+    temperature, top-k, top-p; rows beyond the step's requests are greedy."""
+    from railgun_b200.engine.runner import sampling_views
+    alloc = PageAllocator([16], [16], [0], 8)
+    for rid in (5, 6, 7):
+        alloc.add_request(rid)
+        alloc.reserve(rid, 3)
+        alloc.commit(rid, 3)
+    alloc.set_request(5, prompt_len=3, num_generated=0, max_new_tokens=9, temperature=0.5, top_k=3, top_p=0.75, seed=7)
+    alloc.set_request(7, prompt_len=1, num_generated=2, max_new_tokens=9, temperature=1.5, top_k=40, top_p=0.25,
+                      seed=2 ** 64 - 1)
+    B, MB = 4, 2
+    off = (5 + 1) * B + B * MB                               # what StaticDecodeBatch computes for one group (even)
+    buf = np.full(off + 7 * B, -99, dtype=np.int32)
+    ids = np.array([5, 6, 7], dtype=np.int64)
+    assert alloc.pack_decode(ids, B, MB, buf[B:], sampling=buf[off:], draw_ahead=0) is True
+    v = sampling_views(buf, off, B)
+    assert v["seed"].tolist() == [7, 0, -1, 0] and v["counter"].tolist() == [0, 0, 2, 0]
+    assert v["temperature"].tolist() == [0.5, 0.0, 1.5, 0.0] and v["top_k"].tolist() == [3, 0, 40, 0]
+    assert v["top_p"].tolist() == [0.75, 1.0, 0.25, 1.0]
+    assert buf[B:2 * B].tolist() == [3, 3, 3, 0]              # positions; the padding row is at 0
+    # the step after it, launched ahead: the draws are numbered one further
+    alloc.pack_decode(ids, B, MB, buf[B:], ahead=1, sampling=buf[off:], draw_ahead=1)
+    assert v["counter"].tolist() == [1, 1, 3, 0] and buf[B:2 * B].tolist() == [4, 4, 4, 0]
+    # all greedy: nothing samples
+    assert alloc.pack_decode(np.array([6], dtype=np.int64), B, MB, buf[B:], sampling=buf[off:]) is False
+    assert not v["temperature"].any()
+
+
+def test_request_records():
+    """One record of fixed size per state slot: the cache manager keeps the position, the scheduler the lengths
+    and the sampling parameters; a slot's record is cleared when the request leaves, and the scheduler writes it
+    again when a preempted request comes back."""
+    from railgun_b200.cache.manager import REQUEST_RECORD
+    from railgun_b200.engine.scheduler import Scheduler, SchedulerConfig
+    alloc = PageAllocator([4], [6], [0], 2)
+    assert REQUEST_RECORD.itemsize == 64 and alloc.records.shape == (2,)
+    assert alloc.records["request_id"].tolist() == [-1, -1]
+    s = Scheduler(alloc, SchedulerConfig(64, 2, 0, 64))
+    s.add_request(11, [1] * 7, 9, temperature=0.7, top_k=5, top_p=0.9, seed=2 ** 63 + 5)
+    s.add_request(12, [2] * 6, 9)
+    s.schedule()
+    r = alloc.record(11)
+    assert (r["request_id"], r["num_computed"], r["prompt_len"], r["num_generated"], r["max_new_tokens"]) == (11, 0, 7, 0, 9)
+    assert (float(r["temperature"]), r["top_k"], float(r["top_p"]), int(r["seed"])) == (np.float32(0.7), 5, np.float32(0.9), 2 ** 63 + 5)
+    s.update([11, 12], [40, 41])
+    r = alloc.record(11)
+    assert (r["num_computed"], r["num_generated"], r["last_token"]) == (7, 1, 40)
+    assert s.sampling_many([11, 12])["counter"].tolist() == [1, 1]
+    # decoding until the pool is exhausted preempts the request admitted last; its record goes with its slot
+    for step in range(6):
+        entries = s.schedule()
+        if s.preempted():
+            break
+        s.update([e.request_id for e in entries], [50 + step] * len(entries))
+    assert s.preempted() == [12] and not alloc.has(12)
+    assert sorted(alloc.records["request_id"].tolist()) == [-1, 11]
+    generated = s.num_generated(12)
+    s.abort(11)
+    s.schedule()                                             # 12 comes back, as one longer prompt
+    r = alloc.record(12)
+    assert (r["prompt_len"], r["num_generated"], r["num_computed"]) == (6, generated, 0) and r["temperature"] == 0.0
+    alloc.check()
 
 
 def test_rows_of_a_step_launched_ahead():

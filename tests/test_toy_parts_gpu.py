@@ -1,6 +1,8 @@
 """Parts that are not in the framework, defined here and registered from
 outside: a mixer with state of its own (a decaying running sum kept in the
-request's state slot), a feed-forward of another shape, a feed-forward that
+request's state slot), once planned on the host and once written with device
+operations only so that its steps replay from CUDA graphs, a layer with three
+branches and three norms, a feed-forward of another shape, a feed-forward that
 routes every token to one of several experts, a position encoding that is no
 rotation, and architectures made of them beside the built-in attention.
 Nothing in the framework's files changes; the models are built, stepped in
@@ -23,13 +25,15 @@ def register_toys():
     from railgun_b200 import ops
     from railgun_b200.cache.manager import StateNeed
     from railgun_b200.config.registry import Architecture, register_architecture
-    from railgun_b200.parts import (FeedForward, LayerSpec, Mixer, ModelSpec, PartSpec, register_feed_forward,
-                                    register_mixer)
+    from railgun_b200.parts import (FeedForward, LayerSpec, Mixer, ModelSpec, PartSpec, SubLayer,
+                                    register_feed_forward, register_mixer)
     from railgun_b200.weights.loader import TensorSpec
 
     class DecayingSum(Mixer):
         """state_t = DECAY * state_{t-1} + x_t ; y_t = W state_t.  The state of
-        each request lives in its slot between steps."""
+        each request lives in its slot between steps.  This one walks the
+        requests on the host, so it says that its steps cannot be captured."""
+        graph_safe = False
 
         @classmethod
         def tensor_specs(cls, p, prefix):
@@ -56,6 +60,35 @@ def register_toys():
                     out[t] = s
             return ops.linear(out.to(x.dtype), self.w)
 
+    class DecayingSumOnDevice(DecayingSum):
+        """The same mixer from the step's device-side description alone (token offsets, start positions and
+        state slots as tensors; the longest portion as a number that the step's layout fixes): nothing is read
+        back, so the model's steps can be captured and replayed.  Rows without a request (slot -1, the padding
+        of a static decode batch) touch no state."""
+        graph_safe = True
+
+        def forward(self, x, batch, cache, writes=True):
+            state = cache.state                                            # [slots, H] float32
+            cu = batch.cu_seqlens.long()
+            first, counts = cu[:-1], cu[1:] - cu[:-1]
+            slots = batch.state_slots.long()
+            live = slots >= 0
+            slot = slots.clamp(min=0)
+            fresh = (batch.start_pos == 0) & live
+            out = torch.zeros_like(x, dtype=torch.float32)
+            xf = x.float()
+            last_row = x.shape[0] - 1
+            for j in range(batch.max_query_len):
+                on = live & (counts > j)
+                row = (first + j).clamp(max=last_row)
+                old = state[slot]
+                base = torch.where(fresh[:, None], torch.zeros_like(old), old) if j == 0 else old
+                new = DECAY * base + xf[row]
+                # every live slot gets exactly one change, rows that are off add zero: duplicates cannot collide
+                state.index_add_(0, slot, torch.where(on[:, None], new - old, torch.zeros_like(old)))
+                out.index_add_(0, row, torch.where(on[:, None], new, torch.zeros_like(new)))
+            return ops.linear(out.to(x.dtype), self.w)
+
     class ReluMLP(FeedForward):
         @classmethod
         def tensor_specs(cls, p, prefix):
@@ -71,6 +104,7 @@ def register_toys():
             return ops.linear(torch.relu(ops.linear(x, self.up)), self.down)
 
     register_mixer("toy_decaying_sum", DecayingSum, replace=True)
+    register_mixer("toy_decaying_sum_on_device", DecayingSumOnDevice, replace=True)
     register_feed_forward("toy_relu_mlp", ReluMLP, replace=True)
 
     def config_from_dict(d, where=""):
@@ -86,11 +120,18 @@ def register_toys():
         attn = PartSpec("paged_attention", dict(
             hidden_size=H, num_heads=c.heads, num_kv_heads=c.kv_heads, head_dim=c.head_dim, window=0, scale=None,
             position=PartSpec("rope", dict(head_dim=c.head_dim, theta=1000.0, scaling=None, max_position=c.max_pos))))
-        toy = PartSpec("toy_decaying_sum", dict(hidden_size=H))
+        toy = PartSpec(getattr(c, "toy_mixer", "toy_decaying_sum"), dict(hidden_size=H))
         swiglu = PartSpec("swiglu", dict(hidden_size=H, intermediate_size=c.inner))
         relu = PartSpec("toy_relu_mlp", dict(hidden_size=H, inner=c.inner))
         layers = []
         for i, kind in enumerate(c.layer_kinds):             # mixers and feed-forwards differ layer by layer
+            if kind == "three":
+                # a block of three branches, each behind a norm of its own: attention, then two feed-forwards
+                layers.append(LayerSpec(prefix=f"model.layers.{i}.", sublayers=(
+                    SubLayer(norm("input_layernorm.weight"), attn, "mixer"),
+                    SubLayer(norm("post_attention_layernorm.weight"), relu, "ffn"),
+                    SubLayer(norm("third_layernorm.weight"), swiglu, "ffn"))))
+                continue
             layers.append(LayerSpec(prefix=f"model.layers.{i}.", mixer=toy if kind == "toy" else attn,
                                     mixer_norm=norm("input_layernorm.weight"),
                                     ffn=relu if kind == "toy" else swiglu,
@@ -132,9 +173,48 @@ def plain_toy_forward(model_dir, ids):
             v = P.linear(h, w[p + "self_attn.v_proj.weight"]).reshape(T, nkv, d)
             x = x + P.linear(P.attention(q, k, v, pos).reshape(T, nh * d), w[p + "self_attn.o_proj.weight"])
             h = P.rms_norm(x, w[p + "post_attention_layernorm.weight"], cfg["eps"])
+            if kind == "three":
+                x = x + P.linear(np.maximum(P.linear(h, w[p + "toy.up.weight"]), 0), w[p + "toy.down.weight"])
+                h = P.rms_norm(x, w[p + "third_layernorm.weight"], cfg["eps"])
             x = x + P.swiglu(h, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"],
                              w[p + "mlp.down_proj.weight"])
     return P.linear(P.rms_norm(x, w["model.norm.weight"], cfg["eps"]), w["emb"])
+
+
+def test_stateful_layers_and_three_branch_layers_replay_from_graphs(tmp_path):
+    """The stateful mixer written with device operations only, beside attention layers and a layer of three
+    branches with three norms: steps of single tokens replay CUDA graphs (static batches with padding rows),
+    large repeated steps replay graphs captured for their layout, and every logit matches the plain statement."""
+    from railgun_b200.config.registry import load_config
+    from railgun_b200.engine.runner import ModelRunner
+    from railgun_b200.replay import Replayer
+    from railgun_b200.weights.random_init import write_random_model
+    register_toys()
+    cfg_dict = dict(TOY_CFG, toy_mixer="toy_decaying_sum_on_device", layer_kinds=["attn", "toy", "three", "toy"])
+    mdir = tmp_path / "toy"
+    mdir.mkdir()
+    (mdir / "config.json").write_text(json.dumps(cfg_dict))
+    arch, cfg = load_config(mdir)
+    write_random_model(cfg, 3, mdir, std=0.15)
+    (mdir / "config.json").write_text(json.dumps(cfg_dict))
+    reqs = {f"t{i}": p for i, p in enumerate(helpers.prompts(TOY_CFG["vocab"], [30, 9, 55, 41, 17], seed=8))}
+    for mode, make in (("tail", lambda r: helpers.trace_tail_decode(r, 12)),
+                       ("mixed", lambda r: helpers.trace_mixed(r, max_live=3, seed=2))):
+        steps = make(reqs)
+        runner = ModelRunner(mdir, dtype="float32", page_size=8, max_tokens=helpers.peak_tokens(steps, 64),
+                             max_requests=3)
+        assert runner.use_graphs and len(runner.cache.state) == 2
+        runner.shape_graph_min_tokens = 2
+        rp = Replayer(runner, tmp_path / mode)
+        for s in steps:
+            rp.feed(s)
+        assert runner._static, "no step of single tokens replayed a graph"
+        rows = helpers.collect(steps, tmp_path / mode, TOY_CFG["vocab"])
+        for name, toks in reqs.items():
+            ref = plain_toy_forward(mdir, toks)
+            for p in range(len(toks)):
+                assert np.abs(rows[(name, p)] - ref[p]).max() / np.abs(ref).max() < 2e-5, (mode, name, p)
+        runner.alloc.check()
 
 
 @pytest.mark.parametrize("dtype,tol", [("float32", 2e-5), ("bfloat16", 3e-2)])
@@ -157,6 +237,7 @@ def test_toy_architecture_with_a_stateful_mixer(mode, dtype, tol, tmp_path):
     runner = ModelRunner(mdir, dtype=dtype, page_size=8, max_tokens=helpers.peak_tokens(steps, 64),
                          max_requests=3)
     assert len(runner.cache.state) == 2 and len(runner.cache.kv) == 2      # two stateful layers, two paged ones
+    assert not runner.use_graphs                            # the mixer said that it plans on the host
     rp = Replayer(runner, tmp_path / "out")
     for s in steps:
         rp.feed(s)
