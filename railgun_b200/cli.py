@@ -3,7 +3,10 @@
 ``generate`` keeps the reference's options and meanings
 (crates/vllm-cli/src/generate.rs:29-53): ``--model/-m DIR``, ``--max-tokens``
 (default 128), ``--temperature`` (default 0.0 = greedy; honoured here, the
-reference parses and ignores it), ``--cuda-device N``, ``--show-token-ids``.
+reference parses and ignores it), ``--cuda-device N``, ``--show-token-ids``.  ``--random-weights SEED`` runs a
+folder's config.json with seeded random weights.  Log messages are filtered by
+``RAILGUN_LOG`` (default info), as the reference filters by an environment
+variable (crates/vllm-cli/src/main.rs:40-49).
 Prompts are token ids (``--prompt-ids 1,2,3;4,5``), or, as in the reference,
 text (``--prompt/-p TEXT``) when the model folder holds a ``tokenizer.json``
 (read with the ``tokenizers`` library, the one the reference's
@@ -48,6 +51,8 @@ def make_parser() -> argparse.ArgumentParser:
     g.add_argument("--num-gpu-blocks", type=int, default=1000)
     g.add_argument("--max-model-len", type=int, default=4096)
     g.add_argument("--max-prefill-chunk", type=int, default=0)
+    g.add_argument("--random-weights", type=int, default=None, metavar="SEED",
+                   help="ignore the folder's weights: draw them from SEED for its config.json (into a temporary folder)")
 
     r = sub.add_parser("random-weights", help="write a model folder with seeded random weights")
     r.add_argument("--config", required=True, help="a config.json to take the sizes from")
@@ -100,8 +105,19 @@ def run_generate(args) -> int:
     if not prompts or any(not p for p in prompts):
         print("error: the prompt needs at least one token", file=sys.stderr)
         return 2
+    model_dir, scratch = args.model, None
+    if args.random_weights is not None:
+        import os
+        import shutil
+        import tempfile
+        from .config.registry import load_config
+        from .weights.random_init import write_random_model
+        scratch = tempfile.mkdtemp(prefix="railgun_random_")
+        write_random_model(load_config(args.model)[1], args.random_weights, scratch)
+        shutil.copyfile(os.path.join(str(args.model), "config.json"), os.path.join(scratch, "config.json"))
+        model_dir = scratch
     t0 = time.time()
-    engine = Engine(args.model, dtype=args.dtype, cuda_device=args.cuda_device, block_size=args.block_size,
+    engine = Engine(model_dir, dtype=args.dtype, cuda_device=args.cuda_device, block_size=args.block_size,
                     num_gpu_blocks=args.num_gpu_blocks, max_num_seqs=args.max_num_seqs,
                     max_num_batched_tokens=args.max_num_batched_tokens, max_model_len=args.max_model_len,
                     max_prefill_chunk=args.max_prefill_chunk)
@@ -121,6 +137,9 @@ def run_generate(args) -> int:
             print(",".join(str(t) for t in o.token_ids))
         if o.error:
             print(f"[error] request {o.request_id}: {o.error}", file=sys.stderr)
+    if scratch is not None:
+        import shutil
+        shutil.rmtree(scratch, ignore_errors=True)
     n = sum(len(o.token_ids) for o in outs)
     print(f"[stats] {n} tokens in {dt * 1e3:.1f} ms = {n / dt:.1f} tok/s (load {load_ms:.0f} ms)")
     return 0

@@ -19,6 +19,7 @@ from __future__ import annotations
 import contextlib
 import dataclasses
 import gc
+import os
 
 import numpy as np
 import torch
@@ -63,6 +64,10 @@ def raise_device_error(code: int):
     if code == 1:
         raise RuntimeError("a kernel met a position outside its table")
     raise RuntimeError(f"a kernel flagged error {code}; the step's result is invalid")
+
+
+# RAILGUN_B200_NVTX=1 puts a named range around every step (visible in a profiler's timeline).
+NVTX = os.environ.get("RAILGUN_B200_NVTX", "0") == "1"
 
 
 def parse_dtype(name):
@@ -270,6 +275,15 @@ class ModelRunner:
         entries and of each entry's ``want``, or None if nothing is wanted.
         The result may be a view of a buffer the next step overwrites."""
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
+        if NVTX:
+            torch.cuda.nvtx.range_push(f"step {len(entries)} requests {sum(len(e.tokens) for e in entries)} tokens")
+            try:
+                return self._step(entries)
+            finally:
+                torch.cuda.nvtx.range_pop()
+        return self._step(entries)
+
+    def _step(self, entries):
         self.last_greedy = None
         if self.use_graphs and entries and all(
                 len(e.tokens) == 1 and list(e.want) == [0] and self.alloc.has(e.request_id) for e in entries):

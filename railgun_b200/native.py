@@ -45,7 +45,10 @@ _loaded: dict[str, ctypes.CDLL] = {}
 
 
 def _say(msg: str) -> None:
-    print(f"[railgun_b200] {msg}", file=sys.stderr, flush=True)
+    from . import log
+    log.info(msg)
+    for h in log.handlers:
+        h.flush()
 
 
 def _find(tool: str, extra: list[str]) -> str:

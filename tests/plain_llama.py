@@ -11,8 +11,14 @@ Three of the reference's CUDA kernels do compile as host C++ through a small
 stand-in header; ``tests/golden/make_reference_kernel_golden.py`` ran them once
 and ``tests/test_golden.py`` holds ``attention`` and ``rope`` below against
 their stored outputs (cache layout, head grouping, softmax-weighted values for
-a single query, rotation of pairs (i, i + d/2)).  Everything else rests on the
-formulas.
+a single query, rotation of pairs (i, i + d/2)).  Everything else (RMSNorm with
+eps inside the root, SiLU and the gated feed-forward, the llama3 frequency
+scaling, the causal mask inside a prompt, head grouping in a whole model, the
+tied or untied head) rests on the formulas alone; for those the whole model is
+stated a second time, independently, as scalar loops in C++
+(``tests/ref/llama_scalar.cpp``), and ``tests/test_plain_twin.py`` holds the two
+statements' logits together.  Model code of installed packages is not used as
+a source for either.
 
 Whole sequences, no cache, float64 arithmetic, one function per part.  It
 shares no code with ``railgun_b200``: it reads config.json and

@@ -21,6 +21,22 @@ def test_generate_options_and_defaults():
                        "--cuda-device", "1", "--show-token-ids", "--dtype", "f32"])
     assert (a.prompt_ids, a.max_tokens, a.temperature, a.top_k, a.top_p, a.seed) == ("1,2;3", 7, 0.5, 40, 0.9, 3)
     assert (a.stop_token_ids, a.cuda_device, a.show_token_ids, a.dtype) == ("2,9", 1, True, "f32")
+    assert a.random_weights is None
+    assert ap.parse_args(["generate", "-m", "dir", "--prompt-ids", "1", "--random-weights", "5"]).random_weights == 5
+
+
+def test_log_level_comes_from_the_environment(monkeypatch):
+    import logging
+    import railgun_b200
+    monkeypatch.setenv("RAILGUN_LOG", "error")
+    railgun_b200.init_logging()
+    assert railgun_b200.log.level == logging.ERROR
+    monkeypatch.setenv("RAILGUN_LOG", "debug")
+    railgun_b200.init_logging()
+    assert railgun_b200.log.level == logging.DEBUG
+    monkeypatch.delenv("RAILGUN_LOG")
+    railgun_b200.init_logging()
+    assert railgun_b200.log.level == logging.INFO              # the reference's default
 
 
 @pytest.mark.parametrize("argv", [["generate", "-m", "dir"],                                  # no prompt at all

@@ -298,6 +298,20 @@ def test_generate_command(tmp_path):
     assert lines[-1].startswith("[stats] 12 tokens") and "tok/s" in lines[-1]
 
 
+def test_generate_command_with_random_weights(tmp_path):
+    """``--random-weights SEED``: the folder's config.json with weights drawn from the seed; the same seed gives
+    the same tokens, another seed other weights."""
+    def run(seed):
+        proc = subprocess.run(
+            [sys.executable, os.path.join(ROOT, "bin", "railgun"), "generate", "--model", str(helpers.model_dir("A")),
+             "--prompt-ids", "5,6,7", "--max-tokens", "8", "--dtype", "f32", "--num-gpu-blocks", "32",
+             "--random-weights", str(seed)], capture_output=True, text=True, timeout=600)
+        assert proc.returncode == 0, proc.stderr[-2000:]
+        return proc.stdout.strip().splitlines()[0]
+    first = run(3)
+    assert len(first.split(",")) == 8 and run(3) == first and run(4) != first
+
+
 def test_generate_command_with_a_text_prompt(tmp_path):
     """``--prompt/-p TEXT`` with a tokenizer.json in the model folder (a word-level toy made here): the
     same tokens as the ids path, the text printed after the prompt, generation ended by the tokenizer's
