@@ -421,6 +421,20 @@ def run_kernels(args):
                     rows = ops.skinny_gemm_residual(x, weights(H, H)[0], resid, nw, 1e-5)
                     more["norm_finishing_us"] = round(timed(lambda: [ops.skinny_gemm_scaled(rows, w, silu_mul=silu) for w in ws]), 2)
                 out(f"decode product {name} M{M} ({n} x {k})", us, GBs=round(n * k * 2 / us / 1e3, 1), cublas_us=round(us_lib, 2), **more)
+    if on("decode_gemm_mid"):
+        # decode batches of 17 to 64 rows: the swapped-operand tcgen05 product against the library
+        for M in (32, 64):
+            x = torch.randn(M, H, device=dev).to(torch.bfloat16)
+            xi = torch.randn(M, I, device=dev).to(torch.bfloat16)
+            for name, n, k, silu in (("qkv", QKV, H, False), ("o", H, H, False), ("gate_up", 2 * I, H, True), ("down", H, I, False)):
+                ws = weights(n, k)
+                inp = xi if k == I else x
+                res = {}
+                for sp in (0, 1, 2, 4, 8):
+                    res[f"splits{sp}"] = round(timed(lambda: [ops.tc_stream_gemm(inp, w, silu_mul=silu, splits=sp) for w in ws]), 2)
+                us_lib = timed(lambda: [ops.silu_mul(torch.mm(inp, w.t()), interleaved=True) if silu else torch.mm(inp, w.t()) for w in ws])
+                out(f"decode product {name} M{M} ({n} x {k})", res["splits0"], GBs=round(n * k * 2 / res["splits0"] / 1e3, 1),
+                    cublas_us=round(us_lib, 2), **res)
     if on("decode_attention"):
         for B, ctx in ((1, 1024), (8, 1024), (64, 1024), (8, 8192)):
             blocks = -(-ctx // page)
@@ -490,7 +504,7 @@ def main():
                     help="all: the contract's line; decode / prefill: one short measurement (for profiling); "
                          "kernels: the hot kernels one by one")
     ap.add_argument("--cases", default="", help="--mode kernels: comma-separated subset of sampling, decode_gemm, "
-                    "decode_attention, prefill_gemm, prefill_attention")
+                    "decode_gemm_mid, decode_attention, prefill_gemm, prefill_attention")
     ap.add_argument("--batch", type=int, default=8, help="--mode decode: requests in the batch")
     ap.add_argument("--tokens", type=int, default=PREFILL_TOKENS, help="--mode prefill: prompt length")
     ap.add_argument("--context", type=int, default=CONTEXT, help="--mode decode: tokens each request holds")

@@ -555,6 +555,152 @@ def tc_gemm(x: torch.Tensor, weight: torch.Tensor, out_dtype=None, silu_mul: boo
     return out
 
 
+TC_STREAM_MAX_ROWS = 64
+# From 17 rows up to here a decode batch's layer products go through the streaming tcgen05 product with the
+# neighbouring operations in its epilogues (residual addition, RMSNorm, rotation and cache write, SiLU-mul).  Alone
+# the product is level with the library's; the step gains what the separate small kernels cost (measured at
+# 1,024-token contexts: 10 % at batch 24, 6 % at 48, 3 % at 64).  RAILGUN_B200_TC_STREAM_ROWS overrides (16: off).
+TC_STREAM_AUTO_ROWS = int(os.environ.get("RAILGUN_B200_TC_STREAM_ROWS", "64"))
+
+
+def tc_stream_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    """Can the weight-streaming tcgen05 product (up to 64 rows of x) take these operands?"""
+    return 0 < x.shape[0] <= TC_STREAM_MAX_ROWS and tc_gemm_ok(x, weight)
+
+
+def tc_stream_gemm(x, weight: torch.Tensor, out_dtype=None, silu_mul: bool = False, splits: int = 0,
+                   check: bool = False) -> torch.Tensor:
+    """y = x W^T for up to 64 rows of x on the tcgen05 tensor cores with the operands swapped: 128 rows of W per
+    tile stream through once, the rows of x are the narrow side.  ``silu_mul``: W is interleaved gate|up storage
+    and y = silu(gate) * up.  ``splits``: 1, 2, 4 or 8 CTAs of a cluster share a tile's K and add their partial
+    sums in rank order (0: as many as keep the product in one wave).  A row's result does not depend on the other
+    rows.  ``x`` may be a ``NormedRows`` (an RMSNorm not finished yet): the product runs over its scaled rows and
+    multiplies the 32-bit sums by 1 / rms.  The kernel's waits are bounded; ``tc_gemm_check()`` (or ``check=True``)
+    raises if one gave up."""
+    rows = x if isinstance(x, NormedRows) else None
+    if rows is not None:
+        x = rows.scaled
+    if not tc_stream_ok(x, weight):
+        raise KernelError(f"tc_stream_gemm refuses x {tuple(x.shape)} {x.dtype} stride {x.stride()}, "
+                          f"W {tuple(weight.shape)} {weight.dtype}: bfloat16, at most 64 rows, K a multiple of 8")
+    M, K = x.shape
+    N = weight.shape[0]
+    if weight.shape[1] != K:
+        raise KernelError(f"tc_stream_gemm: x has {K} columns, W has {weight.shape[1]}")
+    out_dtype = out_dtype or torch.bfloat16
+    if silu_mul and (N % 16 or out_dtype != torch.bfloat16):
+        raise KernelError("tc_stream_gemm: the SiLU-mul epilogue needs N % 16 == 0 and bfloat16 output")
+    if splits not in (0, 1, 2, 4, 8) or (splits and -(-K // 64) < splits):
+        raise KernelError(f"tc_stream_gemm: {splits} splits of K = {K}")
+    err = _tc_err.get(x.device)
+    if err is None:
+        err = _tc_err[x.device] = torch.zeros(1, dtype=torch.int32, device=x.device)
+    global _tc_unchecked
+    _tc_unchecked = True
+    out = torch.empty((M, N // 2 if silu_mul else N), dtype=out_dtype, device=x.device)
+    _ok(_fn("gemm_stream_tcgen05", "rg_tc_stream_gemm")(
+        _ptr(x), c_int(x.stride(0)), _ptr(weight), _ptr(out), c_int(out.shape[1]), c_int(_dtype_code(out)),
+        c_int(1 if silu_mul else 0), c_int(M), c_int(N), c_int(K), c_int(splits),
+        _ptr(rows.partials if rows is not None else None), c_int(rows.blocks if rows is not None else 0),
+        c_int(rows.partials.stride(0) if rows is not None else 0), c_float(rows.eps if rows is not None else 0.0),
+        _ptr(err), _stream()), "tc_stream_gemm")
+    if check:
+        tc_gemm_check(x.device)
+    return out
+
+
+def tc_stream_rope_ok(x, weight: torch.Tensor, d: int) -> bool:
+    """Can the q|k|v projection of these rows (17 to 64 of them) rotate and write the cache in the streaming
+    tcgen05 product's own kernel?"""
+    if d % 16:
+        return False
+    if isinstance(x, NormedRows):
+        return tc_stream_scaled_ok(x, weight)
+    return SKINNY_AUTO_ROWS < x.shape[0] <= TC_STREAM_AUTO_ROWS and tc_stream_ok(x, weight)
+
+
+def tc_stream_gemm_rope_cache(x, weight: torch.Tensor, table: torch.Tensor, positions: torch.Tensor, slots, kv_cache,
+                              nh: int, nkv: int, d: int, err_flag=None, splits: int = 0) -> torch.Tensor:
+    """``skinny_gemm_rope_cache`` for up to 64 rows: the q|k|v projection with the rotary encoding and the cache
+    write in the product's epilogue.  Returns [M, (nh+2nkv)d] whose q heads are rotated (its k and v columns are
+    not written); k (rotated) and v go to ``kv_cache`` at ``slots`` (None: no write).  ``x``: bfloat16 rows or a
+    ``NormedRows``; ``weight``'s q and k rows are in ``rope_pair_order``."""
+    rows = x if isinstance(x, NormedRows) else None
+    xin = rows.scaled if rows is not None else x
+    if d % 16 or not tc_stream_ok(xin, weight):
+        raise KernelError(f"tc_stream_gemm_rope_cache refuses rows {tuple(xin.shape)}, W {tuple(weight.shape)}, head size {d}")
+    M, K = xin.shape
+    N = weight.shape[0]
+    if weight.shape[1] != K or N != (nh + 2 * nkv) * d:
+        raise KernelError(f"tc_stream_gemm_rope_cache: W {tuple(weight.shape)} is not [({nh} + 2 x {nkv}) x {d}, {K}]")
+    _check(table, "rope table", torch.float32)
+    _check(positions, "positions", torch.int32)
+    if table.shape[1] != d or positions.numel() < M:
+        raise KernelError("tc_stream_gemm_rope_cache: the table's head size or the number of positions does not match")
+    page_size = 0
+    if slots is not None:
+        _check(slots, "slots", torch.int32)
+        _check(kv_cache, "kv_cache", torch.bfloat16)
+        page_size = kv_cache.shape[3]
+        if tuple(kv_cache.shape[1:]) != (2, nkv, page_size, d) or slots.numel() < M:
+            raise KernelError(f"kv cache shape {tuple(kv_cache.shape)} does not match [pages, 2, {nkv}, page, {d}]")
+    err = _tc_err.get(xin.device)
+    if err is None:
+        err = _tc_err[xin.device] = torch.zeros(1, dtype=torch.int32, device=xin.device)
+    global _tc_unchecked
+    _tc_unchecked = True
+    out = torch.empty((M, N), dtype=torch.bfloat16, device=xin.device)
+    _ok(_fn("gemm_stream_tcgen05", "rg_tc_stream_gemm_rope_cache")(
+        _ptr(xin), c_int(xin.stride(0)), _ptr(weight), _ptr(out), c_int(N), c_int(M), c_int(N), c_int(K), c_int(splits),
+        _ptr(rows.partials if rows is not None else None), c_int(rows.blocks if rows is not None else 0),
+        c_int(rows.partials.stride(0) if rows is not None else 0), c_float(rows.eps if rows is not None else 0.0),
+        _ptr(table), _ptr(positions), _ptr(slots), _ptr(kv_cache if slots is not None else None), c_int(nh), c_int(nkv),
+        c_int(d), c_int(page_size), c_int(table.shape[0]), _ptr(err_flag), _ptr(err), _stream()),
+        "tc_stream_gemm_rope_cache")
+    return out
+
+
+def tc_stream_fused_ok(x: torch.Tensor, weight: torch.Tensor, resid: torch.Tensor) -> bool:
+    """Can x W^T be added to ``resid`` inside the streaming tcgen05 product (which then also prepares the next
+    norm)?  Decode batches above the skinny product's and up to ``TC_STREAM_AUTO_ROWS`` rows."""
+    return (SKINNY_AUTO_ROWS < x.shape[0] <= TC_STREAM_AUTO_ROWS and tc_stream_ok(x, weight)
+            and resid.dtype == torch.float32 and resid.is_contiguous() and resid.shape == (x.shape[0], weight.shape[0])
+            and resid.shape[1] % 8 == 0)
+
+
+def tc_stream_gemm_residual(x: torch.Tensor, weight: torch.Tensor, resid: torch.Tensor, norm_weight: torch.Tensor,
+                            eps: float, splits: int = 0) -> NormedRows:
+    """resid += x W^T (32-bit, in place), and the RMSNorm (``norm_weight``, ``eps``) of the new rows but for the
+    factor 1 / rms, which the product that reads the result applies (``skinny_gemm_residual`` for 17 to 64 rows)."""
+    if not tc_stream_ok(x, weight):
+        raise KernelError(f"tc_stream_gemm_residual refuses x {tuple(x.shape)} {x.dtype}, W {tuple(weight.shape)}")
+    _check(resid, "resid", torch.float32)
+    _check(norm_weight, "norm_weight", torch.float32)
+    M, K = x.shape
+    N = weight.shape[0]
+    if weight.shape[1] != K or resid.shape != (M, N) or norm_weight.numel() != N:
+        raise KernelError(f"tc_stream_gemm_residual: x {tuple(x.shape)}, W {tuple(weight.shape)}, residual "
+                          f"{tuple(resid.shape)}, norm weight {norm_weight.numel()}")
+    partials = torch.empty((-(-N // 128), TC_STREAM_MAX_ROWS), dtype=torch.float32, device=x.device)
+    scaled = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    err = _tc_err.get(x.device)
+    if err is None:
+        err = _tc_err[x.device] = torch.zeros(1, dtype=torch.int32, device=x.device)
+    global _tc_unchecked
+    _tc_unchecked = True
+    tiles = c_int(0)
+    _ok(_fn("gemm_stream_tcgen05", "rg_tc_stream_gemm_residual")(
+        _ptr(x), c_int(x.stride(0)), _ptr(weight), _ptr(resid), c_int(resid.stride(0)), _ptr(norm_weight), _ptr(scaled),
+        _ptr(partials), c_int(partials.stride(0)), c_int(M), c_int(N), c_int(K), c_int(splits), ctypes.byref(tiles),
+        _ptr(err), _stream()), "tc_stream_gemm_residual")
+    return NormedRows(resid, scaled, partials, tiles.value, norm_weight, eps, torch.bfloat16)
+
+
+def tc_stream_scaled_ok(rows: NormedRows, weight: torch.Tensor) -> bool:
+    return (rows.dtype == torch.bfloat16 and SKINNY_AUTO_ROWS < rows.shape[0] <= TC_STREAM_AUTO_ROWS
+            and tc_stream_ok(rows.scaled, weight) and rows.shape[1] == weight.shape[1])
+
+
 _tc_unchecked = False
 
 
@@ -678,6 +824,8 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype=None) -> torch.Tenso
     if isinstance(x, NormedRows):
         if (out_dtype is None or out_dtype == torch.bfloat16) and skinny_scaled_ok(x, weight):
             return skinny_gemm_scaled(x, weight)              # the norm is finished inside the product
+        if tc_stream_scaled_ok(x, weight):
+            return tc_stream_gemm(x, weight, out_dtype)      # likewise, for 17 to 64 rows
         x = x.materialize()
     if not x.is_cuda:
         raise KernelError("linear: CUDA tensors only (there is no CPU path)")

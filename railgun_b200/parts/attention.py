@@ -80,6 +80,11 @@ class PagedAttention(Mixer):
             # a few single tokens: projection, rotation and cache write in one kernel
             qkv = ops.skinny_gemm_rope_cache(x, self.w_qkv, self.position.rotary_table, batch.positions,
                                              slots if writes else None, cache.kv, nh, nkv, d, batch.err_flag)
+        elif (self.paired8 and self.env.dtype == torch.bfloat16 and batch.decode_only
+              and ops.tc_stream_rope_ok(x, self.w_qkv, d)):
+            # 17 to 64 single tokens: the same in the streaming tcgen05 product
+            qkv = ops.tc_stream_gemm_rope_cache(x, self.w_qkv, self.position.rotary_table, batch.positions,
+                                                slots if writes else None, cache.kv, nh, nkv, d, batch.err_flag)
         else:
             qkv = ops.linear(x, self.w_qkv)
             kv_dest = (cache.kv, slots) if writes else None

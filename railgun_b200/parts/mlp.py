@@ -44,9 +44,15 @@ class SwiGLU(FeedForward):
             if self.interleaved and ops.skinny_scaled_ok(x, self.w_gate_up):
                 act = ops.skinny_gemm_scaled(x, self.w_gate_up, silu_mul=True)   # decode: norm, product and SiLU-mul in one
                 return ops.PendingLinear(act, self.w_down) if defer else ops.linear(act, self.w_down)
+            if self.interleaved and ops.tc_stream_scaled_ok(x, self.w_gate_up):
+                act = ops.tc_stream_gemm(x, self.w_gate_up, silu_mul=True)       # the same for 17 to 64 rows
+                return ops.PendingLinear(act, self.w_down) if defer else ops.linear(act, self.w_down)
             x = x.materialize()
         if self.interleaved and x.shape[0] <= ops.SKINNY_AUTO_ROWS and ops.skinny_gemm_ok(x, self.w_gate_up):
             act = ops.skinny_gemm(x, self.w_gate_up, silu_mul=True)              # decode: weights streamed once
+        elif (self.interleaved and x.shape[0] <= ops.TC_STREAM_AUTO_ROWS and ops.tc_stream_ok(x, self.w_gate_up)):
+            # decode batches of 17 to 32 rows: the swapped-operand tcgen05 product, SiLU-mul in its epilogue
+            act = ops.tc_stream_gemm(x, self.w_gate_up, silu_mul=True)
         elif self.interleaved and x.shape[0] >= ops.TC_GEMM_MIN_ROWS and ops.tc_gemm_ok(x, self.w_gate_up):
             # prefill: tcgen05 on CTA pairs, SiLU-mul in the epilogue
             act = ops.tc_gemm(x, self.w_gate_up, silu_mul=True, tile="256x256")

@@ -35,6 +35,8 @@ class RMSNorm(Norm):
             # norm; the product that reads the result finishes it
             if rows is None and self.env.dtype == torch.bfloat16 and ops.skinny_fused_ok(pending.x, pending.weight, resid):
                 return ops.skinny_gemm_residual(pending.x, pending.weight, resid, self.weight, self.eps)
+            if rows is None and self.env.dtype == torch.bfloat16 and ops.tc_stream_fused_ok(pending.x, pending.weight, resid):
+                return ops.tc_stream_gemm_residual(pending.x, pending.weight, resid, self.weight, self.eps)
             pending = pending.materialize()
         return ops.add_rmsnorm(resid, pending, self.weight, self.eps, self.env.dtype, rows)
 

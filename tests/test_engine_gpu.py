@@ -300,10 +300,11 @@ def test_generate_command(tmp_path):
 
 def test_generate_command_with_random_weights(tmp_path):
     """``--random-weights SEED``: the folder's config.json with weights drawn from the seed; the same seed gives
-    the same tokens, another seed other weights."""
+    the same tokens, another seed other weights (the configuration with an untied head: with a tied one and small
+    random weights every model just repeats its last token)."""
     def run(seed):
         proc = subprocess.run(
-            [sys.executable, os.path.join(ROOT, "bin", "railgun"), "generate", "--model", str(helpers.model_dir("A")),
+            [sys.executable, os.path.join(ROOT, "bin", "railgun"), "generate", "--model", str(helpers.model_dir("B")),
              "--prompt-ids", "5,6,7", "--max-tokens", "8", "--dtype", "f32", "--num-gpu-blocks", "32",
              "--random-weights", str(seed)], capture_output=True, text=True, timeout=600)
         assert proc.returncode == 0, proc.stderr[-2000:]

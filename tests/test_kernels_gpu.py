@@ -675,6 +675,141 @@ def test_tc_gemm(M, N, K, tile):
     assert torch.equal(ops.tc_gemm(pitch[:, :K], w, out_dtype=torch.float32, tile=tile, check=True), out32)
 
 
+@pytest.mark.parametrize("splits", [0, 1, 2, 4, 8])
+@pytest.mark.parametrize("M,N,K", [(64, 256, 512), (17, 300, 520), (33, 3072, 2048), (1, 48, 512), (50, 2048, 8192),
+                                   (64, 1000, 8 * 67)])
+def test_tc_stream_gemm(M, N, K, splits):
+    """The swapped-operand streaming product: every split count against the 64-bit product, rows independent of
+    the batch, a longer row pitch."""
+    from railgun_b200 import ops
+    g = torch.Generator().manual_seed(M + N + K)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(N, K, generator=g) / K ** 0.5).to(torch.bfloat16).to(DEV)
+    ref = x.double() @ w.double().T
+    out = ops.tc_stream_gemm(x, w, splits=splits, check=True)
+    assert out.dtype == torch.bfloat16 and rel_err(out, ref) < 1e-2
+    out32 = ops.tc_stream_gemm(x, w, out_dtype=torch.float32, splits=splits, check=True)
+    assert rel_err(out32, ref) < 2e-5                        # exact products, 32-bit accumulation
+    # a row's result does not depend on what else is in the batch
+    alone = ops.tc_stream_gemm(x[M // 2:M // 2 + 1].contiguous(), w, out_dtype=torch.float32, splits=splits, check=True)
+    assert torch.equal(alone[0], out32[M // 2])
+    pitch = torch.zeros(M, K + 24, dtype=torch.bfloat16, device=DEV)
+    pitch[:, :K] = x
+    assert torch.equal(ops.tc_stream_gemm(pitch[:, :K], w, out_dtype=torch.float32, splits=splits, check=True), out32)
+
+
+@pytest.mark.parametrize("splits", [0, 1, 4])
+@pytest.mark.parametrize("M,I,K", [(40, 504, 136 * 4), (64, 8192, 2048)])
+def test_tc_stream_gemm_silu_mul(M, I, K, splits):
+    from railgun_b200 import ops
+    g = torch.Generator().manual_seed(M + I + K)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+    gate = (torch.randn(I, K, generator=g) / K ** 0.5).to(torch.bfloat16).to(DEV)
+    up = (torch.randn(I, K, generator=g) / K ** 0.5).to(torch.bfloat16).to(DEV)
+    gd, ud = x.double() @ gate.double().T, x.double() @ up.double().T
+    ref = gd / (1 + torch.exp(-gd)) * ud
+    out = ops.tc_stream_gemm(x, ops.interleave_gate_up(gate, up), silu_mul=True, splits=splits, check=True)
+    assert out.shape == (M, I) and rel_err(out, ref) < 1e-2
+
+
+@pytest.mark.parametrize("splits", [0, 1, 4])
+@pytest.mark.parametrize("M", [17, 40, 64])
+@pytest.mark.parametrize("H,K", [(200, 136), (2048, 2048), (2048, 8192), (3080, 520)])
+def test_tc_stream_gemm_residual_then_scaled(M, H, K, splits):
+    """The streaming product for 17 to 64 rows adds to the residual in its own kernel and prepares the next
+    RMSNorm; the product after it finishes the norm: against 64-bit references."""
+    from railgun_b200 import ops
+    g = torch.Generator().manual_seed(M * 7 + H + K)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(H, K, generator=g) / K ** 0.5).to(torch.bfloat16).to(DEV)
+    resid0 = (torch.randn(M, H, generator=g) * 3).to(DEV)
+    nw = (torch.rand(H, generator=g) + 0.5).to(DEV)
+    eps = 1e-3
+    resid = resid0.clone()
+    if -(-K // 64) < splits:
+        splits = 0                                                             # too few 64-wide boxes of K to split so far
+    rows = ops.tc_stream_gemm_residual(x, w, resid, nw, eps, splits=splits)
+    ops.tc_gemm_check()
+    ref_resid = resid0.double() + x.double() @ w.double().T
+    assert rel_err(resid, ref_resid) < 2e-5        # 32-bit accumulation over all of K in the tensor core (as test_tc_gemm)
+    assert torch.equal(rows.scaled, (resid * nw).to(torch.bfloat16))           # one rounding, of the 32-bit product
+    ss = rows.partials[:rows.blocks, :M].double().sum(0)
+    assert rows.blocks == -(-H // 128) and rel_err(ss, (resid.double() ** 2).sum(1)) < 1e-6
+    # a row's result does not depend on the batch around it
+    alone = resid0[M - 1:].clone()
+    ops.tc_stream_gemm_residual(x[M - 1:].contiguous(), w, alone, nw, eps, splits=splits)
+    assert torch.equal(alone[0], resid[M - 1])
+    # the consumers
+    normed = ref_resid * torch.rsqrt((ref_resid ** 2).mean(1, keepdim=True) + eps) * nw.double()
+    for N2, silu in ((136, False), (1008, True), (3072, False)):
+        w2 = (torch.randn(N2, H, generator=g) / H ** 0.5).to(torch.bfloat16).to(DEV)
+        y = ops.tc_stream_gemm(rows, w2, silu_mul=silu, splits=splits if -(-H // 64) >= max(splits, 1) else 0, check=True)
+        z = normed @ w2.double().T
+        if silu:
+            z = z.view(M, N2 // 16, 2, 8)
+            z = (z[:, :, 0] / (1 + torch.exp(-z[:, :, 0])) * z[:, :, 1]).reshape(M, N2 // 2)
+        assert y.dtype == torch.bfloat16 and rel_err(y, z) < 1e-2
+        if not silu and ops.tc_stream_scaled_ok(rows, w2):
+            assert rel_err(ops.linear(rows, w2), z) < 1e-2                     # linear() takes the unfinished norm
+    assert rel_err(rows.materialize(), normed) < 1e-2
+
+
+@pytest.mark.parametrize("M", [17, 40, 64])
+@pytest.mark.parametrize("nh,nkv,d,K,page", [(4, 2, 64, 256, 16), (32, 8, 64, 2048, 16), (6, 3, 48, 136, 8), (40, 8, 128, 1024, 32)])
+def test_tc_stream_projection_with_rotation_and_cache_write(M, nh, nkv, d, K, page):
+    """The q|k|v projection of 17 to 64 single tokens, rotated and written to the cache in the streaming product's
+    epilogue, against the product followed by the rope kernel; from plain rows and from rows whose norm the
+    product finishes."""
+    from railgun_b200 import ops
+    from railgun_b200.parts.rope import rope_table
+    g = torch.Generator().manual_seed(M + nh + d + K)
+    N, NP, max_pos = (nh + 2 * nkv) * d, 9, 300
+    table = rope_table(d, 500000.0, None, max_pos).to(DEV)
+    w = (torch.randn(N, K, generator=g) / K ** 0.5).to(torch.bfloat16).to(DEV)
+    positions = torch.randint(0, max_pos, (M,), generator=g, dtype=torch.int32).to(DEV)
+    slots = torch.randperm(NP * page, generator=g)[:M].to(torch.int32)
+    slots[1] = -1                                               # a token whose keys are not stored
+    slots = slots.to(DEV)
+
+    def check(x):
+        kv_f = torch.zeros(NP, 2, nkv, page, d, dtype=torch.bfloat16, device=DEV)
+        kv_u = torch.zeros_like(kv_f)
+        fused = ops.tc_stream_gemm_rope_cache(x, w, table, positions, slots, kv_f, nh, nkv, d)
+        ops.tc_gemm_check()
+        plain = ops.tc_stream_gemm(x, w, check=True)            # the same product, then the rope kernel
+        ops.rope_cache_write(plain, table, positions, slots, kv_u, nh, nkv, d, page, paired8=True)
+        # the unfused route rounds the projection to bfloat16 before it rotates: equal within that rounding
+        assert rel_err(fused[:, :nh * d], plain[:, :nh * d].double()) < 1e-2
+        assert rel_err(kv_f, kv_u.double()) < 1e-2
+        assert torch.equal(kv_f != 0, kv_u != 0)                # the same places written, nothing else
+
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+    check(x)
+    wp = (torch.randn(K, 64, generator=g) / 8).to(torch.bfloat16).to(DEV)
+    resid = torch.randn(M, K, generator=g).to(DEV)
+    rows = ops.tc_stream_gemm_residual(torch.randn(M, 64, generator=g).to(torch.bfloat16).to(DEV), wp, resid,
+                                       (torch.rand(K, generator=g) + 0.5).to(DEV), 1e-5)
+    check(rows)
+    kv = torch.zeros(NP, 2, nkv, page, d, dtype=torch.bfloat16, device=DEV)
+    ops.tc_stream_gemm_rope_cache(x, w, table, positions, None, kv, nh, nkv, d)
+    assert not kv.any()
+    assert not ops.tc_stream_rope_ok(x, w, 24)
+
+
+def test_tc_stream_gemm_refusals():
+    from railgun_b200 import ops
+    x = torch.zeros(65, 64, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(32, 64, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(ops.KernelError):
+        ops.tc_stream_gemm(x, w)                              # more than 64 rows
+    with pytest.raises(ops.KernelError):
+        ops.tc_stream_gemm(x[:8], w, splits=3)                # not a power of two
+    with pytest.raises(ops.KernelError):
+        ops.tc_stream_gemm(x[:8], w, splits=2)                # K of one box cannot be split in two
+    with pytest.raises(ops.KernelError):
+        ops.tc_stream_gemm(x[:8].float(), w)
+
+
 @pytest.mark.parametrize("tile", ["128x256", "256x128", "256x256"])
 @pytest.mark.parametrize("M,I,K", [(100, 504, 136), (1100, 8192, 2048)])
 def test_tc_gemm_silu_mul(M, I, K, tile):
