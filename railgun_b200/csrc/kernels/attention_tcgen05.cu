@@ -8,7 +8,7 @@
 //                        core reads
 //   O += P V             tcgen05.mma, M 128 x N 64 x K 64 (keys), V read as it lies in the cache ([key][dim],
 //                        an MN-major operand), accumulated in TMEM over the key tiles
-// The three are a software pipeline: S has two buffers in TMEM and P two in shared memory, so while the threads
+// The three are a software pipeline: S and P (bfloat16, two keys per cell) have two buffers each in TMEM, so while the threads
 // work on tile j the tensor core computes S(j+1) and O += P(j-1) V(j-1); K and V tiles come through rings of
 // three, fetched by TMA (one box per page, or 64 rows of a larger page, 128-byte swizzle) through the request's
 // block table two tiles ahead.  Two such CTAs fit an SM.
@@ -27,7 +27,10 @@
 #define FA_BM 128
 #define FA_BN 64
 #define FA_D 64
+#ifndef FA_KV_STAGES
 #define FA_KV_STAGES 3
+#endif
+#define FA_S_BUFFERS 2
 #define FA_THREADS 192            // warps 0-3: softmax / output rows; warp 4: TMA producer; warp 5: MMA issue, TMEM owner
 
 // Two 32-bit operations in one instruction (packed f32x2 arithmetic): the same roundings as two scalar
@@ -48,6 +51,22 @@ __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
     asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
     return r;
 }
+// The same three with their order fixed against one another and against the stores (volatile).
+__device__ __forceinline__ float ex2_in_order(float x) {
+    float y;
+    asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint64_t add2_in_order(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm volatile("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ uint32_t bf16x2_in_order(float lo, float hi) {      // lo in the low half
+    uint32_t r;
+    asm volatile("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
 __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
@@ -62,13 +81,15 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ 
              const int* __restrict__ tiles, const int* __restrict__ positions, int nh, int nkv, int page_size,
              int window, float scale_log2, int* err) {
     extern __shared__ unsigned char smem_raw[];
-    constexpr uint32_t Q_BYTES = FA_BM * 128, KV_BYTES = FA_BN * 128, P_BYTES = FA_BM * 128;   // rows of 64 bfloat16
+    constexpr uint32_t Q_BYTES = FA_BM * 128, KV_BYTES = FA_BN * 128;                          // rows of 64 bfloat16
     const uint32_t base = (smem_addr(smem_raw) + 1023u) & ~1023u;            // swizzled tiles need 1024-byte alignment
-    const uint32_t sQ = base, sK0 = sQ + Q_BYTES, sV0 = sK0 + FA_KV_STAGES * KV_BYTES, sP0 = sV0 + FA_KV_STAGES * KV_BYTES;
-    const uint32_t bars = sP0 + 2 * P_BYTES;
-    // q_full | k_full[3] k_empty[3] v_full[3] v_empty[3] | s_full[2] p_full[2] p_free[2]
-    const uint32_t q_full = bars, k_full0 = bars + 8, k_empty0 = bars + 32, v_full0 = bars + 56, v_empty0 = bars + 80,
-                   s_full0 = bars + 104, p_full0 = bars + 120, p_free0 = bars + 136;
+    const uint32_t sQ = base, sK0 = sQ + Q_BYTES, sV0 = sK0 + FA_KV_STAGES * KV_BYTES;
+    const uint32_t bars = sV0 + FA_KV_STAGES * KV_BYTES;
+    // q_full | k_full[] k_empty[] v_full[] v_empty[] (one per stage) | s_full[2] p_full[2] p_free[2]
+    const uint32_t q_full = bars, k_full0 = bars + 8, k_empty0 = k_full0 + 8 * FA_KV_STAGES, v_full0 = k_empty0 + 8 * FA_KV_STAGES,
+                   v_empty0 = v_full0 + 8 * FA_KV_STAGES, s_full0 = v_empty0 + 8 * FA_KV_STAGES,
+                   p_full0 = s_full0 + 8 * FA_S_BUFFERS, p_free0 = p_full0 + 16;
+    static_assert(8 + 32 * FA_KV_STAGES + 8 * FA_S_BUFFERS + 32 <= 256, "the barriers have 256 bytes");
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
 
@@ -87,14 +108,17 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ 
             mbar_init(k_full0 + 8 * s, 1); mbar_init(k_empty0 + 8 * s, 1);
             mbar_init(v_full0 + 8 * s, 1); mbar_init(v_empty0 + 8 * s, 1);
         }
-        for (int b = 0; b < 2; ++b) { mbar_init(s_full0 + 8 * b, 1); mbar_init(p_full0 + 8 * b, 4); mbar_init(p_free0 + 8 * b, 1); }
+        for (int b = 0; b < FA_S_BUFFERS; ++b) mbar_init(s_full0 + 8 * b, 1);
+        for (int b = 0; b < 2; ++b) { mbar_init(p_full0 + 8 * b, 4); mbar_init(p_free0 + 8 * b, 1); }
         fence_barrier_init();
     }
-    if (warp == 5) tmem_alloc(&tmem_base_slot, 256u);                        // S: columns [0,64) and [64,128), O: [128,192)
+    // S: columns [0,64) and [64,128); O: [128,192); P (bfloat16, two keys per cell): [192,224) and [224,256)
+    if (warp == 5) tmem_alloc(&tmem_base_slot, 256u);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem_s0 = tmem_base_slot, tmem_o = tmem_base_slot + 128u;
+    const uint32_t tmem_s0 = tmem_base_slot, tmem_o = tmem_base_slot + (uint32_t)(FA_S_BUFFERS * FA_BN);
+    const uint32_t tmem_p0 = tmem_o + (uint32_t)FA_D;
     pdl_wait();
     pdl_trigger();
 
@@ -143,21 +167,26 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ 
                 tma_load_2d(sV0 + s * KV_BYTES + lane * box_bytes, &kv_map, v_full0 + 8 * s, 0,
                             ((page * 2 + 1) * nkv + kvh) * page_size + in_page);
         }
-    } else if (warp == 5 && lane == 0) {
-        // ---- MMA issue
+    } else if (warp == 5) {
+        // ---- MMA issue.  The whole warp walks the loop and waits (so that tile indices, descriptors and
+        // addresses are uniform values of the warp); one elected lane issues.
         // S: D F32, A/B BF16 K-major, N 64, M 128.  PV: the same with B MN-major (bit 16).
         constexpr uint32_t idesc_s = make_idesc(FA_BM, FA_BN, false);
         constexpr uint32_t idesc_o = make_idesc(FA_BM, FA_D, true);
+        const bool issuer = elect_one();
         auto issue_s = [&](int j) -> bool {                                   // S(j) = Q K(j)^T into buffer j & 1
-            const int s = j % FA_KV_STAGES, u = j / FA_KV_STAGES;
+            const int s = j % FA_KV_STAGES, u = j / FA_KV_STAGES, sb = j % FA_S_BUFFERS;
             if (!mbar_wait(k_full0 + 8 * s, u & 1, err, 22, &abort_flag)) return false;
             tc_fence_after();
-            const uint64_t qd = desc_k_major(sQ), kd = desc_k_major(sK0 + s * KV_BYTES);
+            if (issuer) {
+                const uint64_t qd = desc_k_major(sQ), kd = desc_k_major(sK0 + s * KV_BYTES);
 #pragma unroll
-            for (int k = 0; k < FA_D / 16; ++k)
-                tc_mma(tmem_s0 + (uint32_t)((j & 1) * FA_BN), qd + 2u * k, kd + 2u * k, idesc_s, k > 0 ? 1u : 0u);
-            tc_commit(s_full0 + 8 * (j & 1));
-            tc_commit(k_empty0 + 8 * s);
+                for (int k = 0; k < FA_D / 16; ++k)
+                    tc_mma(tmem_s0 + (uint32_t)(sb * FA_BN), qd + 2u * k, kd + 2u * k, idesc_s, k > 0 ? 1u : 0u);
+                tc_commit(s_full0 + 8 * sb);
+                tc_commit(k_empty0 + 8 * s);
+            }
+            __syncwarp();
             return true;
         };
         bool ok = mbar_wait(q_full, 0, err, 21, &abort_flag);
@@ -170,15 +199,19 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ 
             if (ok) ok = mbar_wait(p_full0 + 8 * b, (j >> 1) & 1, err, 23, &abort_flag);
             if (!ok) break;
             tc_fence_after();
+            if (issuer) {
 #pragma unroll
-            for (int k = 0; k < FA_BN / 16; ++k) {
-                const uint64_t pd = desc_k_major(sP0 + (uint32_t)b * P_BYTES) + 2u * k;     // 16 keys = 32 bytes along a row
-                const uint64_t vd = desc_mn_major(sV0 + s * KV_BYTES + (uint32_t)k * 2048u, KV_BYTES);  // 16 keys = 16 rows
-                tc_mma(tmem_o, pd, vd, idesc_o, (j > 0 || k > 0) ? 1u : 0u);
+                for (int k = 0; k < FA_BN / 16; ++k) {
+                    const uint64_t vd = desc_mn_major(sV0 + s * KV_BYTES + (uint32_t)k * 2048u, KV_BYTES);  // 16 keys = 16 rows
+                    tc_mma_a_tmem(tmem_o, tmem_p0 + (uint32_t)(b * (FA_BN / 2) + k * 8), vd, idesc_o,    // 16 keys = 8 cells
+                                  (j > 0 || k > 0) ? 1u : 0u);
+                }
+                tc_commit(p_free0 + 8 * b);                                   // P(j) consumed, O complete through tile j
+                tc_commit(v_empty0 + 8 * s);
             }
-            tc_commit(p_free0 + 8 * b);                                       // P(j) consumed, O complete through tile j
-            tc_commit(v_empty0 + 8 * s);
-            // S(j+2) into the buffer the threads have just finished with
+            __syncwarp();
+            // S(j+2) into the buffer the threads have just finished with.  It is issued after O += P(j) V(j), so
+            // its completion (s_full) also tells the threads that P's buffer j & 1 has been read.
             if (j + 2 < n_kt) ok = issue_s(j + 2);
         }
     } else if (warp < 4) {
@@ -189,11 +222,11 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ 
         float m_ref = -INFINITY, l_run = 0.f;                                 // reference maximum (log2 domain), row sum
         bool ok = true;
         for (int j = 0; j < n_kt && ok; ++j) {
-            const int b = j & 1;
+            const int b = j & 1, sb = j % FA_S_BUFFERS;
             const int key_base = (kt0 + j) * FA_BN;
-            const uint32_t tmem_s = tmem_s0 + (uint32_t)(b * FA_BN) + lane_off;
-            const uint32_t sP = sP0 + (uint32_t)b * P_BYTES + (uint32_t)row * 128u;
-            ok = mbar_wait_warp(s_full0 + 8 * b, (j >> 1) & 1, err, 31, &abort_flag);
+            const uint32_t tmem_s = tmem_s0 + (uint32_t)(sb * FA_BN) + lane_off;
+            const uint32_t tmem_p = tmem_p0 + (uint32_t)(b * (FA_BN / 2)) + lane_off;
+            ok = mbar_wait(s_full0 + 8 * sb, (j / FA_S_BUFFERS) & 1, err, 31, &abort_flag);     // every lane polls: no exchange
             if (!ok) break;
             tc_fence_after();
             // Interior tiles (every key attended by every row of the CTA) take the short path; the tile on the
@@ -201,7 +234,7 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ 
             const bool edge = key_base + FA_BN - 1 > p0 || (window > 0 && key_base < p0 + FA_BM - window);
             const int k_hi = prow - key_base;                                 // columns <= k_hi are not in the future
             const int k_lo = window > 0 ? prow - window + 1 - key_base : -1;  // columns >= k_lo are inside the window
-            bool p_writable = j < 2;                                          // has O += P(j-2) V(j-2) read this P buffer?
+            // P's buffer j & 1 is free: S(j) was issued after O += P(j-2) V(j-2), and the tensor core completes in order
 
             // One pass over the row: p = 2^(s scale - reference) -> P in shared memory (bfloat16, 16-byte pieces
             // XOR-swizzled by row), the row sum, and the largest p as packed bfloat16.  EDGE is a compile-time
@@ -214,38 +247,42 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ 
                 tc_ld32_nowait(tmem_s, v[0]);
                 tc_ld32_nowait(tmem_s + 32u, v[1]);
                 tc_ld_wait();
+                // Four groups of 16 columns.  The exponentials of a group are issued back to back, and their
+                // consumers (row sum, conversion, the store of P) only after the next group's exponentials: a
+                // thread waits for no exponential it has just issued.  The order is pinned with volatile asm.
+                float p[2][16];
+                auto exps = [&](int g) {
 #pragma unroll
-                for (int c = 0; c < FA_BN / 32; ++c) {
-                    uint32_t pk[16];
-#pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        float s0 = __uint_as_float(v[c][i]), s1 = __uint_as_float(v[c][i + 1]);
+                    for (int i = 0; i < 16; i += 2) {
+                        const int col = g * 16 + i;
+                        float s0 = __uint_as_float(v[col >> 5][col & 31]), s1 = __uint_as_float(v[col >> 5][(col & 31) + 1]);
                         if (EDGE) {
-                            const int col = c * 32 + i;
                             if (col > k_hi || col < k_lo) s0 = -INFINITY;
                             if (col + 1 > k_hi || col + 1 < k_lo) s1 = -INFINITY;
                         }
                         float t0, t1;
                         unpack2(fma2(pack2(s0, s1), scale2, nms2), t0, t1);
-                        const float p0v = ex2(t0), p1v = ex2(t1);
-                        rs2[(i >> 1) & 3] = add2(rs2[(i >> 1) & 3], pack2(p0v, p1v));
-                        const __nv_bfloat162 hh = __floats2bfloat162_rn(p0v, p1v);
-                        pk[i >> 1] = *reinterpret_cast<const uint32_t*>(&hh);
+                        p[g & 1][i] = ex2_in_order(t0);
+                        p[g & 1][i + 1] = ex2_in_order(t1);
                     }
-                    if (!p_writable) {
-                        // two tiles back; completed long ago as a rule
-                        ok = mbar_wait_warp(p_free0 + 8 * b, ((j - 2) >> 1) & 1, err, 32, &abort_flag);
-                        p_writable = true;
-                    }
-                    // columns c*32 .. c*32+31 of this row: pieces c * 4 .. + 3
+                };
+                auto consume = [&](int g) {
+                    uint32_t pk[8];
 #pragma unroll
-                    for (int q4 = 0; q4 < 4; ++q4) {
-                        const uint32_t piece = (uint32_t)(c * 4 + q4) ^ (uint32_t)(row & 7);
-                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(sP + piece * 16u),
-                                     "r"(pk[q4 * 4]), "r"(pk[q4 * 4 + 1]), "r"(pk[q4 * 4 + 2]), "r"(pk[q4 * 4 + 3])
-                                     : "memory");
+                    for (int i = 0; i < 16; i += 2) {
+                        rs2[(i >> 1) & 3] = add2_in_order(rs2[(i >> 1) & 3], pack2(p[g & 1][i], p[g & 1][i + 1]));
+                        pk[i >> 1] = bf16x2_in_order(p[g & 1][i], p[g & 1][i + 1]);
                     }
-                }
+                    tc_st8(tmem_p + (uint32_t)(g * 8), pk);                  // keys g*16 .. g*16+15 of this row
+                };
+                exps(0);
+                exps(1);
+                consume(0);
+                exps(2);
+                consume(1);
+                exps(3);
+                consume(2);
+                consume(3);
                 float lo, hi;
                 unpack2(add2(add2(rs2[0], rs2[1]), add2(rs2[2], rs2[3])), lo, hi);
                 return lo + hi;
@@ -302,8 +339,8 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ 
             }
             if (!ok) break;
             l_run += row_sum;
+            tc_st_wait();                                                     // P is in tensor memory
             tc_fence_before();
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // P must be visible to the tensor core
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full0 + 8 * b);                      // S(j) has been read, P(j) is written
         }
@@ -345,7 +382,7 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ 
     }
 }
 
-static const size_t FA_SMEM_BYTES = (size_t)FA_BM * 128 + 2 * FA_KV_STAGES * FA_BN * 128 + 2 * FA_BM * 128 + 256 + 1024;
+static const size_t FA_SMEM_BYTES = (size_t)FA_BM * 128 + 2 * FA_KV_STAGES * FA_BN * 128 + 256 + 1024;
 
 // q: the fused qkv buffer [n_rows_total, q_stride] (head h of q at column h * 64); out [n_rows_total, nh * 64];
 // kv_cache [num_pages, 2, nkv, page_size, 64]; tiles [n_tiles][3] with at most 128 rows each.
