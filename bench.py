@@ -476,6 +476,9 @@ def run_kernels(args):
                     res[tile] = f"{us:.1f} us, {fl / us / 1e6:.0f} TFLOP/s"
                 us_lib = timed(lambda: [ops.silu_mul(torch.mm(inp, w.t()), interleaved=True) if silu else torch.mm(inp, w.t()) for w in ws])
                 out(f"prefill product {name} M{M} ({n} x {k})", us_lib, cublas_TFLOPs=round(fl / us_lib / 1e6), **res)
+    if on("primitives"):
+        # cycles of the building blocks of the tcgen05 kernels (per warp instruction and scheduler, per MMA, per wait)
+        print(json.dumps({"case": "sm_100a primitives, cycles", **ops.probe_sm100(dev)}), flush=True)
     if on("prefill_attention"):
         for T in (2048, 8192):
             blocks = -(-T // page)
@@ -504,7 +507,7 @@ def main():
                     help="all: the contract's line; decode / prefill: one short measurement (for profiling); "
                          "kernels: the hot kernels one by one")
     ap.add_argument("--cases", default="", help="--mode kernels: comma-separated subset of sampling, decode_gemm, "
-                    "decode_gemm_mid, decode_attention, prefill_gemm, prefill_attention")
+                    "decode_gemm_mid, decode_attention, prefill_gemm, prefill_attention, primitives")
     ap.add_argument("--batch", type=int, default=8, help="--mode decode: requests in the batch")
     ap.add_argument("--tokens", type=int, default=PREFILL_TOKENS, help="--mode prefill: prompt length")
     ap.add_argument("--context", type=int, default=CONTEXT, help="--mode decode: tokens each request holds")

@@ -746,6 +746,27 @@ def prefill_attention_tc(q, out, kv_cache, block_table, tiles, positions, nh: in
         _stream()), "prefill_attention_tc")
 
 
+def probe_sm100(device="cuda:0") -> dict:
+    """Cycle counts of the building blocks of the tcgen05 kernels on this GPU
+    (csrc/kernels/probe_sm100.cu): a diagnostic, on no product path."""
+    from ctypes import c_double
+    names = ["ex2.approx.ftz.f32", "cvt.rn.bf16x2.f32", "fma.rn.f32x2", "fma.rn.f32", "max.f32",
+             "tcgen05.mma M128 N64 K16", "tcgen05.mma M128 N128 K16", "tcgen05.mma M128 N256 K16",
+             "four N64 MMAs + two commits", "mbarrier wait (done), every lane", "mbarrier wait (done), lane 0 + shuffle",
+             "fence.proxy.async", "mbarrier.arrive", "tcgen05.st x8 + wait::st",
+             "softmax pass of 64 columns, 2 warps per scheduler", "softmax pass of 64 columns, 1 warp per scheduler"]
+    dev = torch.device(device)
+    scratch = torch.randn(148 * 512 * 64, device=dev)
+    cyc = torch.zeros(16, dtype=torch.int64, device=dev)
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    out = (c_double * len(names))()
+    with torch.cuda.device(dev):
+        _ok(_fn("probe_sm100", "rg_probe_sm100")(out, _ptr(scratch), _ptr(cyc), _ptr(err), _stream()), "probe_sm100")
+    if int(err.item()) != 0 or any(v < 0 for v in out):
+        raise KernelError(f"probe_sm100: a bounded wait gave up (code {int(err.item())})")
+    return {n: round(float(v), 1) for n, v in zip(names, out)}
+
+
 def tc_gemm_check(device=None) -> None:
     """Raise if a wait inside a tcgen05 product gave up since the last check
     (synchronises; free when no such product ran since)."""

@@ -931,3 +931,17 @@ def test_prefill_attention_tcgen05_refuses_other_shapes():
                                  torch.zeros(1, 1, dtype=torch.int32, device=DEV),
                                  torch.tensor([[0, 4, 0]], dtype=torch.int32, device=DEV),
                                  torch.zeros(4, dtype=torch.int32, device=DEV), 1, 1, 64, 0, 1.0)
+
+
+@pytest.mark.gpu
+def test_probe_sm100_reports_cycles_in_range():
+    """The diagnostic that times the tcgen05 kernels' building blocks runs and gives figures of the right order:
+    an exponential takes 8 cycles of a scheduler's special-function unit, a tcgen05.mma of N 256 four times one of
+    N 64 at most, and a wait on a completed barrier costs more with one polling lane and a shuffle."""
+    from railgun_b200 import ops
+    r = ops.probe_sm100(DEV)
+    assert 6.0 < r["ex2.approx.ftz.f32"] < 12.0
+    assert 0.5 < r["fma.rn.f32"] < 2.5
+    assert 20 < r["tcgen05.mma M128 N64 K16"] <= r["tcgen05.mma M128 N128 K16"] <= r["tcgen05.mma M128 N256 K16"] < 400
+    assert r["mbarrier wait (done), every lane"] < r["mbarrier wait (done), lane 0 + shuffle"]
+    assert r["softmax pass of 64 columns, 1 warp per scheduler"] < r["softmax pass of 64 columns, 2 warps per scheduler"]
