@@ -109,7 +109,7 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ 
             mbar_init(v_full0 + 8 * s, 1); mbar_init(v_empty0 + 8 * s, 1);
         }
         for (int b = 0; b < FA_S_BUFFERS; ++b) mbar_init(s_full0 + 8 * b, 1);
-        for (int b = 0; b < 2; ++b) { mbar_init(p_full0 + 8 * b, 4); mbar_init(p_free0 + 8 * b, 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(p_full0 + 8 * b, FA_BM); mbar_init(p_free0 + 8 * b, 1); }   // p_full: every softmax thread
         fence_barrier_init();
     }
     // S: columns [0,64) and [64,128); O: [128,192); P (bfloat16, two keys per cell): [192,224) and [224,256)
@@ -148,21 +148,18 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ 
             const int page = page_next;
             const int in_page = ((kt0 + j) * FA_BN + lane * rows_per_box) % page_size;
             if (j + 1 < n_kt) page_next = page_of(kt0 + j + 1);
-            if (lane == 0) {
-                if (u > 0) ok = mbar_wait(k_empty0 + 8 * s, (u & 1) ^ 1, err, 11, &abort_flag);
-                if (ok) mbar_expect_tx(k_full0 + 8 * s, KV_BYTES);
-            }
-            ok = __shfl_sync(0xffffffffu, ok, 0);
+            // every lane polls (a wait by one lane and a shuffle costs four times as much when the phase is done)
+            if (u > 0) ok = mbar_wait_all(k_empty0 + 8 * s, (u & 1) ^ 1, err, 11, &abort_flag);
             if (!ok) break;
+            if (lane == 0) mbar_expect_tx(k_full0 + 8 * s, KV_BYTES);
+            __syncwarp();
             if (lane < boxes)
                 tma_load_2d(sK0 + s * KV_BYTES + lane * box_bytes, &kv_map, k_full0 + 8 * s, 0,
                             ((page * 2 + 0) * nkv + kvh) * page_size + in_page);
-            if (lane == 0) {
-                if (u > 0) ok = mbar_wait(v_empty0 + 8 * s, (u & 1) ^ 1, err, 12, &abort_flag);
-                if (ok) mbar_expect_tx(v_full0 + 8 * s, KV_BYTES);
-            }
-            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (u > 0) ok = mbar_wait_all(v_empty0 + 8 * s, (u & 1) ^ 1, err, 12, &abort_flag);
             if (!ok) break;
+            if (lane == 0) mbar_expect_tx(v_full0 + 8 * s, KV_BYTES);
+            __syncwarp();
             if (lane < boxes)
                 tma_load_2d(sV0 + s * KV_BYTES + lane * box_bytes, &kv_map, v_full0 + 8 * s, 0,
                             ((page * 2 + 1) * nkv + kvh) * page_size + in_page);
@@ -174,10 +171,11 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ 
         constexpr uint32_t idesc_s = make_idesc(FA_BM, FA_BN, false);
         constexpr uint32_t idesc_o = make_idesc(FA_BM, FA_D, true);
         const bool issuer = elect_one();
-        auto issue_s = [&](int j) -> bool {                                   // S(j) = Q K(j)^T into buffer j & 1
-            const int s = j % FA_KV_STAGES, u = j / FA_KV_STAGES, sb = j % FA_S_BUFFERS;
-            if (!mbar_wait(k_full0 + 8 * s, u & 1, err, 22, &abort_flag)) return false;
-            tc_fence_after();
+        auto wait_k = [&](int j) -> bool {
+            return mbar_wait_all(k_full0 + 8 * (j % FA_KV_STAGES), (j / FA_KV_STAGES) & 1, err, 22, &abort_flag);
+        };
+        auto issue_s = [&](int j) {                                           // S(j) = Q K(j)^T into buffer j & 1; K(j) is there
+            const int s = j % FA_KV_STAGES, sb = j % FA_S_BUFFERS;
             if (issuer) {
                 const uint64_t qd = desc_k_major(sQ), kd = desc_k_major(sK0 + s * KV_BYTES);
 #pragma unroll
@@ -187,16 +185,19 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ 
                 tc_commit(k_empty0 + 8 * s);
             }
             __syncwarp();
-            return true;
         };
-        bool ok = mbar_wait(q_full, 0, err, 21, &abort_flag);
-        if (ok) ok = issue_s(0);
-        if (ok && n_kt > 1) ok = issue_s(1);
+        bool ok = mbar_wait_all(q_full, 0, err, 21, &abort_flag);
+        if (ok) ok = wait_k(0);
+        if (ok) { tc_fence_after(); issue_s(0); }
+        if (ok && n_kt > 1) ok = wait_k(1);
+        if (ok && n_kt > 1) { tc_fence_after(); issue_s(1); }
         for (int j = 0; j < n_kt && ok; ++j) {
-            // O += P(j) V(j): the threads have read S(j) and written P(j)
+            // O += P(j) V(j): the threads have read S(j) and written P(j).  What else the tensor core will need is
+            // waited for first, while the threads are in their pass.
             const int s = j % FA_KV_STAGES, u = j / FA_KV_STAGES, b = j & 1;
-            ok = mbar_wait(v_full0 + 8 * s, u & 1, err, 24, &abort_flag);
-            if (ok) ok = mbar_wait(p_full0 + 8 * b, (j >> 1) & 1, err, 23, &abort_flag);
+            ok = mbar_wait_all(v_full0 + 8 * s, u & 1, err, 24, &abort_flag);
+            if (ok && j + 2 < n_kt) ok = wait_k(j + 2);
+            if (ok) ok = mbar_wait_all(p_full0 + 8 * b, (j >> 1) & 1, err, 23, &abort_flag);
             if (!ok) break;
             tc_fence_after();
             if (issuer) {
@@ -212,7 +213,7 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ 
             __syncwarp();
             // S(j+2) into the buffer the threads have just finished with.  It is issued after O += P(j) V(j), so
             // its completion (s_full) also tells the threads that P's buffer j & 1 has been read.
-            if (j + 2 < n_kt) ok = issue_s(j + 2);
+            if (j + 2 < n_kt) issue_s(j + 2);
         }
     } else if (warp < 4) {
         // ---- softmax and output: thread = query row
@@ -226,7 +227,7 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ 
             const int key_base = (kt0 + j) * FA_BN;
             const uint32_t tmem_s = tmem_s0 + (uint32_t)(sb * FA_BN) + lane_off;
             const uint32_t tmem_p = tmem_p0 + (uint32_t)(b * (FA_BN / 2)) + lane_off;
-            ok = mbar_wait(s_full0 + 8 * sb, (j / FA_S_BUFFERS) & 1, err, 31, &abort_flag);     // every lane polls: no exchange
+            ok = mbar_wait_all(s_full0 + 8 * sb, (j / FA_S_BUFFERS) & 1, err, 31, &abort_flag);     // every lane polls: no exchange
             if (!ok) break;
             tc_fence_after();
             // Interior tiles (every key attended by every row of the CTA) take the short path; the tile on the
@@ -319,7 +320,7 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ 
                 if (j > 0) {
                     // rescale this warp's rows of O and the row sums: O must be complete through tile j - 1 (the
                     // product of tile j waits for this tile's P, so nothing else writes O meanwhile)
-                    ok = mbar_wait_warp(p_free0 + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1, err, 33, &abort_flag);
+                    ok = mbar_wait_all(p_free0 + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1, err, 33, &abort_flag);
                     if (!ok) break;
                     tc_fence_after();
                     const float alpha = ex2(m_ref - (m_new == -INFINITY ? 0.f : m_new));
@@ -341,10 +342,9 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ 
             l_run += row_sum;
             tc_st_wait();                                                     // P is in tensor memory
             tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(p_full0 + 8 * b);                      // S(j) has been read, P(j) is written
+            mbar_arrive(p_full0 + 8 * b);                                     // this row of S(j) has been read, of P(j) written
         }
-        if (ok) ok = mbar_wait_warp(p_free0 + 8 * ((n_kt - 1) & 1), ((n_kt - 1) >> 1) & 1, err, 34, &abort_flag);
+        if (ok) ok = mbar_wait_all(p_free0 + 8 * ((n_kt - 1) & 1), ((n_kt - 1) >> 1) & 1, err, 34, &abort_flag);
         if (ok) {
             tc_fence_after();
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;

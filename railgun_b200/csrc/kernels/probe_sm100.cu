@@ -113,7 +113,7 @@ __global__ void __launch_bounds__(128) probe_sync_kernel(long long* cyc, int* er
     bool ok = true;
     uint32_t v[32], w[8] = {1, 2, 3, 4, 5, 6, 7, 8};
     t[0] = clock64();
-    for (int i = 0; i < R; ++i) ok &= mbar_wait(bar, 0, err, 1, &abort_flag);
+    for (int i = 0; i < R; ++i) ok &= mbar_wait_all(bar, 0, err, 1, &abort_flag);
     t[1] = clock64();
     for (int i = 0; i < R; ++i) ok &= mbar_wait_warp(bar, 0, err, 1, &abort_flag);
     t[2] = clock64();
