@@ -447,7 +447,11 @@ def run_kernels(args):
             splits = ops.decode_splits(B, nkv, ctx)
             us = timed(lambda: [ops.decode_attention(q, QKV, o, kv, bt, None, B, req, pos, nh, nkv, d, 0, d ** -0.5, splits)
                                 for kv in kvs])
-            out(f"decode attention B{B} ctx{ctx} splits{splits}", us, GBs=round(B * ctx * nkv * d * 4 / us / 1e3, 1))
+            more = {}
+            if 2 <= splits <= 8:     # beside the engine's way (a second kernel adds the splits): the splits as a cluster
+                more["cluster_us"] = round(timed(lambda: [ops.decode_attention(
+                    q, QKV, o, kv, bt, None, B, req, pos, nh, nkv, d, 0, d ** -0.5, splits, cluster=True) for kv in kvs]), 2)
+            out(f"decode attention B{B} ctx{ctx} splits{splits}", us, GBs=round(B * ctx * nkv * d * 4 / us / 1e3, 1), **more)
     if on("sampling"):
         V = cfg["vocab_size"]
         for rows in (8, 64):

@@ -463,15 +463,18 @@ _decode_counters: dict = {}
 
 def decode_attention(q, q_stride: int, out, kv_cache, block_table, rows, n_tokens: int, req_of_token, positions,
                      nh: int, nkv: int, d: int, window: int, scale: float, num_splits: int,
-                     scratch=None, fused_reduce=None) -> None:
+                     scratch=None, fused_reduce=None, cluster: bool = False) -> None:
     """Split attention for single tokens: token rows ``rows`` (None: rows
     0..n_tokens-1) each attend their request's context.  Partial results go
     through scratch memory (allocated here unless given) and are reduced into
-    ``out`` [T, nh*d]: by the block that finishes last for each token and head
-    tile (``fused_reduce``, always in split order) or by a second kernel.
-    Default: fused when there is a single split (the kernel then writes the
-    result itself), a second kernel otherwise (measured faster: the last block
-    would reduce alone at the end of the launch)."""
+    ``out`` [T, nh*d] by the block that finishes last for each token and head
+    tile (``fused_reduce``) or by a second kernel (the default: measured
+    faster, the last block would reduce alone at the end of the launch); a
+    single split writes the result itself.  ``cluster`` (2 to 8 splits): the
+    splits of a (token, head tile) are one thread-block cluster and add their
+    partial results through distributed shared memory; the fastest way for the
+    kernel alone, not inside a decode step (see attention_mma.cu), so the
+    engine leaves it off.  Every way adds the splits in split order."""
     if fused_reduce is None:
         fused_reduce = num_splits == 1
     page_size = _check_paged(q, kv_cache, block_table, nkv, d)
@@ -480,6 +483,14 @@ def decode_attention(q, q_stride: int, out, kv_cache, block_table, rows, n_token
     _check(out, "out", q.dtype)
     if rows is not None:
         _check(rows, "rows", torch.int32)
+    if cluster:
+        if not 2 <= num_splits <= 8:
+            raise KernelError("decode_attention: a cluster takes 2 to 8 splits")
+        _ok(_fn("attention_mma", "rg_decode_attention_cluster")(
+            _ptr(q), c_int(q_stride), _ptr(out), _ptr(kv_cache), _ptr(block_table), c_int(block_table.shape[1]),
+            _ptr(rows), c_int(n_tokens), _ptr(req_of_token), _ptr(positions), c_int(nh), c_int(nkv), c_int(d),
+            c_int(page_size), c_int(window or 0), c_float(scale), c_int(num_splits), _stream()), "decode_attention")
+        return
     if scratch is None:
         part_o = torch.empty((n_tokens, nh, num_splits, d), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((n_tokens, nh, num_splits, 2), dtype=torch.float32, device=q.device)

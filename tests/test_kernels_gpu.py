@@ -479,6 +479,12 @@ def test_decode_attention_mma(case_id, splits):
     ops.decode_attention(q, nh * d, two, c["kv"].to(DEV), c["bt"].to(DEV), None, T, req, pos, nh, nkv, d, window,
                          scale, splits, fused_reduce=False)
     assert torch.equal(two, out)
+    # the splits as one cluster, added up through distributed shared memory: the same numbers again
+    if 2 <= splits <= 8:
+        clu = torch.full((T, nh * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+        ops.decode_attention(q, nh * d, clu, c["kv"].to(DEV), c["bt"].to(DEV), None, T, req, pos, nh, nkv, d, window,
+                             scale, splits, cluster=True)
+        assert torch.equal(clu, out)
     # and again: the counters were left at zero
     again = torch.full((T, nh * d), float("nan"), dtype=torch.bfloat16, device=DEV)
     ops.decode_attention(q, nh * d, again, c["kv"].to(DEV), c["bt"].to(DEV), None, T, req, pos, nh, nkv, d, window,
