@@ -401,8 +401,14 @@ extern "C" int rg_prefill_attention_tc(const void* q, int q_stride, int n_rows_t
     e = rg_make_map(&kvm, kv_cache, (unsigned long long)num_pages * 2ull * nkv * page_size, FA_D, FA_D,
                     page_size < FA_BN ? page_size : FA_BN);
     if (e) return e;
-    cudaError_t ce = cudaFuncSetAttribute(fa_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FA_SMEM_BYTES);
-    if (ce != cudaSuccess) return (int)ce;
+    static unsigned long long smem_allowed = 0;                              // one bit per device: set once, not per call
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev > 63) dev = 63;
+    if (dev == 63 || !(smem_allowed >> dev & 1ull)) {
+        cudaError_t ce = cudaFuncSetAttribute(fa_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FA_SMEM_BYTES);
+        if (ce != cudaSuccess) return (int)ce;
+        smem_allowed |= 1ull << dev;
+    }
     return rg_launch(fa_tc_kernel, dim3(n_tiles * nh), dim3(FA_THREADS), FA_SMEM_BYTES, (cudaStream_t)stream, 1, qm, kvm,
                      (bf16*)out, block_table, max_blocks, tiles, positions, nh, nkv, page_size, window,
                      scale * 1.4426950408889634f, err);
