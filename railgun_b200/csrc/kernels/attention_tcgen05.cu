@@ -4,14 +4,19 @@
 //   S = Q K^T            tcgen05.mma, M 128 (queries) x N 64 (keys) x K 64 (head), accumulator in TMEM
 //   softmax              128 threads, one per query row: the row is read from TMEM with tcgen05.ld, masked by
 //                        absolute position, p = 2^(s scale - reference) and the row sum run inside the thread
-//                        (no shuffles); P goes to shared memory as bfloat16 in the swizzled layout the tensor
-//                        core reads
-//   O += P V             tcgen05.mma, M 128 x N 64 x K 64 (keys), V read as it lies in the cache ([key][dim],
-//                        an MN-major operand), accumulated in TMEM over the key tiles
-// The three are a software pipeline: S and P (bfloat16, two keys per cell) have two buffers each in TMEM, so while the threads
-// work on tile j the tensor core computes S(j+1) and O += P(j-1) V(j-1); K and V tiles come through rings of
-// three, fetched by TMA (one box per page, or 64 rows of a larger page, 128-byte swizzle) through the request's
-// block table two tiles ahead.  Two such CTAs fit an SM.
+//                        (no shuffles); P goes back to TMEM as bfloat16, two keys per 32-bit cell (tcgen05.st)
+//   O += P V             tcgen05.mma, M 128 x N 64 x K 64 (keys), P read from TMEM as the A operand, V read as it
+//                        lies in the cache ([key][dim], an MN-major operand), accumulated in TMEM over the key tiles
+// The three are a software pipeline: S and P have two buffers each in TMEM, so while the threads work on tile j the
+// tensor core computes S(j+1) and O += P(j-1) V(j-1); K and V tiles come through rings of three, fetched by TMA
+// (one box per page, or 64 rows of a larger page, 128-byte swizzle) through the request's block table two tiles
+// ahead.  Two such CTAs fit an SM (256 of its 512 TMEM columns each).
+//
+// Hand-overs are kept cheap, because a tile's fixed costs weigh as much as its exponentials (measured, see
+// probe_sm100.cu): the threads wait once per tile (S(j) is issued after O += P(j-2) V(j-2), so its completion also
+// says that P's buffer is free); every wait is made by all lanes of its warp with a vote at the end (76 cycles
+// when the phase is done, against 270 for one polling lane and a shuffle); every softmax thread arrives on P's
+// barrier itself; the MMA warp waits for the next K before it waits for P.
 //
 // The exponentials use a reference maximum that is set from the first tile and raised only when a later tile's
 // p summed to more than 2^8 in some row (then that tile's row maximum is taken, O and the row sum are rescaled, O
@@ -27,9 +32,7 @@
 #define FA_BM 128
 #define FA_BN 64
 #define FA_D 64
-#ifndef FA_KV_STAGES
 #define FA_KV_STAGES 3
-#endif
 #define FA_S_BUFFERS 2
 #define FA_THREADS 192            // warps 0-3: softmax / output rows; warp 4: TMA producer; warp 5: MMA issue, TMEM owner
 
