@@ -122,9 +122,9 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ 
     tc_fence_after();
     const uint32_t tmem_s0 = tmem_base_slot, tmem_o = tmem_base_slot + (uint32_t)(FA_S_BUFFERS * FA_BN);
     const uint32_t tmem_p0 = tmem_o + (uint32_t)FA_D;
-    pdl_wait();
-    pdl_trigger();
-
+    // Tiles, positions and block tables were written before the step's first kernel started: they are read, and the
+    // first pages looked up, before the wait for the kernel before this one (which rotates q and writes this
+    // portion's keys and values); only what moves q, K, V or the output comes after it.
     const int p0 = positions[row0];
     const int hi = p0 + nrows - 1;
     const int lo = window > 0 ? max(0, p0 - window + 1) : 0;
@@ -136,15 +136,21 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ 
         // read is not on the critical path) and issues that box of K and of V.
         const int rows_per_box = min(page_size, FA_BN), boxes = FA_BN / rows_per_box;
         const uint32_t box_bytes = (uint32_t)rows_per_box * 128u;
-        if (lane == 0) {
-            mbar_expect_tx(q_full, Q_BYTES);
-            tma_load_2d(sQ, &q_map, q_full, h * FA_D, row0);
-        }
         auto page_of = [&](int kt) -> int {                                  // beyond the context: any page (masked)
             const int key = kt * FA_BN + lane * rows_per_box;
             return lane < boxes ? bt[min(key / page_size, max_blocks - 1)] : 0;
         };
         int page_next = page_of(kt0);
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&q_map)) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&kv_map)) : "memory");
+        }
+        pdl_wait();
+        pdl_trigger();
+        if (lane == 0) {
+            mbar_expect_tx(q_full, Q_BYTES);
+            tma_load_2d(sQ, &q_map, q_full, h * FA_D, row0);
+        }
         bool ok = true;
         for (int j = 0; j < n_kt && ok; ++j) {
             const int s = j % FA_KV_STAGES, u = j / FA_KV_STAGES;
@@ -168,6 +174,7 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ 
                             ((page * 2 + 1) * nkv + kvh) * page_size + in_page);
         }
     } else if (warp == 5) {
+        pdl_wait();
         // ---- MMA issue.  The whole warp walks the loop and waits (so that tile indices, descriptors and
         // addresses are uniform values of the warp); one elected lane issues.
         // S: D F32, A/B BF16 K-major, N 64, M 128.  PV: the same with B MN-major (bit 16).
@@ -219,6 +226,7 @@ fa_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ 
             if (j + 2 < n_kt) issue_s(j + 2);
         }
     } else if (warp < 4) {
+        pdl_wait();
         // ---- softmax and output: thread = query row
         const int row = warp * 32 + lane;
         const int prow = p0 + row;
