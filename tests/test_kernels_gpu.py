@@ -951,3 +951,37 @@ def test_probe_sm100_reports_cycles_in_range():
     assert 20 < r["tcgen05.mma M128 N64 K16"] <= r["tcgen05.mma M128 N128 K16"] <= r["tcgen05.mma M128 N256 K16"] < 400
     assert r["mbarrier wait (done), every lane"] < r["mbarrier wait (done), lane 0 + shuffle"]
     assert r["softmax pass of 64 columns, 1 warp per scheduler"] < r["softmax pass of 64 columns, 2 warps per scheduler"]
+
+
+@pytest.mark.gpu
+def test_attention_kernels_at_long_contexts():
+    """Portions of prompts and single tokens far into contexts of 40,000 and 70,001 tokens (5,000 pages a request):
+    the split decode kernel with one, eight and two hundred splits, and both prefill kernels, whose portions start
+    hundreds of key tiles into the context."""
+    from railgun_b200 import ops
+    nh, nkv, d, page, ctx, ql = 8, 2, 64, 16, [40000, 70001], [256, 130]
+    c = make_paged_case(len(ctx), ctx, ql, nh, nkv, d, page, torch.bfloat16, seed=5)
+    scale = d ** -0.5
+    ref = attention_reference(c, nh, nkv, d, page, 0, scale)
+    T = c["T"]
+    q = c["q"].reshape(T, nh * d).contiguous().to(DEV)
+    req = torch.tensor(c["req"], dtype=torch.int32, device=DEV)
+    pos = torch.tensor(c["positions"], dtype=torch.int32, device=DEV)
+    kv, bt = c["kv"].to(DEV), c["bt"].to(DEV)
+    for splits in (1, 8, 200):
+        out = torch.full((T, nh * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+        ops.decode_attention(q, nh * d, out, kv, bt, None, T, req, pos, nh, nkv, d, 0, scale, splits)
+        assert rel_err(out, ref) < 1e-2, splits
+    out = torch.full((T, nh * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.prefill_attention(q, nh * d, out, kv, bt, _tiles_of(ql), pos, nh, nkv, d, 0, scale)
+    assert rel_err(out, ref) < 1e-2
+    wide = torch.zeros(T, (nh + 2 * nkv) * d, dtype=torch.bfloat16, device=DEV)
+    wide[:, :nh * d] = q
+    tiles, off = [], 0
+    for r, n in enumerate(ql):
+        tiles += [(off + k, min(128, n - k), r) for k in range(0, n, 128)]
+        off += n
+    out = torch.full((T, nh * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.prefill_attention_tc(wide, out, kv, bt, torch.tensor(tiles, dtype=torch.int32, device=DEV), pos, nh, nkv, d, 0, scale)
+    ops.tc_gemm_check()
+    assert rel_err(out, ref) < 1e-2
